@@ -1,0 +1,366 @@
+#!/usr/bin/env python
+"""Benchmark of the fused elementwise / row-reduction prefill path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one pass of the path over a batch of 4096 synthetic tokens per GPU:
+for each of 43 layers the four fused launches (Q8_0 embedding gather + residual
++ RMSNorm -> f32 + bf16; YaRN RoPE + E4M3 KV-cache store; clamped SwiGLU x
+router weights summed over 6 experts; 4x4 Sinkhorn + mix of the 4
+hyper-connection streams).  Rank 0 prints ONE JSON line.
+
+`--impl reference` times the CPU restatement of the same path (the oracle) on
+the host cores; it is the only mode, with the `cpu_baseline` leg of the default
+mode, that touches anything under oracle/.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+T_TOKENS, N_EMBD, VOCAB, KV_DIM, N_ROT, N_SLOTS, FF_DIM, TOP_K, N_LAYERS = (
+    4096, 4096, 129280, 512, 64, 65536, 2048, 6, 43)
+OP_NAMES = ("gather", "kvstore", "swiglu", "hcmix")
+METRIC, UNIT = "fused_path_tokens_per_s", "tokens/s"
+FALLBACK_HBM_GBS = 6650.0      # earlier measurement on this pool, used only without MEASURED_PEAKS.json
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel
+# at the benchmark shape, from the ncu capture summarised under profiles/.
+NCU_TRAFFIC_BYTES = {"hcmix": None, "swiglu": None, "gather": None, "kvstore": None}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--tokens", type=int, default=T_TOKENS, help="token rows per GPU (weak) or per job (strong)")
+    ap.add_argument("--layers", type=int, default=N_LAYERS)
+    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--graph", type=int, default=1, help="replay the layer chain from a CUDA graph")
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU work budget of the baseline sample")
+    return ap.parse_args()
+
+
+def workload_config(args, tokens_per_gpu):
+    return {
+        "workload": "43-layer fused-op chain over 4096-token prefill rows (BASELINE configs[4]: "
+                    "per layer the ops of configs[1..4] at their full shapes)",
+        "tokens_per_gpu": tokens_per_gpu, "n_layers": args.layers, "n_embd": N_EMBD, "vocab": VOCAB,
+        "embedding": "Q8_0", "kv_dim": KV_DIM, "n_rot": N_ROT, "kv_slots": N_SLOTS,
+        "rope": "base 10000, YaRN factor 16, orig ctx 4096", "fp8_scale": "per-row amax/448",
+        "ff_dim": FF_DIM, "top_k": TOP_K, "glu": "gate<=10, |up|<=10 (reference clamp), expf",
+        "sinkhorn_iters": 20, "sharding": "token rows per rank, no collective",
+        "l2": "inputs larger than L2: 1.17 GB touched per layer between reuses of any buffer",
+    }
+
+
+# ----------------------------------------------------------------------------- inputs
+
+def make_inputs(tokens, seed):
+    """Seeded synthetic host inputs with the benchmark configs' shapes and distributions."""
+    import numpy as np
+    sys.path.insert(0, str(ROOT / "tests"))
+    import inputs as gen
+    g = gen.rng(seed)
+    return dict(
+        ids=g.integers(0, VOCAB, tokens).astype(np.int32), pos=np.arange(tokens, dtype=np.int32),
+        residual=gen.normal(g, (tokens, N_EMBD)), norm_w=gen.uniform(g, (N_EMBD,), 0.5, 1.5),
+        kv=gen.normal(g, (tokens, KV_DIM), 1.5), gate=gen.normal(g, (tokens, TOP_K, FF_DIM), 2.0),
+        up=gen.normal(g, (tokens, TOP_K, FF_DIM), 2.0), router_w=gen.router_weights(g, tokens, TOP_K),
+        hc_logits=gen.normal(g, (tokens, 16)), hc_resid=gen.normal(g, (tokens, 4, N_EMBD)))
+
+
+def make_table(seed=1234):
+    sys.path.insert(0, str(ROOT / "tests"))
+    import inputs as gen
+    return gen.q8_0_table(gen.rng(seed), VOCAB, N_EMBD)
+
+
+# ----------------------------------------------------------------------------- clocks
+
+class ClockSampler(threading.Thread):
+    """Polls SM clock and throttle reasons through NVML (read-only) while running."""
+
+    REASONS = {0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+               0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting"}
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.under_load, self.stop_flag = index, [], False, False
+        self.max_mhz, self.reasons, self.ok = None, set(), False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        while not self.stop_flag:
+            try:
+                mhz = self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM)
+                try:
+                    mask = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                self.samples.append((self.under_load, mhz))
+                if self.under_load:
+                    self.reasons |= {n for b, n in self.REASONS.items() if mask & b}
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def summary(self):
+        loaded = [m for u, m in self.samples if u] or [m for _, m in self.samples]
+        return {"sm_mhz": statistics.median(loaded) if loaded else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(loaded)}
+
+
+def physical_gpu_index(local_rank):
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except (ValueError, IndexError):
+            return local_rank
+    return local_rank
+
+
+# ----------------------------------------------------------------------------- CPU legs
+
+def oracle_layer_pass(oracle, table, x, rope, lo, hi):
+    """One layer of the path for rows [lo, hi) through the CPU oracle."""
+    import numpy as np
+    s = slice(lo, hi)
+    oracle.embed_gather_rows(table, oracle.TABLE_Q8_0, x["ids"][s], N_EMBD, residual=x["residual"][s],
+                             norm_w=x["norm_w"], want_bf16=True)
+    oracle.rope_fp8_store_rows(x["kv"][s], x["pos"][s], rope, N_ROT, oracle.FP8_ROW_AMAX)
+    oracle.swiglu_rows(x["gate"][s], x["up"][s], x["router_w"][s], oracle.GLU_CLAMP_REF, 10.0, combine=True)
+    oracle.hc_sinkhorn_mix_rows(x["hc_logits"][s], x["hc_resid"][s])
+    return hi - lo
+
+
+def cpu_path_seconds(x, table, n_tokens, n_layers, threads):
+    """Time n_layers of the path over the first n_tokens rows with `threads` host threads."""
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import oracle_lib as oracle
+    oracle.lib()
+    rope = oracle.rope_params_explicit(10000.0, 16.0, 4096)
+    bounds = [(n_tokens * i // threads, n_tokens * (i + 1) // threads) for i in range(threads)]
+
+    def work(lo, hi):
+        for _ in range(n_layers):
+            oracle_layer_pass(oracle, table, x, rope, lo, hi)
+
+    t0 = time.perf_counter()
+    if threads == 1:
+        work(0, n_tokens)
+    else:
+        ts = [threading.Thread(target=work, args=b) for b in bounds if b[1] > b[0]]
+        [t.start() for t in ts]
+        [t.join() for t in ts]
+    dt = time.perf_counter() - t0
+    return dt
+
+
+def cpu_baseline_leg(x, table, budget_s, full_layers):
+    """Scalar oracle, one thread, on a bounded sample; throughput scaled to the full layer count."""
+    sample_tokens = min(128, len(x["ids"]))
+    probe = cpu_path_seconds(x, table, sample_tokens, 1, 1)
+    layers = max(1, min(full_layers, int(budget_s / max(probe, 1e-6))))
+    dt = cpu_path_seconds(x, table, sample_tokens, layers, 1)
+    per_layer = dt / layers
+    value = sample_tokens / (per_layer * full_layers)
+    return {"value": value, "unit": UNIT, "cores": 1, "kind": "port",
+            "sample": f"{sample_tokens} tokens x {layers} layers in {dt:.2f} s on one thread; "
+                      f"scaled to {full_layers} layers"}
+
+
+def run_reference_arm(args):
+    """The reference's CPU path: the scalar C restatement, all host threads, bounded sample per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = len(os.sched_getaffinity(0))
+    tokens = min(args.tokens, 8 * threads)
+    x = make_inputs(tokens, seed=100)
+    table = make_table()
+    probe = cpu_path_seconds(x, table, tokens, 1, threads)
+    total_steps = args.steps + args.warmup
+    layers = max(1, min(args.layers, int(120.0 / max(probe * total_steps, 1e-6))))
+    for _ in range(args.warmup):
+        cpu_path_seconds(x, table, tokens, layers, threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_path_seconds(x, table, tokens, layers, threads)
+    dt = (time.perf_counter() - t0) / args.steps
+    ms_per_step = dt / layers * args.layers * 1e3 * (args.tokens / tokens)
+    value = args.tokens / (ms_per_step * 1e-3)
+    sample = (f"each step: {tokens} tokens x {layers} layers on {threads} threads "
+              f"({dt:.2f} s), scaled to {args.tokens} tokens x {args.layers} layers")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, args.tokens),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference ships no CPU implementation of this path (its CPU model, antirez/ds4, is not "
+                "in its tree); this is the scalar C restatement of its kernels' arithmetic",
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- GPU arm
+
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    from ds4cuda_b200 import shard
+    from ds4cuda_b200.path import PrefillPath
+
+    tokens = shard.tokens_per_rank(world, args.tokens, args.scaling)[rank]
+    path = PrefillPath(n_tokens=tokens, max_layers=args.layers, use_graph=args.graph)
+    table = make_table()
+    path.upload_table(table)
+    x = make_inputs(tokens, seed=100 + rank)
+    pinned_in = {k: torch.from_numpy(v).pin_memory() for k, v in x.items()}
+    path.upload(pinned_in)
+
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
+
+    # ---- device-resident timing: W warm-up steps, then exactly K timed steps
+    for _ in range(args.warmup):
+        path.run_device(args.layers)
+    torch.cuda.synchronize()
+    shard.barrier()
+    torch.cuda.synchronize()
+    sampler.under_load = True
+    ms_total = path.time_device(args.layers, 0, args.steps)
+    torch.cuda.synchronize()
+    sampler.under_load = False
+    shard.barrier()
+    ms_step = shard.max_over_ranks(ms_total) / args.steps
+    job_tokens = shard.sum_over_ranks(tokens)
+    value = job_tokens / (ms_step * 1e-3)
+
+    # ---- per-kernel durations inside the chain (events around every launch)
+    per_op_ms, per_op_n = path.profile_ops(args.layers)
+    ops_table = {}
+    peaks_file = ROOT / "MEASURED_PEAKS.json"
+    if peaks_file.exists():
+        peak, peak_src = float(json.loads(peaks_file.read_text())["hbm_gbs"]), "measured"
+    else:
+        peak, peak_src = FALLBACK_HBM_GBS, "fallback"
+    for i, name in enumerate(OP_NAMES):
+        us = per_op_ms[i] * 1e3 / per_op_n[i]
+        gbs = path.op_bytes(i) / (us * 1e-6) / 1e9
+        ops_table[name] = {"us_per_launch": round(us, 2), "algorithmic_bytes": path.op_bytes(i),
+                           "gbs": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4),
+                           "frac_of_8000": round(gbs / 8000.0, 4)}
+    dominant = max(OP_NAMES, key=lambda n: ops_table[n]["us_per_launch"])
+    roofline = {"bound": "hbm", "kernel": dominant, "achieved": ops_table[dominant]["gbs"], "peak": peak,
+                "peak_source": peak_src, "unit": "GB/s", "frac": ops_table[dominant]["frac_of_peak"],
+                "traffic": NCU_TRAFFIC_BYTES[dominant]}
+    step_bytes = sum(path.op_bytes(i) for i in range(4)) * args.layers
+    hbm_gbs_step = step_bytes / (ms_step * 1e-3) / 1e9
+
+    # ---- end to end through the host-buffer entry point: H2D of every input,
+    #      the layer chain, D2H of every output, per step
+    out_shapes = path.output_shapes()
+    tdt = {"float32": torch.float32, "uint16": torch.int16, "uint8": torch.uint8}
+    pinned_out = {k: torch.empty(s, dtype=tdt[np.dtype(d).name]).pin_memory()
+                  for k, (s, d) in out_shapes.items() if k != "kv_tail"}
+    h2d = sum(t.numel() * t.element_size() for t in pinned_in.values())
+    d2h = sum(t.numel() * t.element_size() for t in pinned_out.values())
+    path.run_host(pinned_in, args.layers, pinned_out)            # warm-up
+    torch.cuda.synchronize()
+    shard.barrier()
+    sampler.under_load = True
+    e2e_ms = 0.0
+    for _ in range(max(1, args.e2e_steps)):
+        e2e_ms += path.run_host(pinned_in, args.layers, pinned_out)["ms"]
+    sampler.under_load = False
+    torch.cuda.synchronize()
+    shard.barrier()
+    e2e_ms_step = shard.max_over_ranks(e2e_ms) / max(1, args.e2e_steps)
+    e2e_value = job_tokens / (e2e_ms_step * 1e-3)
+
+    sampler.stop_flag = True
+    sampler.join(timeout=2)
+    clocks = sampler.summary()
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu = cpu_baseline_leg(x, table, args.cpu_seconds, args.layers)
+
+    launches = path.launches_per_run(args.layers) * args.steps
+    path.close()
+    if world > 1:
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling,
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, tokens),
+        "hbm_gbs_per_gpu": round(hbm_gbs_step, 1),
+        "hbm_frac_of_peak": round(hbm_gbs_step / peak, 4), "hbm_frac_of_8000": round(hbm_gbs_step / 8000.0, 4),
+        "ops": ops_table, "roofline": roofline, "cpu_baseline": cpu,
+        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms_step,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches, "cuda_graph": bool(args.graph), "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    args = parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gpus > 1 and world == 1 and "RANK" not in os.environ:
+        # launched without torchrun: start one rank per GPU ourselves
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", str(29400 + os.getpid() % 500),
+               str(Path(__file__).resolve())] + sys.argv[1:]
+        raise SystemExit(subprocess.call(cmd))
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,235 @@
+// capi.cu — the checked `extern "C"` entry points of libds4b200 for the batched
+// kernels: argument validation, launch, launch-error check.  Nothing here
+// allocates or synchronises (ds4b200_device_status() excepted).
+#include <cerrno>
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/ds4b200.h"
+#include "kernels.cuh"
+
+namespace ds4b200 {
+thread_local char t_error[256] = "";
+
+int set_error(int code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_error, sizeof t_error, fmt, ap);
+    va_end(ap);
+    return code;
+}
+}  // namespace ds4b200
+
+namespace {
+
+using ds4b200::t_error;
+#define fail ds4b200::set_error
+
+int launched(const char *what) {
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(-EIO, "%s: %s", what, cudaGetErrorString(e));
+    return 0;
+}
+
+bool a16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+bool a4(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 3u) == 0; }
+
+#define REQUIRE(cond, ...) do { if (!(cond)) return fail(-EINVAL, __VA_ARGS__); } while (0)
+#define STREAM(s) static_cast<cudaStream_t>(s)
+
+}  // namespace
+
+extern "C" {
+
+const char *ds4b200_version(void) { return "ds4b200 0.1 (sm_100a)"; }
+const char *ds4b200_last_error(void) { return t_error; }
+
+int ds4b200_device_status(void) {
+    const int v = ds4b200::read_and_clear_device_status();
+    if (v < 0) return fail(-EIO, "device_status: CUDA error");
+    return v;
+}
+
+int ds4b200_add_f32(const float *a, const float *b, float *y, int64_t n, void *stream) {
+    REQUIRE(n >= 0, "add: n < 0");
+    if (n == 0) return 0;
+    REQUIRE(a && b && y, "add: null pointer");
+    ds4b200::add_f32(a, b, y, n, STREAM(stream));
+    return launched("add");
+}
+
+int ds4b200_rms_norm_rows_f32(const float *x, const float *residual_in, const float *w,
+                              int64_t weight_dim, float *y_f32, uint16_t *y_bf16,
+                              float *residual_out, int64_t n_rows, int n, float eps,
+                              void *stream) {
+    REQUIRE(n_rows >= 0 && n >= 0, "rms_norm_rows: negative size");
+    if (n_rows == 0 || n == 0) return 0;
+    REQUIRE(n_rows < ((int64_t)1 << 31), "rms_norm_rows: n_rows >= 2^31");
+    REQUIRE(x, "rms_norm_rows: x is null");
+    REQUIRE(y_f32 || y_bf16, "rms_norm_rows: no output");
+    REQUIRE(weight_dim == 0 || weight_dim == n || weight_dim == (int64_t)n * n_rows,
+            "rms_norm_rows: weight_dim must be 0, n or n*n_rows");
+    REQUIRE(weight_dim == 0 || w, "rms_norm_rows: w is null");
+    REQUIRE(!residual_out || residual_in, "rms_norm_rows: residual_out without residual_in");
+    ds4b200::rms_norm_rows(x, residual_in, w, weight_dim, y_f32, y_bf16, residual_out, n_rows, n,
+                           eps, STREAM(stream));
+    return launched("rms_norm_rows");
+}
+
+int ds4b200_embed_gather_rows(const void *table, int table_dtype, const int32_t *ids,
+                              int64_t n_tokens, int n_embd, const float *residual_in,
+                              const float *norm_w, float eps, float *out_rows, int n_replicas,
+                              float *normed_f32, uint16_t *normed_bf16, void *stream) {
+    REQUIRE(n_tokens >= 0 && n_embd >= 0, "embed_gather_rows: negative size");
+    if (n_tokens == 0 || n_embd == 0) return 0;
+    REQUIRE(n_tokens < ((int64_t)1 << 31), "embed_gather_rows: n_tokens >= 2^31");
+    REQUIRE(table && ids, "embed_gather_rows: null table or ids");
+    REQUIRE(table_dtype == DS4B200_TABLE_F16 || table_dtype == DS4B200_TABLE_Q8_0,
+            "embed_gather_rows: unknown table dtype");
+    REQUIRE(table_dtype != DS4B200_TABLE_Q8_0 || n_embd % 32 == 0,
+            "embed_gather_rows: Q8_0 rows need n_embd %% 32 == 0");
+    REQUIRE(!out_rows || n_replicas >= 1, "embed_gather_rows: n_replicas < 1");
+    REQUIRE(out_rows || norm_w, "embed_gather_rows: no output");
+    REQUIRE(!norm_w || normed_f32 || normed_bf16, "embed_gather_rows: norm_w without normed output");
+    ds4b200::embed_gather_rows(table, table_dtype, ids, 0, n_tokens, n_embd, residual_in, norm_w,
+                               eps, out_rows, n_replicas, normed_f32, normed_bf16, STREAM(stream));
+    return launched("embed_gather_rows");
+}
+
+int ds4b200_rope_rows_f32(const float *x_in, float *x_out, int64_t n_tokens, int n_heads,
+                          int head_dim, int n_rot, const int32_t *pos,
+                          const ds4b200_rope_params *params, int inverse, int unit_rms,
+                          float eps, void *stream) {
+    REQUIRE(n_tokens >= 0 && n_heads >= 0 && head_dim >= 0, "rope_rows: negative size");
+    if (n_tokens == 0 || n_heads == 0 || head_dim == 0) return 0;
+    REQUIRE(n_tokens * n_heads < ((int64_t)1 << 31), "rope_rows: too many rows");
+    REQUIRE(x_in && x_out && pos && params, "rope_rows: null pointer");
+    REQUIRE(n_rot >= 0 && n_rot <= head_dim && (n_rot & 1) == 0, "rope_rows: n_rot must be even and <= head_dim");
+    REQUIRE(params->theta_scale > 0.0f || params->freq_base > 0.0f, "rope_rows: no theta_scale and no freq_base");
+    ds4b200::rope_rows(x_in, x_out, n_tokens, n_heads, head_dim, n_rot, pos, 0, *params, inverse,
+                       unit_rms, eps, STREAM(stream));
+    return launched("rope_rows");
+}
+
+int ds4b200_fp8_kv_round_trip_rows_f32(const float *kv_in, float *kv_out, int64_t n_rows,
+                                       int head_dim, int n_rot, void *stream) {
+    REQUIRE(n_rows >= 0 && head_dim >= 0, "fp8_kv_round_trip_rows: negative size");
+    if (n_rows == 0 || head_dim == 0) return 0;
+    REQUIRE(kv_in && kv_out, "fp8_kv_round_trip_rows: null pointer");
+    REQUIRE(n_rot >= 0 && n_rot <= head_dim && (head_dim - n_rot) % 64 == 0,
+            "fp8_kv_round_trip_rows: head_dim - n_rot must be a multiple of 64");
+    ds4b200::fp8_kv_round_trip_rows(kv_in, kv_out, n_rows, head_dim, n_rot, STREAM(stream));
+    return launched("fp8_kv_round_trip_rows");
+}
+
+int ds4b200_rope_fp8_store_rows(const float *kv_in, int64_t n_rows, int head_dim, int n_rot,
+                                const int32_t *pos, const ds4b200_rope_params *params,
+                                const float *norm_w, float eps, int scale_mode,
+                                const int32_t *slots, uint8_t *codes, float *scales,
+                                float *tail_out, float *rope_out, void *stream) {
+    REQUIRE(n_rows >= 0, "rope_fp8_store_rows: n_rows < 0");
+    if (n_rows == 0) return 0;
+    REQUIRE(kv_in && codes && scales, "rope_fp8_store_rows: null pointer");
+    REQUIRE(head_dim > 0 && head_dim <= 1024 && head_dim % 4 == 0,
+            "rope_fp8_store_rows: head_dim must be a multiple of 4, at most 1024");
+    REQUIRE(n_rot >= 0 && n_rot <= head_dim && n_rot % 4 == 0, "rope_fp8_store_rows: n_rot must be a multiple of 4");
+    REQUIRE(scale_mode == DS4B200_FP8_BLOCK64_POW2 || scale_mode == DS4B200_FP8_ROW_AMAX,
+            "rope_fp8_store_rows: unknown scale mode");
+    REQUIRE(scale_mode != DS4B200_FP8_BLOCK64_POW2 || ((head_dim - n_rot) % 64 == 0 && n_rot % 64 == 0),
+            "rope_fp8_store_rows: BLOCK64_POW2 needs head_dim - n_rot and n_rot multiples of 64");
+    REQUIRE(!params || pos, "rope_fp8_store_rows: params without pos");
+    REQUIRE(!params || params->theta_scale > 0.0f || params->freq_base > 0.0f,
+            "rope_fp8_store_rows: no theta_scale and no freq_base");
+    REQUIRE(a16(kv_in) && a16(norm_w) && a16(tail_out) && a16(rope_out) && a4(codes),
+            "rope_fp8_store_rows: kv_in, norm_w, tail_out, rope_out need 16-byte and codes 4-byte alignment");
+    ds4b200::rope_fp8_store_rows(kv_in, n_rows, head_dim, n_rot, pos, params, norm_w, eps,
+                                 scale_mode, slots, codes, scales, tail_out, rope_out,
+                                 STREAM(stream));
+    return launched("rope_fp8_store_rows");
+}
+
+int ds4b200_swiglu_rows_f32(const float *gate, const float *up, const float *weights, float *out,
+                            int64_t n_tokens, int k, int n, int mode, float clamp, int combine,
+                            int fast_exp, void *stream) {
+    REQUIRE(n_tokens >= 0 && k >= 0 && n >= 0, "swiglu_rows: negative size");
+    if (n_tokens == 0 || k == 0 || n == 0) return 0;
+    REQUIRE(gate && up && out, "swiglu_rows: null pointer");
+    REQUIRE(mode >= DS4B200_GLU_PLAIN && mode <= DS4B200_GLU_CLAMP_SYM, "swiglu_rows: unknown mode");
+    ds4b200::swiglu_rows(gate, up, weights, out, n_tokens, k, n, mode, clamp, combine, fast_exp,
+                         STREAM(stream));
+    return launched("swiglu_rows");
+}
+
+int ds4b200_hc_pre_rows_f32(const float *residual_hc, const uint16_t *hc_fn,
+                            const float *hc_scale, const float *hc_base, float *post, float *comb,
+                            float *out, int64_t n_tokens, int n_embd, int sinkhorn_iters,
+                            float eps, void *stream) {
+    REQUIRE(n_tokens >= 0, "hc_pre_rows: n_tokens < 0");
+    if (n_tokens == 0) return 0;
+    REQUIRE(n_tokens < ((int64_t)1 << 31), "hc_pre_rows: n_tokens >= 2^31");
+    REQUIRE(residual_hc && hc_fn && hc_scale && hc_base && post && comb && out,
+            "hc_pre_rows: null pointer");
+    REQUIRE(n_embd > 0 && n_embd % 4 == 0 && n_embd <= 8192,
+            "hc_pre_rows: n_embd must be a multiple of 4, at most 8192");
+    REQUIRE(sinkhorn_iters >= 1, "hc_pre_rows: sinkhorn_iters < 1");
+    ds4b200::hc_pre_rows(residual_hc, hc_fn, hc_scale, hc_base, post, comb, out, n_tokens, n_embd,
+                         sinkhorn_iters, eps, STREAM(stream));
+    return launched("hc_pre_rows");
+}
+
+int ds4b200_hc_post_rows_f32(const float *block_out, const float *block_out2,
+                             const float *residual_hc, const float *post, const float *comb,
+                             float *out_hc, int64_t n_tokens, int n_embd, void *stream) {
+    REQUIRE(n_tokens >= 0, "hc_post_rows: n_tokens < 0");
+    if (n_tokens == 0) return 0;
+    REQUIRE(n_tokens < ((int64_t)1 << 31), "hc_post_rows: n_tokens >= 2^31");
+    REQUIRE(residual_hc && comb && out_hc, "hc_post_rows: null pointer");
+    REQUIRE(!block_out || post, "hc_post_rows: block_out without post");
+    REQUIRE(!block_out2 || block_out, "hc_post_rows: block_out2 without block_out");
+    REQUIRE(n_embd > 0 && n_embd % 4 == 0 && n_embd <= 8192,
+            "hc_post_rows: n_embd must be a multiple of 4, at most 8192");
+    ds4b200::hc_post_rows(block_out, block_out2, residual_hc, post, comb, nullptr, nullptr, out_hc,
+                          n_tokens, n_embd, 0, 0.0f, STREAM(stream));
+    return launched("hc_post_rows");
+}
+
+int ds4b200_hc_sinkhorn_mix_rows_f32(const float *logits, const float *residual_hc, float *out_hc,
+                                     float *comb_out, int64_t n_tokens, int n_embd,
+                                     int sinkhorn_iters, float eps, void *stream) {
+    REQUIRE(n_tokens >= 0, "hc_sinkhorn_mix_rows: n_tokens < 0");
+    if (n_tokens == 0) return 0;
+    REQUIRE(n_tokens < ((int64_t)1 << 31), "hc_sinkhorn_mix_rows: n_tokens >= 2^31");
+    REQUIRE(logits && residual_hc && out_hc, "hc_sinkhorn_mix_rows: null pointer");
+    REQUIRE(n_embd > 0 && n_embd % 4 == 0 && n_embd <= 8192,
+            "hc_sinkhorn_mix_rows: n_embd must be a multiple of 4, at most 8192");
+    REQUIRE(sinkhorn_iters >= 1, "hc_sinkhorn_mix_rows: sinkhorn_iters < 1");
+    ds4b200::hc_post_rows(nullptr, nullptr, residual_hc, nullptr, nullptr, logits, comb_out, out_hc,
+                          n_tokens, n_embd, sinkhorn_iters, eps, STREAM(stream));
+    return launched("hc_sinkhorn_mix_rows");
+}
+
+int ds4b200_e4m3_encode_f32(const float *x, uint8_t *codes, int64_t n, void *stream) {
+    REQUIRE(n >= 0, "e4m3_encode: n < 0");
+    if (n == 0) return 0;
+    REQUIRE(x && codes, "e4m3_encode: null pointer");
+    ds4b200::e4m3_encode(x, codes, n, STREAM(stream));
+    return launched("e4m3_encode");
+}
+
+int ds4b200_e4m3_decode_f32(const uint8_t *codes, float *x, int64_t n, void *stream) {
+    REQUIRE(n >= 0, "e4m3_decode: n < 0");
+    if (n == 0) return 0;
+    REQUIRE(x && codes, "e4m3_decode: null pointer");
+    ds4b200::e4m3_decode(codes, x, n, STREAM(stream));
+    return launched("e4m3_decode");
+}
+
+int ds4b200_e4m3_selfcheck(uint32_t first_bits, uint64_t count, unsigned long long *mismatches,
+                           void *stream) {
+    REQUIRE(mismatches, "e4m3_selfcheck: null pointer");
+    REQUIRE(count <= ((uint64_t)1 << 32), "e4m3_selfcheck: count > 2^32");
+    ds4b200::e4m3_selfcheck(first_bits, count, mismatches, STREAM(stream));
+    return launched("e4m3_selfcheck");
+}
+
+}  // extern "C"

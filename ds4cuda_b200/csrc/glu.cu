@@ -1,0 +1,157 @@
+// glu.cu — SwiGLU over token rows: plain silu(g)*u (cuda/glu.cu:56-75), the
+// clamped, router-weighted form of the routed-expert epilogue
+// (cuda/moe_iq2_pair.cu:352-373), and the sum over the k selected experts fused
+// in, so the k gate rows and k up rows of a token are read once and one
+// combined row is written.
+//
+// Data movement: pure streaming.  One thread owns one float4 column of one
+// token across all k slots: 2k independent 128-bit loads are in flight per
+// thread before the first use, stores are 128-bit, all coalesced.
+#include "device_utils.cuh"
+#include "kernels.cuh"
+
+namespace ds4b200 {
+namespace {
+
+template <bool FAST>
+__device__ __forceinline__ float exp_sel(float x) { return FAST ? __expf(x) : expf(x); }
+
+template <int MODE, bool FAST>
+__device__ __forceinline__ float glu_one(float g, float u, float clamp) {
+    if (MODE == DS4B200_GLU_PLAIN) {
+        // g * sigmoid_stable(g) * u, cuda/glu.cu:56-75
+        float sg;
+        if (g >= 0.0f) { const float e = exp_sel<FAST>(-g); sg = 1.0f / (1.0f + e); }
+        else           { const float e = exp_sel<FAST>(g);  sg = e / (1.0f + e); }
+        return (g * sg) * u;
+    }
+    if (clamp > 1.0e-6f) {
+        if (g > clamp) g = clamp;
+        if (MODE == DS4B200_GLU_CLAMP_SYM && g < -clamp) g = -clamp;
+        if (u > clamp) u = clamp;
+        if (u < -clamp) u = -clamp;
+    }
+    float s;
+    if (g >= 0.0f) { const float e = exp_sel<FAST>(-g); s = g / (1.0f + e); }
+    else           { const float e = exp_sel<FAST>(g);  s = g * e / (1.0f + e); }
+    return s * u;
+}
+
+template <int MODE, bool FAST>
+__device__ __forceinline__ float4 glu4(float4 g, float4 u, float clamp) {
+    return make_float4(glu_one<MODE, FAST>(g.x, u.x, clamp), glu_one<MODE, FAST>(g.y, u.y, clamp),
+                       glu_one<MODE, FAST>(g.z, u.z, clamp), glu_one<MODE, FAST>(g.w, u.w, clamp));
+}
+
+// K > 0: compile-time slot count (loads fully unrolled); K == 0: runtime k.
+template <int K, int MODE, bool FAST>
+__global__ void __launch_bounds__(256)
+swiglu_vec_kernel(const float *__restrict__ gate, const float *__restrict__ up,
+                  const float *__restrict__ weights, float *__restrict__ out, int64_t n_tokens,
+                  int k_rt, int n4, float clamp, int combine) {
+    const int k = K > 0 ? K : k_rt;
+    const int64_t total = n_tokens * n4;
+    for (int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; gid < total;
+         gid += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = gid / n4;
+        const int c = (int)(gid - t * n4);
+        const int64_t base = (t * k) * (int64_t)n4 + c;       // float4 index of slot 0
+        if (K > 0) {
+            float4 g[K > 0 ? K : 1], u[K > 0 ? K : 1];
+#pragma unroll
+            for (int s = 0; s < K; ++s) {
+                g[s] = ld_stream4(gate + 4 * (base + (int64_t)s * n4));
+                u[s] = ld_stream4(up + 4 * (base + (int64_t)s * n4));
+            }
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int s = 0; s < K; ++s) {
+                float4 v = glu4<MODE, FAST>(g[s], u[s], clamp);
+                if (weights) {
+                    const float w = __ldg(weights + t * k + s);
+                    v.x *= w; v.y *= w; v.z *= w; v.w *= w;
+                }
+                if (combine) acc = (s == 0) ? v : add4(acc, v);
+                else st_stream4(out + 4 * (base + (int64_t)s * n4), v);
+            }
+            if (combine) st_stream4(out + 4 * gid, acc);
+        } else {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < k; ++s) {
+                float4 v = glu4<MODE, FAST>(ld_stream4(gate + 4 * (base + (int64_t)s * n4)),
+                                            ld_stream4(up + 4 * (base + (int64_t)s * n4)), clamp);
+                if (weights) {
+                    const float w = __ldg(weights + t * k + s);
+                    v.x *= w; v.y *= w; v.z *= w; v.w *= w;
+                }
+                if (combine) acc = (s == 0) ? v : add4(acc, v);
+                else st_stream4(out + 4 * (base + (int64_t)s * n4), v);
+            }
+            if (combine) st_stream4(out + 4 * gid, acc);
+        }
+    }
+}
+
+template <int MODE, bool FAST>
+__global__ void swiglu_scalar_kernel(const float *gate, const float *up, const float *weights,
+                                     float *out, int64_t n_tokens, int k, int n, float clamp,
+                                     int combine) {
+    const int64_t total = n_tokens * n;
+    for (int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; gid < total;
+         gid += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = gid / n;
+        const int j = (int)(gid - t * n);
+        float acc = 0.0f;
+        for (int s = 0; s < k; ++s) {
+            const int64_t idx = (t * k + s) * (int64_t)n + j;
+            float v = glu_one<MODE, FAST>(gate[idx], up[idx], clamp);
+            if (weights) v *= weights[t * k + s];
+            if (combine) acc = (s == 0) ? v : acc + v;
+            else out[idx] = v;
+        }
+        if (combine) out[gid] = acc;
+    }
+}
+
+template <int MODE, bool FAST>
+void launch_mode(const float *gate, const float *up, const float *weights, float *out,
+                 int64_t n_tokens, int k, int n, float clamp, int combine, cudaStream_t s) {
+    constexpr int kThreads = 256;
+    const bool vec = (n & 3) == 0 && aligned16(gate) && aligned16(up) && aligned16(out);
+    if (!vec) {
+        int64_t blocks = (n_tokens * n + kThreads - 1) / kThreads;
+        if (blocks > 148 * 32) blocks = 148 * 32;
+        swiglu_scalar_kernel<MODE, FAST><<<(unsigned)blocks, kThreads, 0, s>>>(
+            gate, up, weights, out, n_tokens, k, n, clamp, combine);
+        return;
+    }
+    const int n4 = n >> 2;
+    int64_t blocks = (n_tokens * n4 + kThreads - 1) / kThreads;
+    if (blocks > (int64_t)1 << 30) blocks = (int64_t)1 << 30;
+#define DS4B200_GLU(K) swiglu_vec_kernel<K, MODE, FAST><<<(unsigned)blocks, kThreads, 0, s>>>( \
+        gate, up, weights, out, n_tokens, k, n4, clamp, combine)
+    if (k == 1) DS4B200_GLU(1);
+    else if (k == 6) DS4B200_GLU(6);
+    else if (k == 8) DS4B200_GLU(8);
+    else DS4B200_GLU(0);
+#undef DS4B200_GLU
+}
+
+}  // namespace
+
+void swiglu_rows(const float *gate, const float *up, const float *weights, float *out,
+                 int64_t n_tokens, int k, int n, int mode, float clamp, int combine,
+                 int fast_exp, cudaStream_t s) {
+    if (n_tokens <= 0 || k <= 0 || n <= 0) return;
+#define DS4B200_MODE(M)                                                                          \
+    do {                                                                                          \
+        if (fast_exp) launch_mode<M, true>(gate, up, weights, out, n_tokens, k, n, clamp, combine, s); \
+        else launch_mode<M, false>(gate, up, weights, out, n_tokens, k, n, clamp, combine, s);       \
+    } while (0)
+    if (mode == DS4B200_GLU_PLAIN) DS4B200_MODE(DS4B200_GLU_PLAIN);
+    else if (mode == DS4B200_GLU_CLAMP_REF) DS4B200_MODE(DS4B200_GLU_CLAMP_REF);
+    else DS4B200_MODE(DS4B200_GLU_CLAMP_SYM);
+#undef DS4B200_MODE
+}
+
+}  // namespace ds4b200

@@ -1,0 +1,63 @@
+// kernels.cuh — internal launch functions of libds4b200.  Each one picks the
+// 128-bit path when pointers and sizes allow it and a scalar-load path of the
+// same kernel family otherwise, then enqueues on `stream`.  No argument checks
+// here: the checked C ABI (capi.cu) and the drop-in launchers (launchers.cu)
+// sit on top.
+#pragma once
+
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include "../../include/ds4b200.h"
+
+namespace ds4b200 {
+
+// Records the message ds4b200_last_error() returns on this thread; returns code.
+int set_error(int code, const char *fmt, ...);
+
+void add_f32(const float *a, const float *b, float *y, int64_t n, cudaStream_t s);
+
+void rms_norm_rows(const float *x, const float *residual_in, const float *w, int64_t weight_dim,
+                   float *y_f32, uint16_t *y_bf16, float *residual_out, int64_t n_rows, int n,
+                   float eps, cudaStream_t s);
+
+void embed_gather_rows(const void *table, int table_dtype, const int32_t *ids, int single_id,
+                       int64_t n_tokens, int n_embd, const float *residual_in,
+                       const float *norm_w, float eps, float *out_rows, int n_replicas,
+                       float *normed_f32, uint16_t *normed_bf16, cudaStream_t s);
+int read_and_clear_device_status();   // embedding.cu owns the status word
+
+// pos == nullptr: every token uses single_pos.
+void rope_rows(const float *x_in, float *x_out, int64_t n_tokens, int n_heads, int head_dim,
+               int n_rot, const int32_t *pos, int single_pos, const ds4b200_rope_params &p,
+               int inverse, int unit_rms, float eps, cudaStream_t s);
+
+void fp8_kv_round_trip_rows(const float *kv_in, float *kv_out, int64_t n_rows, int head_dim,
+                            int n_rot, cudaStream_t s);
+
+void rope_fp8_store_rows(const float *kv_in, int64_t n_rows, int head_dim, int n_rot,
+                         const int32_t *pos, const ds4b200_rope_params *p, const float *norm_w,
+                         float eps, int scale_mode, const int32_t *slots, uint8_t *codes,
+                         float *scales, float *tail_out, float *rope_out, cudaStream_t s);
+
+void swiglu_rows(const float *gate, const float *up, const float *weights, float *out,
+                 int64_t n_tokens, int k, int n, int mode, float clamp, int combine,
+                 int fast_exp, cudaStream_t s);
+
+void hc_pre_rows(const float *residual_hc, const uint16_t *hc_fn, const float *hc_scale,
+                 const float *hc_base, float *post, float *comb, float *out, int64_t n_tokens,
+                 int n_embd, int iters, float eps, cudaStream_t s);
+
+// logits != nullptr: comb is produced by Sinkhorn from logits (and stored to
+// comb_out when given); otherwise comb/post are read.
+void hc_post_rows(const float *block_out, const float *block_out2, const float *residual_hc,
+                  const float *post, const float *comb, const float *logits, float *comb_out,
+                  float *out_hc, int64_t n_tokens, int n_embd, int iters, float eps,
+                  cudaStream_t s);
+
+void e4m3_encode(const float *x, uint8_t *codes, int64_t n, cudaStream_t s);
+void e4m3_decode(const uint8_t *codes, float *x, int64_t n, cudaStream_t s);
+void e4m3_selfcheck(uint32_t first_bits, uint64_t count, unsigned long long *mismatches,
+                    cudaStream_t s);
+
+}  // namespace ds4b200

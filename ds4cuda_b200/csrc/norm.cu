@@ -1,0 +1,223 @@
+// norm.cu — RMSNorm over rows (with the residual add before it and the bf16
+// cast after it fused in) and the plain f32 add.
+//
+// Arithmetic follows cuda/norm.cu:52-105 and :126-197 of the reference:
+//   ss = sum x^2 (f32), scale = 1/sqrtf(ss/n + eps), y = x*scale*w
+// and cuda/elementwise.cu:36-43 (y = a + b).
+//
+// Data movement: each row is read from HBM once.  A row of up to 8192 floats is
+// held in registers between the reduction and the scaling pass — by one warp
+// (rows up to 1024 floats: no block barrier at all) or by one CTA.  All global
+// traffic is 128-bit, coalesced, with the streaming cache policy.  Rows that are
+// not 16-byte aligned, not a multiple of 4 long, or longer than 8192 take a
+// scalar two-pass kernel (second pass served by L2).
+#include "device_utils.cuh"
+#include "kernels.cuh"
+
+namespace ds4b200 {
+namespace {
+
+struct NormArgs {
+    const float *x;
+    const float *residual_in;
+    const float *w;
+    int64_t weight_dim;
+    float *y_f32;
+    uint16_t *y_bf16;
+    float *residual_out;
+    int64_t n_rows;
+    int n;
+    float eps;
+};
+
+__device__ __forceinline__ const float *row_gain(const NormArgs &a, int64_t row) {
+    if (a.weight_dim == 0) return nullptr;
+    return a.weight_dim == a.n ? a.w : a.w + row * a.n;
+}
+
+// Load this thread's float4s of one row (index first + j*stride), add the
+// residual, store the sum, return the partial sum of squares.
+template <int VPT>
+__device__ __forceinline__ float load_row(const NormArgs &a, int64_t row, int first, int stride,
+                                          float4 (&v)[VPT]) {
+    const int n4 = a.n >> 2;
+    const float *xr = a.x + row * a.n;
+    const float *rr = a.residual_in ? a.residual_in + row * a.n : nullptr;
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = first + j * stride;
+        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < n4) v[j] = ld_stream4(xr + 4 * i);
+    }
+    if (rr) {
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int i = first + j * stride;
+            if (i < n4) v[j] = add4(v[j], ld_stream4(rr + 4 * i));
+        }
+        if (a.residual_out) {
+            float *ro = a.residual_out + row * a.n;
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const int i = first + j * stride;
+                if (i < n4) st_stream4(ro + 4 * i, v[j]);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) ss += dot4(v[j]);
+    return ss;
+}
+
+template <int VPT>
+__device__ __forceinline__ void store_row(const NormArgs &a, int64_t row, int first, int stride,
+                                          const float4 (&v)[VPT], float scale) {
+    const int n4 = a.n >> 2;
+    const float *g = row_gain(a, row);
+    float *yf = a.y_f32 ? a.y_f32 + row * a.n : nullptr;
+    uint16_t *yb = a.y_bf16 ? a.y_bf16 + row * a.n : nullptr;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = first + j * stride;
+        if (i >= n4) continue;
+        float4 y = make_float4(v[j].x * scale, v[j].y * scale, v[j].z * scale, v[j].w * scale);
+        if (g) {
+            const float4 w4 = ld_ro4(g + 4 * i);
+            y.x *= w4.x; y.y *= w4.y; y.z *= w4.z; y.w *= w4.w;
+        }
+        if (yf) st_stream4(yf + 4 * i, y);
+        if (yb) st_bf16x4(yb + 4 * i, y);
+    }
+}
+
+// One CTA per row; the row lives in VPT float4 registers per thread.
+template <int VPT>
+__global__ void rms_norm_cta_kernel(NormArgs a) {
+    __shared__ float red[33];
+    const int64_t row = blockIdx.x;
+    float4 v[VPT];
+    float ss = load_row<VPT>(a, row, threadIdx.x, blockDim.x, v);
+    ss = block_sum(ss, red);
+    const float scale = rms_scale(ss, (float)a.n, a.eps);
+    store_row<VPT>(a, row, threadIdx.x, blockDim.x, v, scale);
+}
+
+// One warp per row (rows up to 1024 floats): shuffle reduction only.
+template <int VPT>
+__global__ void rms_norm_warp_kernel(NormArgs a) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= a.n_rows) return;
+    float4 v[VPT];
+    float ss = load_row<VPT>(a, row, lane, 32, v);
+    ss = warp_sum(ss);
+    const float scale = rms_scale(ss, (float)a.n, a.eps);
+    store_row<VPT>(a, row, lane, 32, v, scale);
+}
+
+// Any n, any natural alignment: scalar loads, two passes over the row.  When a
+// residual is added without residual_out the second pass repeats the add.
+__global__ void rms_norm_scalar_kernel(NormArgs a) {
+    __shared__ float red[33];
+    const int64_t row = blockIdx.x;
+    const float *xr = a.x + row * a.n;
+    const float *rr = a.residual_in ? a.residual_in + row * a.n : nullptr;
+    float *ro = (rr && a.residual_out) ? a.residual_out + row * a.n : nullptr;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < a.n; i += blockDim.x) {
+        float v = xr[i];
+        if (rr) v += rr[i];
+        if (ro) ro[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float scale = rms_scale(ss, (float)a.n, a.eps);
+    const float *g = row_gain(a, row);
+    for (int i = threadIdx.x; i < a.n; i += blockDim.x) {
+        float v = xr[i];
+        if (rr) v += rr[i];
+        float y = v * scale;
+        if (g) y *= g[i];
+        if (a.y_f32) a.y_f32[row * a.n + i] = y;
+        if (a.y_bf16) a.y_bf16[row * a.n + i] = bf16_bits(y);
+    }
+}
+
+__global__ void add_vec_kernel(const float *__restrict__ a, const float *__restrict__ b,
+                               float *__restrict__ y, int64_t n4) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4;
+         i += (int64_t)gridDim.x * blockDim.x)
+        st_stream4(y + 4 * i, add4(ld_stream4(a + 4 * i), ld_stream4(b + 4 * i)));
+}
+__global__ void add_scalar_kernel(const float *__restrict__ a, const float *__restrict__ b,
+                                  float *__restrict__ y, int64_t n) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)gridDim.x * blockDim.x)
+        y[i] = a[i] + b[i];
+}
+
+template <int VPT>
+void launch_cta(const NormArgs &a, int threads, cudaStream_t s) {
+    rms_norm_cta_kernel<VPT><<<(unsigned)a.n_rows, threads, 0, s>>>(a);
+}
+template <int VPT>
+void launch_warp(const NormArgs &a, cudaStream_t s) {
+    constexpr int kRowsPerCta = 8;
+    const unsigned grid = (unsigned)((a.n_rows + kRowsPerCta - 1) / kRowsPerCta);
+    rms_norm_warp_kernel<VPT><<<grid, kRowsPerCta * 32, 0, s>>>(a);
+}
+
+}  // namespace
+
+void add_f32(const float *a, const float *b, float *y, int64_t n, cudaStream_t s) {
+    if (n <= 0) return;
+    constexpr int kThreads = 256;
+    if (aligned16(a) && aligned16(b) && aligned16(y) && (n & 3) == 0) {
+        const int64_t n4 = n >> 2;
+        const int64_t blocks = (n4 + kThreads - 1) / kThreads;
+        add_vec_kernel<<<(unsigned)(blocks < 148 * 16 ? blocks : 148 * 16), kThreads, 0, s>>>(a, b, y, n4);
+    } else {
+        const int64_t blocks = (n + kThreads - 1) / kThreads;
+        add_scalar_kernel<<<(unsigned)(blocks < 148 * 16 ? blocks : 148 * 16), kThreads, 0, s>>>(a, b, y, n);
+    }
+}
+
+void rms_norm_rows(const float *x, const float *residual_in, const float *w, int64_t weight_dim,
+                   float *y_f32, uint16_t *y_bf16, float *residual_out, int64_t n_rows, int n,
+                   float eps, cudaStream_t s) {
+    if (n_rows <= 0 || n <= 0) return;
+    const NormArgs a{x, residual_in, w, weight_dim, y_f32, y_bf16, residual_out, n_rows, n, eps};
+    const bool vec = (n & 3) == 0 && n <= 8192 && aligned16(x) && aligned16(residual_in) &&
+                     aligned16(w) && aligned16(y_f32) && aligned8(y_bf16) &&
+                     aligned16(residual_out);
+    if (!vec) {
+        rms_norm_scalar_kernel<<<(unsigned)n_rows, 256, 0, s>>>(a);
+        return;
+    }
+    const int n4 = n >> 2;
+    if (n4 <= 256 && n_rows >= 64) {           // warp per row
+        const int vpt = (n4 + 31) / 32;
+        if (vpt <= 1) launch_warp<1>(a, s);
+        else if (vpt <= 2) launch_warp<2>(a, s);
+        else if (vpt <= 4) launch_warp<4>(a, s);
+        else launch_warp<8>(a, s);
+        return;
+    }
+    // CTA per row.  A handful of rows: as many threads as float4s (one load
+    // per thread, shortest dependency chain).  Many rows: 256 threads so that
+    // several CTAs share an SM.
+    int threads = 256;
+    if (n_rows < 296) {
+        threads = ((n4 + 31) / 32) * 32;
+        if (threads > 1024) threads = 1024;
+        if (threads < 32) threads = 32;
+    }
+    const int vpt = (n4 + threads - 1) / threads;
+    if (vpt <= 1) launch_cta<1>(a, threads, s);
+    else if (vpt <= 2) launch_cta<2>(a, threads, s);
+    else if (vpt <= 4) launch_cta<4>(a, threads, s);
+    else launch_cta<8>(a, threads, s);
+}
+
+}  // namespace ds4b200

@@ -1,0 +1,424 @@
+// rope_fp8.cu — partial (tail) YaRN RoPE over head rows, the E4M3FN KV
+// quantiser, and the two fused: RMSNorm -> RoPE -> FP8 bytes + scales written
+// straight into the KV cache.
+//
+// Arithmetic follows the reference:
+//   RoPE      cuda/rope.cu:136-201 (inverse: cuda/attn_out.cu:54-107): pair k of
+//             the tail uses theta_extrap = (float)pos * theta_scale^k built by k
+//             successive f32 multiplies, the YaRN ramp mix, accurate cosf/sinf.
+//   FP8       cuda/fp8_kv.cu:144-195: per 64 elements of the non-rotated prefix,
+//             scale = exp2f(ceilf(log2f(max(amax,1e-4)/448))), nearest E4M3FN
+//             value with ties to the even index, saturating at 448.
+//
+// Data movement: one warp owns one row of up to 1024 floats in registers
+// (lane l holds float4 number l, l+32, ...), so loads and stores are 128-bit and
+// coalesced, reductions are shuffles only, and the fused kernel reads 4 bytes
+// and writes ~1 byte per element instead of four f32 round trips.
+#include "device_utils.cuh"
+#include "kernels.cuh"
+
+namespace ds4b200 {
+namespace {
+
+constexpr int kRowsPerCta = 8;      // warps per CTA in the warp-per-row kernels
+
+struct RopeDev {
+    float freq_base, theta_scale, freq_scale, ext_factor, attn_factor, corr_low, corr_high;
+};
+
+__device__ __forceinline__ float rope_theta_scale(const RopeDev &p, int n_rot) {
+    return p.theta_scale > 0.0f ? p.theta_scale : powf(p.freq_base, -2.0f / (float)n_rot);
+}
+
+// cos/sin multipliers of tail pair k given theta_extrap for that pair.
+__device__ __forceinline__ void rope_cs(const RopeDev &p, int k, float theta_extrap, bool inverse,
+                                        float &c, float &s) {
+    const float theta_interp = p.freq_scale * theta_extrap;
+    float theta = theta_interp;
+    float mscale = p.attn_factor;
+    if (p.ext_factor != 0.0f) {
+        const float y = ((float)k - p.corr_low) / fmaxf(0.001f, p.corr_high - p.corr_low);
+        const float ramp_mix = (1.0f - fminf(1.0f, fmaxf(0.0f, y))) * p.ext_factor;
+        theta = theta_interp * (1.0f - ramp_mix) + theta_extrap * ramp_mix;
+        mscale *= 1.0f + 0.1f * logf(1.0f / p.freq_scale);
+    }
+    c = cosf(theta) * mscale;
+    s = sinf(theta) * mscale;
+    if (inverse) s = -s;
+}
+
+__device__ __forceinline__ void rotate(float &x0, float &x1, float c, float s) {
+    const float a = x0, b = x1;
+    x0 = a * c - b * s;
+    x1 = a * s + b * c;
+}
+
+// Rotate the float4 that starts at tail element `e_tail` (a multiple of 4).
+__device__ __forceinline__ void rope_float4(float4 &v, int e_tail, float posf, float ts,
+                                            const RopeDev &p, bool inverse) {
+    const int k0 = e_tail >> 1;
+    float te = posf;
+    for (int k = 0; k < k0; ++k) te *= ts;
+    float c, s;
+    rope_cs(p, k0, te, inverse, c, s);
+    rotate(v.x, v.y, c, s);
+    te *= ts;
+    rope_cs(p, k0 + 1, te, inverse, c, s);
+    rotate(v.z, v.w, c, s);
+}
+
+// ------------------------------- RoPE rows ---------------------------------
+template <int VPT>
+__global__ void __launch_bounds__(kRowsPerCta * 32)
+rope_rows_kernel(const float *x_in, float *x_out, int64_t n_rows, int n_heads, int head_dim,
+                 int n_rot, const int32_t *pos, int single_pos, RopeDev p, int inverse,
+                 int unit_rms, float eps) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * kRowsPerCta + (threadIdx.x >> 5);
+    if (row >= n_rows) return;
+    const int n4 = head_dim >> 2, n_nope = head_dim - n_rot;
+    const float *xr = x_in + row * head_dim;
+    float *yr = x_out + row * head_dim;
+    float4 v[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = lane + 32 * j;
+        v[j] = (i < n4) ? ld_stream4(xr + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (unit_rms) {
+        float ss = 0.0f;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) ss += dot4(v[j]);
+        const float scale = rms_scale(warp_sum(ss), (float)head_dim, eps);
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) { v[j].x *= scale; v[j].y *= scale; v[j].z *= scale; v[j].w *= scale; }
+    }
+    const float posf = (float)(pos ? pos[row / n_heads] : single_pos);
+    const float ts = rope_theta_scale(p, n_rot);
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = lane + 32 * j;
+        if (i >= n4) continue;
+        if (4 * i >= n_nope) rope_float4(v[j], 4 * i - n_nope, posf, ts, p, inverse != 0);
+        st_stream4(yr + 4 * i, v[j]);
+    }
+}
+
+// Any head_dim / n_rot (even) / alignment: one CTA per row, scalar accesses.
+__global__ void rope_rows_scalar_kernel(const float *x_in, float *x_out, int n_heads,
+                                        int head_dim, int n_rot, const int32_t *pos,
+                                        int single_pos, RopeDev p, int inverse, int unit_rms,
+                                        float eps) {
+    __shared__ float red[33];
+    const int64_t row = blockIdx.x;
+    const int n_nope = head_dim - n_rot;
+    const float *xr = x_in + row * head_dim;
+    float *yr = x_out + row * head_dim;
+    float scale = 1.0f;
+    if (unit_rms) {
+        float ss = 0.0f;
+        for (int i = threadIdx.x; i < head_dim; i += blockDim.x) ss += xr[i] * xr[i];
+        scale = rms_scale(block_sum(ss, red), (float)head_dim, eps);   // barrier: all reads done
+    }
+    for (int i = threadIdx.x; i < n_nope; i += blockDim.x) {
+        const float v = xr[i];
+        yr[i] = unit_rms ? v * scale : v;
+    }
+    const float posf = (float)(pos ? pos[row / n_heads] : single_pos);
+    const float ts = rope_theta_scale(p, n_rot);
+    for (int k = threadIdx.x; k < n_rot / 2; k += blockDim.x) {
+        float te = posf;
+        for (int q = 0; q < k; ++q) te *= ts;
+        float c, s;
+        rope_cs(p, k, te, inverse != 0, c, s);
+        float x0 = xr[n_nope + 2 * k], x1 = xr[n_nope + 2 * k + 1];
+        if (unit_rms) { x0 *= scale; x1 *= scale; }
+        rotate(x0, x1, c, s);
+        yr[n_nope + 2 * k] = x0;
+        yr[n_nope + 2 * k + 1] = x1;
+    }
+}
+
+// --------------------------- FP8 round trip ---------------------------------
+// head_dim % 64 == 0 and n_rot % 64 == 0: float4 number i belongs to 64-block
+// i/16, i.e. one half-warp, so the block amax is a 4-step shuffle.
+template <int VPT>
+__global__ void __launch_bounds__(kRowsPerCta * 32)
+fp8_round_trip_kernel(const float *kv_in, float *kv_out, int64_t n_rows, int head_dim, int n_rot) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * kRowsPerCta + (threadIdx.x >> 5);
+    if (row >= n_rows) return;
+    const int n4 = head_dim >> 2, n_nope = head_dim - n_rot;
+    const float *xr = kv_in + row * head_dim;
+    float *yr = kv_out + row * head_dim;
+    float4 v[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = lane + 32 * j;
+        v[j] = (i < n4) ? ld_stream4(xr + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = lane + 32 * j;
+        const float amax = fmaxf(halfwarp_max(amax4(v[j])), kFp8AmaxFloor);
+        if (i >= n4) continue;
+        if (4 * i < n_nope) {
+            const float scale = pow2_scale(amax);
+            v[j] = make_float4(e4m3_round_trip(v[j].x, scale), e4m3_round_trip(v[j].y, scale),
+                               e4m3_round_trip(v[j].z, scale), e4m3_round_trip(v[j].w, scale));
+        }
+        st_stream4(yr + 4 * i, v[j]);
+    }
+}
+
+// Scalar path: one warp per row, two elements of a 64-block per lane.
+__global__ void fp8_round_trip_scalar_kernel(const float *kv_in, float *kv_out, int64_t n_rows,
+                                             int head_dim, int n_rot) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= n_rows) return;
+    const int n_nope = head_dim - n_rot;
+    const float *xr = kv_in + row * head_dim;
+    float *yr = kv_out + row * head_dim;
+    for (int off = 0; off < n_nope; off += 64) {
+        const float a = xr[off + lane], b = xr[off + 32 + lane];
+        const float amax = fmaxf(warp_max(fmaxf(fabsf(a), fabsf(b))), kFp8AmaxFloor);
+        const float scale = pow2_scale(amax);
+        yr[off + lane] = e4m3_round_trip(a, scale);
+        yr[off + 32 + lane] = e4m3_round_trip(b, scale);
+    }
+    for (int i = n_nope + lane; i < head_dim; i += 32) yr[i] = xr[i];
+}
+
+// ------------------ fused norm -> RoPE -> FP8 cache store -------------------
+struct StoreArgs {
+    const float *kv_in;
+    int64_t n_rows;
+    int head_dim, n_rot;
+    const int32_t *pos;
+    RopeDev rope;
+    int do_rope;
+    const float *norm_w;
+    float eps;
+    int scale_mode;
+    const int32_t *slots;
+    uint8_t *codes;
+    float *scales;
+    float *tail_out;
+    float *rope_out;
+};
+
+template <int VPT>
+__global__ void __launch_bounds__(kRowsPerCta * 32) rope_fp8_store_kernel(StoreArgs a) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * kRowsPerCta + (threadIdx.x >> 5);
+    if (row >= a.n_rows) return;
+    const int head_dim = a.head_dim, n4 = head_dim >> 2, n_nope = head_dim - a.n_rot;
+    const float *xr = a.kv_in + row * head_dim;
+    float4 v[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = lane + 32 * j;
+        v[j] = (i < n4) ? ld_stream4(xr + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (a.norm_w) {                                   // cuda/forward_layer.cu:868 kv_norm
+        float ss = 0.0f;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) ss += dot4(v[j]);
+        const float scale = rms_scale(warp_sum(ss), (float)head_dim, a.eps);
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int i = lane + 32 * j;
+            if (i >= n4) continue;
+            const float4 w4 = ld_ro4(a.norm_w + 4 * i);
+            v[j] = make_float4(v[j].x * scale * w4.x, v[j].y * scale * w4.y,
+                               v[j].z * scale * w4.z, v[j].w * scale * w4.w);
+        }
+    }
+    if (a.do_rope) {                                  // cuda/forward_layer.cu:910 KV RoPE
+        const float posf = (float)a.pos[row];
+        const float ts = rope_theta_scale(a.rope, a.n_rot);
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int i = lane + 32 * j;
+            if (i < n4 && 4 * i >= n_nope) rope_float4(v[j], 4 * i - n_nope, posf, ts, a.rope, false);
+        }
+    }
+    if (a.rope_out) {
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int i = lane + 32 * j;
+            if (i < n4) st_stream4(a.rope_out + row * head_dim + 4 * i, v[j]);
+        }
+    }
+    const int64_t slot = a.slots ? a.slots[row] : row;
+    uint32_t *code_row = reinterpret_cast<uint32_t *>(a.codes + slot * head_dim);
+    if (a.scale_mode == DS4B200_FP8_ROW_AMAX) {
+        float amax = 0.0f;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) amax = fmaxf(amax, amax4(v[j]));
+        amax = fmaxf(warp_max(amax), kFp8AmaxFloor);
+        const float scale = amax / kFp8Max;
+        if (lane == 0) a.scales[slot] = scale;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int i = lane + 32 * j;
+            if (i >= n4) continue;
+            const float4 q = make_float4(clamp448(v[j].x / scale), clamp448(v[j].y / scale),
+                                         clamp448(v[j].z / scale), clamp448(v[j].w / scale));
+            __stcs(code_row + i, e4m3_encode4(q));
+        }
+    } else {                                          // cuda/fp8_kv.cu:161-180 scale rule
+        const int n_scales = n_nope >> 6;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int i = lane + 32 * j;
+            const float amax = fmaxf(halfwarp_max(amax4(v[j])), kFp8AmaxFloor);
+            if (i >= n4) continue;
+            if (4 * i < n_nope) {
+                const float scale = pow2_scale(amax);
+                if ((lane & 15) == 0) a.scales[slot * n_scales + (i >> 4)] = scale;
+                const float4 q = make_float4(clamp448(v[j].x / scale), clamp448(v[j].y / scale),
+                                             clamp448(v[j].z / scale), clamp448(v[j].w / scale));
+                __stcs(code_row + i, e4m3_encode4(q));
+            } else {
+                __stcs(code_row + i, 0u);
+                if (a.tail_out) st_stream4(a.tail_out + slot * a.n_rot + (4 * i - n_nope), v[j]);
+            }
+        }
+    }
+}
+
+// ------------------------------ E4M3 utilities --------------------------------
+__global__ void e4m3_encode_kernel(const float *x, uint8_t *codes, int64_t n) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)gridDim.x * blockDim.x)
+        codes[i] = e4m3_encode1(x[i]);
+}
+__global__ void e4m3_decode_kernel(const uint8_t *codes, float *x, int64_t n) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const float m = e4m3_magnitude(codes[i] & 0x7fu);
+        x[i] = (codes[i] & 0x80u) ? -m : m;
+    }
+}
+
+// The reference's selection rule stated arithmetically: the largest index whose
+// value is <= ax comes from the exponent and the top three mantissa bits, then
+// the tie rule of cuda/fp8_kv.cu:118-127 decides between it and the next one.
+__device__ __forceinline__ uint32_t e4m3_index_by_rule(float ax) {
+    ax = fminf(ax, kFp8Max);
+    uint32_t i;
+    if (ax < 0.015625f) {
+        i = (uint32_t)(ax * 512.0f);                   // floor; values are m * 2^-9
+    } else {
+        const uint32_t b = __float_as_uint(ax);
+        i = (((b >> 23) - 120u) << 3) | ((b >> 20) & 7u);
+    }
+    if (i < 126u) {
+        const float d0 = fabsf(ax - e4m3_magnitude(i));
+        const float d1 = fabsf(ax - e4m3_magnitude(i + 1u));
+        if (d1 < d0 || (d1 == d0 && (i & 1u))) ++i;
+    }
+    return i;
+}
+
+__global__ void e4m3_selfcheck_kernel(uint32_t first_bits, uint64_t count,
+                                      unsigned long long *mismatches) {
+    unsigned long long bad = 0;
+    for (uint64_t k = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; k < count;
+         k += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t bits = first_bits + (uint32_t)k;
+        const float v = __uint_as_float(bits);
+        if (v != v) continue;
+        const uint32_t want = ((bits >> 24) & 0x80u) | e4m3_index_by_rule(fabsf(v));
+        const uint32_t got = e4m3_encode1(v);
+        bad += (want != got);
+    }
+    bad = __reduce_add_sync(0xffffffffu, (unsigned)bad);
+    if ((threadIdx.x & 31) == 0 && bad) atomicAdd(mismatches, bad);
+}
+
+RopeDev to_dev(const ds4b200_rope_params &p) {
+    return RopeDev{p.freq_base, p.theta_scale, p.freq_scale, p.ext_factor,
+                   p.attn_factor, p.corr_low, p.corr_high};
+}
+
+unsigned warp_row_grid(int64_t n_rows) { return (unsigned)((n_rows + kRowsPerCta - 1) / kRowsPerCta); }
+
+}  // namespace
+
+void rope_rows(const float *x_in, float *x_out, int64_t n_tokens, int n_heads, int head_dim,
+               int n_rot, const int32_t *pos, int single_pos, const ds4b200_rope_params &p,
+               int inverse, int unit_rms, float eps, cudaStream_t s) {
+    const int64_t n_rows = n_tokens * n_heads;
+    if (n_rows <= 0 || head_dim <= 0) return;
+    const RopeDev d = to_dev(p);
+    const bool vec = (head_dim & 3) == 0 && (n_rot & 3) == 0 && head_dim <= 1024 &&
+                     aligned16(x_in) && aligned16(x_out);
+    if (!vec) {
+        rope_rows_scalar_kernel<<<(unsigned)n_rows, 64, 0, s>>>(x_in, x_out, n_heads, head_dim, n_rot,
+                                                              pos, single_pos, d, inverse, unit_rms, eps);
+        return;
+    }
+    const int vpt = ((head_dim >> 2) + 31) / 32;
+    const unsigned grid = warp_row_grid(n_rows);
+#define DS4B200_ROPE(V) rope_rows_kernel<V><<<grid, kRowsPerCta * 32, 0, s>>>( \
+        x_in, x_out, n_rows, n_heads, head_dim, n_rot, pos, single_pos, d, inverse, unit_rms, eps)
+    if (vpt <= 1) DS4B200_ROPE(1);
+    else if (vpt <= 2) DS4B200_ROPE(2);
+    else if (vpt <= 4) DS4B200_ROPE(4);
+    else DS4B200_ROPE(8);
+#undef DS4B200_ROPE
+}
+
+void fp8_kv_round_trip_rows(const float *kv_in, float *kv_out, int64_t n_rows, int head_dim,
+                            int n_rot, cudaStream_t s) {
+    if (n_rows <= 0 || head_dim <= 0) return;
+    const bool vec = (head_dim & 63) == 0 && (n_rot & 63) == 0 && head_dim <= 1024 &&
+                     aligned16(kv_in) && aligned16(kv_out);
+    const unsigned grid = warp_row_grid(n_rows);
+    if (!vec) {
+        fp8_round_trip_scalar_kernel<<<grid, kRowsPerCta * 32, 0, s>>>(kv_in, kv_out, n_rows, head_dim, n_rot);
+        return;
+    }
+    const int vpt = ((head_dim >> 2) + 31) / 32;
+#define DS4B200_FP8RT(V) fp8_round_trip_kernel<V><<<grid, kRowsPerCta * 32, 0, s>>>(kv_in, kv_out, n_rows, head_dim, n_rot)
+    if (vpt <= 1) DS4B200_FP8RT(1);
+    else if (vpt <= 2) DS4B200_FP8RT(2);
+    else if (vpt <= 4) DS4B200_FP8RT(4);
+    else DS4B200_FP8RT(8);
+#undef DS4B200_FP8RT
+}
+
+void rope_fp8_store_rows(const float *kv_in, int64_t n_rows, int head_dim, int n_rot,
+                         const int32_t *pos, const ds4b200_rope_params *p, const float *norm_w,
+                         float eps, int scale_mode, const int32_t *slots, uint8_t *codes,
+                         float *scales, float *tail_out, float *rope_out, cudaStream_t s) {
+    if (n_rows <= 0) return;
+    StoreArgs a{};
+    a.kv_in = kv_in; a.n_rows = n_rows; a.head_dim = head_dim; a.n_rot = n_rot; a.pos = pos;
+    a.do_rope = p != nullptr;
+    if (p) a.rope = to_dev(*p);
+    a.norm_w = norm_w; a.eps = eps; a.scale_mode = scale_mode; a.slots = slots; a.codes = codes;
+    a.scales = scales; a.tail_out = tail_out; a.rope_out = rope_out;
+    const int vpt = ((head_dim >> 2) + 31) / 32;
+    const unsigned grid = warp_row_grid(n_rows);
+    if (vpt <= 1) rope_fp8_store_kernel<1><<<grid, kRowsPerCta * 32, 0, s>>>(a);
+    else if (vpt <= 2) rope_fp8_store_kernel<2><<<grid, kRowsPerCta * 32, 0, s>>>(a);
+    else if (vpt <= 4) rope_fp8_store_kernel<4><<<grid, kRowsPerCta * 32, 0, s>>>(a);
+    else rope_fp8_store_kernel<8><<<grid, kRowsPerCta * 32, 0, s>>>(a);
+}
+
+void e4m3_encode(const float *x, uint8_t *codes, int64_t n, cudaStream_t s) {
+    if (n > 0) e4m3_encode_kernel<<<148 * 8, 256, 0, s>>>(x, codes, n);
+}
+void e4m3_decode(const uint8_t *codes, float *x, int64_t n, cudaStream_t s) {
+    if (n > 0) e4m3_decode_kernel<<<148 * 8, 256, 0, s>>>(codes, x, n);
+}
+void e4m3_selfcheck(uint32_t first_bits, uint64_t count, unsigned long long *mismatches,
+                    cudaStream_t s) {
+    if (count > 0) e4m3_selfcheck_kernel<<<148 * 16, 256, 0, s>>>(first_bits, count, mismatches);
+}
+
+}  // namespace ds4b200

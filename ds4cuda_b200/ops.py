@@ -1,0 +1,170 @@
+"""Host-side mirror of the C ABI on torch CUDA tensors.
+
+Every function here only allocates outputs (torch) and forwards device
+pointers plus torch's current stream to libds4b200.so; the arithmetic lives in
+the CUDA kernels.  Tensors must be contiguous CUDA tensors; nothing runs on CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import (FP8_BLOCK64_POW2, FP8_ROW_AMAX, GLU_CLAMP_REF, GLU_CLAMP_SYM, GLU_PLAIN,
+                   TABLE_F16, TABLE_Q8_0, RopeParams, check)
+
+__all__ = [
+    "FP8_BLOCK64_POW2", "FP8_ROW_AMAX", "GLU_CLAMP_REF", "GLU_CLAMP_SYM", "GLU_PLAIN",
+    "TABLE_F16", "TABLE_Q8_0", "RopeParams", "rope_params_for_layer", "rope_params_explicit",
+    "add", "rms_norm_rows", "embed_gather_rows", "rope_rows", "fp8_kv_round_trip_rows",
+    "rope_fp8_store_rows", "swiglu_rows", "hc_pre_rows", "hc_post_rows", "hc_sinkhorn_mix_rows",
+    "e4m3_encode", "e4m3_decode", "e4m3_selfcheck", "device_status",
+]
+
+
+def _p(t):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise ValueError("ds4cuda_b200 ops take CUDA tensors only")
+    if not t.is_contiguous():
+        raise ValueError("ds4cuda_b200 ops take contiguous tensors")
+    return C.c_void_p(t.data_ptr())
+
+
+def _s():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def rope_params_for_layer(il: int, n_rot: int = 64) -> RopeParams:
+    """Per-layer routing of the reference launcher (cuda/rope.cu:214-250)."""
+    p = RopeParams()
+    _lib.load().ds4b200_rope_params_for_layer(il, n_rot, C.byref(p))
+    return p
+
+
+def rope_params_explicit(freq_base: float, yarn_factor: float, n_ctx_orig: int,
+                         n_rot: int = 64) -> RopeParams:
+    p = RopeParams()
+    _lib.load().ds4b200_rope_params_explicit(freq_base, yarn_factor, n_ctx_orig, n_rot, C.byref(p))
+    return p
+
+
+def device_status() -> int:
+    return _lib.load().ds4b200_device_status()
+
+
+def add(a, b):
+    y = torch.empty_like(a)
+    check(_lib.load().ds4b200_add_f32(_p(a), _p(b), _p(y), a.numel(), _s()))
+    return y
+
+
+def rms_norm_rows(x, w=None, residual=None, eps=1e-6, want_f32=True, want_bf16=False,
+                  want_residual=False):
+    """x [rows, n]; w None | [n] | [rows, n].  Returns (y_f32, y_bf16, residual_out)."""
+    rows, n = x.shape
+    weight_dim = 0 if w is None else w.numel()
+    y = torch.empty_like(x) if want_f32 else None
+    yb = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device) if want_bf16 else None
+    ro = torch.empty_like(x) if want_residual else None
+    check(_lib.load().ds4b200_rms_norm_rows_f32(_p(x), _p(residual), _p(w), weight_dim, _p(y),
+                                                _p(yb), _p(ro), rows, n, eps, _s()))
+    return y, yb, ro
+
+
+def embed_gather_rows(table, table_dtype, ids, n_embd, residual=None, norm_w=None, eps=1e-6,
+                      n_replicas=1, want_rows=True, want_f32=False, want_bf16=False):
+    """Returns (rows [T, n_replicas, n_embd] f32, normed_f32, normed_bf16)."""
+    T = ids.numel()
+    dev = ids.device
+    rows = torch.empty((T, n_replicas, n_embd), dtype=torch.float32, device=dev) if want_rows else None
+    nf = torch.empty((T, n_embd), dtype=torch.float32, device=dev) if want_f32 else None
+    nb = torch.empty((T, n_embd), dtype=torch.bfloat16, device=dev) if want_bf16 else None
+    check(_lib.load().ds4b200_embed_gather_rows(_p(table), table_dtype, _p(ids), T, n_embd,
+                                                _p(residual), _p(norm_w), eps, _p(rows), n_replicas,
+                                                _p(nf), _p(nb), _s()))
+    return rows, nf, nb
+
+
+def rope_rows(x, pos, params, n_rot=64, inverse=False, unit_rms=False, eps=1e-6, out=None):
+    """x [T, H, D], pos [T] int32."""
+    T, H, D = x.shape
+    out = torch.empty_like(x) if out is None else out
+    check(_lib.load().ds4b200_rope_rows_f32(_p(x), _p(out), T, H, D, n_rot, _p(pos),
+                                            C.byref(params), int(inverse), int(unit_rms), eps, _s()))
+    return out
+
+
+def fp8_kv_round_trip_rows(kv, n_rot=64, out=None):
+    rows, D = kv.shape
+    out = torch.empty_like(kv) if out is None else out
+    check(_lib.load().ds4b200_fp8_kv_round_trip_rows_f32(_p(kv), _p(out), rows, D, n_rot, _s()))
+    return out
+
+
+def rope_fp8_store_rows(kv, pos, params, n_rot, scale_mode, codes, scales, slots=None,
+                        norm_w=None, eps=1e-6, tail_out=None, rope_out=None):
+    """Writes into the caller's cache tensors `codes` (uint8) and `scales` (f32)."""
+    rows, D = kv.shape
+    check(_lib.load().ds4b200_rope_fp8_store_rows(
+        _p(kv), rows, D, n_rot, _p(pos), None if params is None else C.byref(params), _p(norm_w),
+        eps, scale_mode, _p(slots), _p(codes), _p(scales), _p(tail_out), _p(rope_out), _s()))
+
+
+def swiglu_rows(gate, up, weights=None, mode=GLU_PLAIN, clamp=0.0, combine=False, fast_exp=False):
+    """gate/up [T, k, n]; returns [T, n] when combine else [T, k, n]."""
+    T, k, n = gate.shape
+    out = torch.empty((T, n) if combine else (T, k, n), dtype=torch.float32, device=gate.device)
+    check(_lib.load().ds4b200_swiglu_rows_f32(_p(gate), _p(up), _p(weights), _p(out), T, k, n, mode,
+                                              clamp, int(combine), int(fast_exp), _s()))
+    return out
+
+
+def hc_pre_rows(resid, fn_f16, scale3, base24, iters=20, eps=1e-6):
+    """resid [T, 4, n]; fn_f16 [24, 4n] float16.  Returns (post [T,4], comb [T,16], out [T,n])."""
+    T, _, n = resid.shape
+    dev = resid.device
+    post = torch.empty((T, 4), dtype=torch.float32, device=dev)
+    comb = torch.empty((T, 16), dtype=torch.float32, device=dev)
+    out = torch.empty((T, n), dtype=torch.float32, device=dev)
+    check(_lib.load().ds4b200_hc_pre_rows_f32(_p(resid), _p(fn_f16), _p(scale3), _p(base24), _p(post),
+                                              _p(comb), _p(out), T, n, iters, eps, _s()))
+    return post, comb, out
+
+
+def hc_post_rows(block_out, resid, post, comb, block_out2=None):
+    T, _, n = resid.shape
+    out = torch.empty_like(resid)
+    check(_lib.load().ds4b200_hc_post_rows_f32(_p(block_out), _p(block_out2), _p(resid), _p(post),
+                                               _p(comb), _p(out), T, n, _s()))
+    return out
+
+
+def hc_sinkhorn_mix_rows(logits, resid, iters=20, eps=1e-6, want_comb=False):
+    T, _, n = resid.shape
+    out = torch.empty_like(resid)
+    comb = torch.empty((T, 16), dtype=torch.float32, device=resid.device) if want_comb else None
+    check(_lib.load().ds4b200_hc_sinkhorn_mix_rows_f32(_p(logits), _p(resid), _p(out), _p(comb), T, n,
+                                                       iters, eps, _s()))
+    return (out, comb) if want_comb else out
+
+
+def e4m3_encode(x):
+    codes = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    check(_lib.load().ds4b200_e4m3_encode_f32(_p(x), _p(codes), x.numel(), _s()))
+    return codes
+
+
+def e4m3_decode(codes):
+    x = torch.empty(codes.shape, dtype=torch.float32, device=codes.device)
+    check(_lib.load().ds4b200_e4m3_decode_f32(_p(codes), _p(x), codes.numel(), _s()))
+    return x
+
+
+def e4m3_selfcheck(first_bits: int, count: int) -> int:
+    """Number of f32 bit patterns in the range whose hardware code differs from the table rule."""
+    bad = torch.zeros(1, dtype=torch.int64, device="cuda")
+    check(_lib.load().ds4b200_e4m3_selfcheck(first_bits, count, _p(bad), _s()))
+    return int(bad.item())

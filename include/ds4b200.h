@@ -1,0 +1,215 @@
+/* ds4b200.h — C ABI of libds4b200.so: the fused elementwise / row-reduction
+ * path of the ds4cuda forward pass, written for NVIDIA B200 (sm_100a).
+ *
+ * Two families of entry points:
+ *
+ *  1. `ds4b200_launch_*`  — `extern "C"` names for the reference's C++
+ *     launchers (`namespace ds4cuda`, declared in ds4b200_launchers.cuh with
+ *     the reference's own signatures).  One token per call, `void`, no checks,
+ *     no allocation, no synchronisation: exactly the reference's convention.
+ *
+ *  2. `ds4b200_*_rows*`   — batched siblings for T-token prefill, explicit
+ *     parameters instead of per-layer routing.  They check their arguments and
+ *     return 0, or a negative errno (-EINVAL bad argument, -EIO launch error);
+ *     ds4b200_last_error() gives the message.  They never allocate or
+ *     synchronise either.
+ *
+ * Every pointer is device memory owned by the caller unless its name starts
+ * with `host_`.  `stream` is a `cudaStream_t` passed as `void *` (NULL = the
+ * default stream).  The library has no CPU fallback: without a CUDA device the
+ * launches fail and the checked entry points return -EIO.
+ */
+#ifndef DS4B200_H
+#define DS4B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- enums and parameter blocks ------------------------------------------ */
+
+enum { DS4B200_TABLE_F16 = 0, DS4B200_TABLE_Q8_0 = 1 };
+
+/* FP8 scale layout.  BLOCK64_POW2 is the reference's rule (cuda/fp8_kv.cu:161-180):
+ * one power-of-two scale per 64 elements of the non-rotated prefix, the rotated
+ * tail kept in f32.  ROW_AMAX is one scale = max(amax,1e-4)/448 per row over all
+ * head_dim elements. */
+enum { DS4B200_FP8_BLOCK64_POW2 = 0, DS4B200_FP8_ROW_AMAX = 1 };
+
+/* SwiGLU flavour.  PLAIN: (g*sigmoid(g))*u (cuda/glu.cu:56-75).  CLAMP_REF:
+ * gate clamped from above, up clamped both sides (cuda/moe_iq2_pair.cu:352-373).
+ * CLAMP_SYM: both clamped both sides. */
+enum { DS4B200_GLU_PLAIN = 0, DS4B200_GLU_CLAMP_REF = 1, DS4B200_GLU_CLAMP_SYM = 2 };
+
+/* RoPE parameters after the per-layer routing of cuda/rope.cu:214-250.
+ * theta_scale <= 0 asks the kernel to evaluate powf(freq_base, -2/n_rot) on the
+ * device, as the reference kernel does (cuda/rope.cu:173). */
+typedef struct ds4b200_rope_params {
+    float freq_base;
+    float theta_scale;
+    float freq_scale;
+    float ext_factor;
+    float attn_factor;
+    float corr_low;
+    float corr_high;
+} ds4b200_rope_params;
+
+/* ---- library state ----------------------------------------------------------- */
+
+const char *ds4b200_version(void);
+/* Message of the last failing checked call on this thread ("" if none). */
+const char *ds4b200_last_error(void);
+/* Bit mask of faults kernels recorded on the current device since the last
+ * call (bit 0: a bulk copy into shared memory did not complete in time);
+ * reading clears it.  Synchronises the device.  Negative errno on failure. */
+int ds4b200_device_status(void);
+
+/* Host-side routing helpers (no device work).
+ * for_layer: the reference's rule, cuda/rope.cu:214-250 (theta_scale left 0). */
+void ds4b200_rope_params_for_layer(int il, int n_rot, ds4b200_rope_params *out);
+void ds4b200_rope_params_explicit(float freq_base, float yarn_factor, int n_ctx_orig,
+                                  int n_rot, ds4b200_rope_params *out);
+
+/* ---- 1. drop-in launchers, C names ---------------------------------------------- */
+
+/* cuda/norm.cuh:24 */
+void ds4b200_launch_rms_norm_f32(const float *x, const float *w, float *y, int n,
+                                 float eps, void *stream);
+/* cuda/norm.cuh:42 */
+void ds4b200_launch_rms_norm_batch_f32(const float *x, const float *w, int weight_dim,
+                                       float *y, int n_rows, int n_per_row, float eps,
+                                       void *stream);
+/* cuda/elementwise.cuh:27 */
+void ds4b200_launch_add_f32(const float *a, const float *b, float *y, int n, void *stream);
+/* cuda/rope.cuh:51 */
+void ds4b200_launch_tail_rope_yarn_f32(const float *x_in, float *x_out, int n_heads,
+                                       int head_dim, int n_rot, int pos, int il, void *stream);
+/* cuda/attn_out.cuh:52 */
+void ds4b200_launch_tail_rope_yarn_inverse_f32(const float *x_in, float *x_out, int n_heads,
+                                               int head_dim, int n_rot, int pos, int il,
+                                               void *stream);
+/* cuda/fp8_kv.cuh:62 */
+void ds4b200_launch_fp8_kv_quantize_round_trip_f32(const float *kv_in, float *kv_out,
+                                                   int n_rows, int head_dim, int n_rot,
+                                                   void *stream);
+/* cuda/glu.cuh:30 */
+void ds4b200_launch_silu_mul_f32(const float *g, const float *u, float *y, int n, void *stream);
+/* cuda/embedding.cuh:46 */
+void ds4b200_launch_embed_token_f16_to_f32(const uint16_t *token_embd_weight, int token_id,
+                                           int n_embd, float *out, void *stream);
+/* cuda/hc_sinkhorn.cuh:55 */
+void ds4b200_launch_hc_attn_pre_f32(const float *residual_hc, const uint16_t *hc_fn,
+                                    const float *hc_scale, const float *hc_base,
+                                    float *post_weights, float *comb, float *out,
+                                    int n_embd, int n_hc, int sinkhorn_iters, float eps,
+                                    void *stream);
+/* cuda/hc_sinkhorn.cuh:80 and :99 (the ffn variant forwards to the same chain) */
+void ds4b200_launch_hc_attn_pre_v2_f32(const float *residual_hc, const uint16_t *hc_fn,
+                                       const float *hc_scale, const float *hc_base,
+                                       float *post_weights, float *comb, float *out,
+                                       int n_embd, int n_hc, int sinkhorn_iters, float eps,
+                                       float *rms_scratch, float *mix_scratch, void *stream);
+/* cuda/hc_sinkhorn.cuh:138 */
+void ds4b200_launch_hc_post_f32(const float *block_out, const float *residual_hc,
+                                const float *post, const float *comb, float *out_hc,
+                                int n_hc, int n_embd, void *stream);
+
+/* ---- 2. batched, checked siblings ---------------------------------------------- */
+
+/* y = a + b over n elements (cuda/elementwise.cu:36-43, any n). */
+int ds4b200_add_f32(const float *a, const float *b, float *y, int64_t n, void *stream);
+
+/* RMSNorm of n_rows rows of n elements (cuda/norm.cu:126-197) with the chain
+ * around it fused: residual_in (nullable) is added first, the sum goes to
+ * residual_out (nullable), the normalised row to y_f32 and/or y_bf16 (either
+ * nullable, RNE).  weight_dim: 0 unit gain, n shared gain, n*n_rows per-row. */
+int ds4b200_rms_norm_rows_f32(const float *x, const float *residual_in, const float *w,
+                              int64_t weight_dim, float *y_f32, uint16_t *y_bf16,
+                              float *residual_out, int64_t n_rows, int n, float eps,
+                              void *stream);
+
+/* Embedding gather for n_tokens ids (cuda/embedding.cu:27-39 for F16 rows,
+ * cuda/dense_q8.cu:60-67 for Q8_0 rows of 34-byte blocks), fused with what
+ * follows it: + residual_in (nullable), n_replicas copies of the f32 row to
+ * out_rows[t][rep][n_embd] (nullable; cuda/forward_token.cu:350-354 makes 4),
+ * and, when norm_w is given, RMSNorm to normed_f32 / normed_bf16 (nullable).
+ * ids outside [0, vocab) are the caller's error, as in the reference. */
+int ds4b200_embed_gather_rows(const void *table, int table_dtype, const int32_t *ids,
+                              int64_t n_tokens, int n_embd, const float *residual_in,
+                              const float *norm_w, float eps, float *out_rows, int n_replicas,
+                              float *normed_f32, uint16_t *normed_bf16, void *stream);
+
+/* Tail RoPE over [n_tokens][n_heads][head_dim] with one position per token
+ * (cuda/rope.cu:136-201; inverse: cuda/attn_out.cu:54-107).  unit_rms != 0
+ * first applies the unit-gain per-head RMSNorm of cuda/forward_layer.cu:890.
+ * In place (x_out == x_in) is allowed. */
+int ds4b200_rope_rows_f32(const float *x_in, float *x_out, int64_t n_tokens, int n_heads,
+                          int head_dim, int n_rot, const int32_t *pos,
+                          const ds4b200_rope_params *params, int inverse, int unit_rms,
+                          float eps, void *stream);
+
+/* FP8 E4M3FN quantise/dequantise round trip, cuda/fp8_kv.cu:144-195. */
+int ds4b200_fp8_kv_round_trip_rows_f32(const float *kv_in, float *kv_out, int64_t n_rows,
+                                       int head_dim, int n_rot, void *stream);
+
+/* Fused KV row chain: optional weighted RMSNorm (norm_w nullable) -> tail RoPE
+ * at pos[r] (params nullable = rows are already rotated) -> E4M3FN bytes and
+ * scales into a cache.  Row r lands in slot slots[r] (slots nullable = r);
+ * codes[slot][head_dim], scales[slot][n_scales] with n_scales =
+ * (head_dim-n_rot)/64 (BLOCK64_POW2) or 1 (ROW_AMAX).  BLOCK64_POW2 writes the
+ * rotated tail as f32 to tail_out[slot][n_rot] (nullable) and zero codes for
+ * it.  rope_out[r][head_dim] (nullable) receives the f32 row before encoding. */
+int ds4b200_rope_fp8_store_rows(const float *kv_in, int64_t n_rows, int head_dim, int n_rot,
+                                const int32_t *pos, const ds4b200_rope_params *params,
+                                const float *norm_w, float eps, int scale_mode,
+                                const int32_t *slots, uint8_t *codes, float *scales,
+                                float *tail_out, float *rope_out, void *stream);
+
+/* SwiGLU over gate/up[n_tokens][k][n].  weights[n_tokens][k] nullable.
+ * combine != 0: out[n_tokens][n] = sum of the k slots in slot order; else
+ * out[n_tokens][k][n].  fast_exp != 0 uses the hardware exp approximation the
+ * reference's expert epilogue uses (cuda/moe_iq2_pair.cu:364,367). */
+int ds4b200_swiglu_rows_f32(const float *gate, const float *up, const float *weights,
+                            float *out, int64_t n_tokens, int k, int n, int mode,
+                            float clamp, int combine, int fast_exp, void *stream);
+
+/* Hyper-connection pre step for n_tokens tokens (cuda/hc_sinkhorn.cu:85-305):
+ * RMS over the 4*n_embd residual, 24-row f16 matvec, sigmoid / Sinkhorn split,
+ * weighted sum.  post[t][4], comb[t][16], out[t][n_embd]. */
+int ds4b200_hc_pre_rows_f32(const float *residual_hc, const uint16_t *hc_fn,
+                            const float *hc_scale, const float *hc_base, float *post,
+                            float *comb, float *out, int64_t n_tokens, int n_embd,
+                            int sinkhorn_iters, float eps, void *stream);
+
+/* Hyper-connection post step (cuda/hc_sinkhorn.cu:619-672) for n_tokens tokens.
+ * block_out nullable (term dropped); block_out2 nullable (when given the block
+ * term is block_out+block_out2, the add of cuda/forward_layer.cu:1447 fused). */
+int ds4b200_hc_post_rows_f32(const float *block_out, const float *block_out2,
+                             const float *residual_hc, const float *post, const float *comb,
+                             float *out_hc, int64_t n_tokens, int n_embd, void *stream);
+
+/* Sinkhorn mixing: logits[t][16] (index src+4*dst) -> row softmax + eps ->
+ * `sinkhorn_iters` normalisation sweeps (cuda/hc_sinkhorn.cu:224-289) -> mix
+ * the 4 residual streams, out_hc[t][dst] = sum_src comb[dst+4*src]*resid[t][src].
+ * comb_out[t][16] nullable. */
+int ds4b200_hc_sinkhorn_mix_rows_f32(const float *logits, const float *residual_hc,
+                                     float *out_hc, float *comb_out, int64_t n_tokens,
+                                     int n_embd, int sinkhorn_iters, float eps, void *stream);
+
+/* E4M3FN code of each of n f32 values (sign bit | nearest index, saturating),
+ * and its inverse; used to check the encoder exhaustively. */
+int ds4b200_e4m3_encode_f32(const float *x, uint8_t *codes, int64_t n, void *stream);
+int ds4b200_e4m3_decode_f32(const uint8_t *codes, float *x, int64_t n, void *stream);
+/* Counts the f32 bit patterns in [first_bits, first_bits+count) whose hardware
+ * E4M3FN code differs from the table search of cuda/fp8_kv.cu:102-131
+ * (NaN patterns skipped).  *mismatches is a device uint64 the caller zeroes. */
+int ds4b200_e4m3_selfcheck(uint32_t first_bits, uint64_t count,
+                           unsigned long long *mismatches, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DS4B200_H */

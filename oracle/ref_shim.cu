@@ -1,0 +1,73 @@
+// ref_shim.cu — `extern "C"` names for the reference's own C++ launchers, so a
+// ctypes harness can drive the reference kernels rebuilt for sm_100a.
+// TEST INFRASTRUCTURE ONLY: compiled together with the reference's sources
+// (where they lie in the reference tree) into oracle/_ref/libds4ref.so by
+// oracle/Makefile.  Nothing here is part of the product library.
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include "attn_out.cuh"
+#include "dense_q8.cuh"
+#include "elementwise.cuh"
+#include "embedding.cuh"
+#include "fp8_kv.cuh"
+#include "glu.cuh"
+#include "hc_sinkhorn.cuh"
+#include "norm.cuh"
+#include "rope.cuh"
+
+#define S(s) static_cast<cudaStream_t>(s)
+using namespace ds4cuda;
+
+extern "C" {
+
+void ds4ref_rms_norm_f32(const float *x, const float *w, float *y, int n, float eps, void *s) {
+    launch_rms_norm_f32(x, w, y, n, eps, S(s));
+}
+void ds4ref_rms_norm_batch_f32(const float *x, const float *w, int weight_dim, float *y, int n_rows,
+                               int n_per_row, float eps, void *s) {
+    launch_rms_norm_batch_f32(x, w, weight_dim, y, n_rows, n_per_row, eps, S(s));
+}
+void ds4ref_add_f32(const float *a, const float *b, float *y, int n, void *s) {
+    launch_add_f32(a, b, y, n, S(s));
+}
+void ds4ref_tail_rope_yarn_f32(const float *x_in, float *x_out, int n_heads, int head_dim, int n_rot,
+                               int pos, int il, void *s) {
+    launch_tail_rope_yarn_f32(x_in, x_out, n_heads, head_dim, n_rot, pos, il, S(s));
+}
+void ds4ref_tail_rope_yarn_inverse_f32(const float *x_in, float *x_out, int n_heads, int head_dim,
+                                       int n_rot, int pos, int il, void *s) {
+    launch_tail_rope_yarn_inverse_f32(x_in, x_out, n_heads, head_dim, n_rot, pos, il, S(s));
+}
+void ds4ref_fp8_kv_quantize_round_trip_f32(const float *kv_in, float *kv_out, int n_rows,
+                                           int head_dim, int n_rot, void *s) {
+    launch_fp8_kv_quantize_round_trip_f32(kv_in, kv_out, n_rows, head_dim, n_rot, S(s));
+}
+void ds4ref_silu_mul_f32(const float *g, const float *u, float *y, int n, void *s) {
+    launch_silu_mul_f32(g, u, y, n, S(s));
+}
+void ds4ref_embed_token_f16_to_f32(const uint16_t *table, int token_id, int n_embd, float *out,
+                                   void *s) {
+    launch_embed_token_f16_to_f32(table, token_id, n_embd, out, S(s));
+}
+void ds4ref_dequant_q8_0_to_f32(const void *blocks, float *dst, int n_blocks, void *s) {
+    launch_dequant_q8_0_to_f32(static_cast<const block_q8_0 *>(blocks), dst, n_blocks, S(s));
+}
+void ds4ref_hc_attn_pre_f32(const float *residual_hc, const uint16_t *fn, const float *scale,
+                            const float *base, float *post, float *comb, float *out, int n_embd,
+                            int n_hc, int iters, float eps, void *s) {
+    launch_hc_attn_pre_f32(residual_hc, fn, scale, base, post, comb, out, n_embd, n_hc, iters, eps, S(s));
+}
+void ds4ref_hc_attn_pre_v2_f32(const float *residual_hc, const uint16_t *fn, const float *scale,
+                               const float *base, float *post, float *comb, float *out, int n_embd,
+                               int n_hc, int iters, float eps, float *rms_scratch, float *mix_scratch,
+                               void *s) {
+    launch_hc_attn_pre_v2_f32(residual_hc, fn, scale, base, post, comb, out, n_embd, n_hc, iters, eps,
+                              rms_scratch, mix_scratch, S(s));
+}
+void ds4ref_hc_post_f32(const float *block_out, const float *residual_hc, const float *post,
+                        const float *comb, float *out_hc, int n_hc, int n_embd, void *s) {
+    launch_hc_post_f32(block_out, residual_hc, post, comb, out_hc, n_hc, n_embd, S(s));
+}
+
+}  // extern "C"

@@ -1,0 +1,126 @@
+"""CPU tests of the drop-in boundary: the shared library loads, exports every
+symbol the headers declare (C names and the reference's mangled C++ names), and
+the checked entry points reject bad arguments before touching the GPU."""
+import ctypes as C
+import re
+import subprocess
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from ds4cuda_b200 import _lib, build
+    build.build()
+    return _lib.load()
+
+
+def _declared(header: str):
+    text = (ROOT / "include" / header).read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ds4b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_c_symbol_is_exported_and_bound(lib):
+    from ds4cuda_b200 import _lib
+    names = _declared("ds4b200.h") + _declared("ds4b200_path.h")
+    assert len(names) > 40
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/ but not exported"
+        assert n in _lib.SIGNATURES, f"{n} has no ctypes signature"
+    assert set(_lib.SIGNATURES) <= set(names)
+
+
+def test_reference_cxx_launchers_are_exported_with_reference_signatures():
+    """The mangled names the reference's forward_layer.o / forward_token.o import."""
+    from ds4cuda_b200 import _lib
+    out = subprocess.run(["nm", "-D", "--defined-only", "-C", str(_lib.LIB_PATH)], capture_output=True,
+                         text=True, check=True).stdout
+    want = [
+        "ds4cuda::launch_rms_norm_f32(float const*, float const*, float*, int, float, CUstream_st*)",
+        "ds4cuda::launch_rms_norm_batch_f32(float const*, float const*, int, float*, int, int, float, CUstream_st*)",
+        "ds4cuda::launch_add_f32(float const*, float const*, float*, int, CUstream_st*)",
+        "ds4cuda::launch_tail_rope_yarn_f32(float const*, float*, int, int, int, int, int, CUstream_st*)",
+        "ds4cuda::launch_tail_rope_yarn_inverse_f32(float const*, float*, int, int, int, int, int, CUstream_st*)",
+        "ds4cuda::launch_fp8_kv_quantize_round_trip_f32(float const*, float*, int, int, int, CUstream_st*)",
+        "ds4cuda::launch_silu_mul_f32(float const*, float const*, float*, int, CUstream_st*)",
+        "ds4cuda::launch_embed_token_f16_to_f32(unsigned short const*, int, int, float*, CUstream_st*)",
+        "ds4cuda::launch_hc_attn_pre_f32(float const*, unsigned short const*, float const*, float const*, float*, float*, float*, int, int, int, float, CUstream_st*)",
+        "ds4cuda::launch_hc_attn_pre_v2_f32(float const*, unsigned short const*, float const*, float const*, float*, float*, float*, int, int, int, float, float*, float*, CUstream_st*)",
+        "ds4cuda::launch_hc_ffn_pre_v2_f32(float const*, unsigned short const*, float const*, float const*, float*, float*, float*, int, int, int, float, float*, float*, CUstream_st*)",
+        "ds4cuda::launch_hc_post_f32(float const*, float const*, float const*, float const*, float*, int, int, CUstream_st*)",
+    ]
+    for sig in want:
+        assert sig in out, f"missing drop-in symbol: {sig}"
+
+
+def test_rope_routing_matches_oracle(lib, oracle):
+    from ds4cuda_b200 import _lib
+    for il in (0, 1, 2, 3, 42):
+        a = _lib.RopeParams()
+        lib.ds4b200_rope_params_for_layer(il, 64, C.byref(a))
+        b = oracle.rope_params_for_layer(il)
+        assert a.theta_scale == 0.0                      # evaluated on the device, as the reference does
+        for f in ("freq_base", "freq_scale", "ext_factor", "attn_factor", "corr_low", "corr_high"):
+            assert getattr(a, f) == getattr(b, f), (il, f)
+    a = _lib.RopeParams()
+    lib.ds4b200_rope_params_explicit(10000.0, 16.0, 4096, 64, C.byref(a))
+    assert bytes(a) == bytes(oracle.rope_params_explicit(10000.0, 16.0, 4096))
+
+
+def test_checked_entry_points_reject_bad_arguments_without_a_gpu(lib):
+    EINVAL = -22
+    p = C.c_void_p(0x1000)       # never dereferenced: every call below fails validation first
+    assert lib.ds4b200_add_f32(None, p, p, 8, None) == EINVAL
+    assert b"null" in lib.ds4b200_last_error()
+    assert lib.ds4b200_add_f32(p, p, p, -1, None) == EINVAL
+    assert lib.ds4b200_add_f32(None, None, None, 0, None) == 0          # empty input is a no-op
+    assert lib.ds4b200_rms_norm_rows_f32(p, None, None, 7, p, None, None, 4, 16, 1e-6, None) == EINVAL
+    assert lib.ds4b200_rms_norm_rows_f32(p, None, None, 0, None, None, None, 4, 16, 1e-6, None) == EINVAL
+    assert lib.ds4b200_rms_norm_rows_f32(p, None, None, 0, p, None, p, 4, 16, 1e-6, None) == EINVAL
+    assert lib.ds4b200_rms_norm_rows_f32(None, None, None, 0, None, None, None, 0, 16, 1e-6, None) == 0
+    assert lib.ds4b200_embed_gather_rows(p, 7, p, 4, 64, None, None, 1e-6, p, 1, None, None, None) == EINVAL
+    assert lib.ds4b200_embed_gather_rows(p, 1, p, 4, 48, None, None, 1e-6, p, 1, None, None, None) == EINVAL
+    assert lib.ds4b200_embed_gather_rows(p, 0, p, 4, 64, None, None, 1e-6, None, 1, None, None, None) == EINVAL
+    from ds4cuda_b200._lib import RopeParams
+    rp = RopeParams(10000.0, 0.75, 1.0, 0.0, 1.0, 0.0, 0.0)
+    assert lib.ds4b200_rope_rows_f32(p, p, 2, 2, 64, 63, p, C.byref(rp), 0, 0, 1e-6, None) == EINVAL
+    assert lib.ds4b200_rope_rows_f32(p, p, 2, 2, 64, 128, p, C.byref(rp), 0, 0, 1e-6, None) == EINVAL
+    assert lib.ds4b200_rope_rows_f32(p, p, 2, 2, 64, 32, p, None, 0, 0, 1e-6, None) == EINVAL
+    assert lib.ds4b200_fp8_kv_round_trip_rows_f32(p, p, 2, 500, 64, None) == EINVAL
+    assert lib.ds4b200_rope_fp8_store_rows(p, 2, 512, 64, p, C.byref(rp), None, 1e-6, 9, None, p, p,
+                                           None, None, None) == EINVAL
+    assert lib.ds4b200_rope_fp8_store_rows(p, 2, 2048, 64, p, C.byref(rp), None, 1e-6, 1, None, p, p,
+                                           None, None, None) == EINVAL
+    assert lib.ds4b200_rope_fp8_store_rows(C.c_void_p(0x1004), 2, 512, 64, p, C.byref(rp), None, 1e-6, 1,
+                                           None, p, p, None, None, None) == EINVAL
+    assert b"alignment" in lib.ds4b200_last_error()
+    assert lib.ds4b200_swiglu_rows_f32(p, p, None, p, 2, 6, 64, 5, 10.0, 1, 0, None) == EINVAL
+    assert lib.ds4b200_hc_pre_rows_f32(p, p, p, p, p, p, p, 2, 4098, 20, 1e-6, None) == EINVAL
+    assert lib.ds4b200_hc_pre_rows_f32(p, p, p, p, p, p, p, 2, 4096, 0, 1e-6, None) == EINVAL
+    assert lib.ds4b200_hc_post_rows_f32(p, None, p, None, p, p, 2, 4096, None) == EINVAL
+    assert lib.ds4b200_hc_post_rows_f32(None, p, p, None, p, p, 2, 4096, None) == EINVAL
+    assert lib.ds4b200_hc_sinkhorn_mix_rows_f32(None, p, p, None, 2, 4096, 20, 1e-6, None) == EINVAL
+    assert lib.ds4b200_path_create(None) is None
+    from ds4cuda_b200._lib import PathConfig
+    bad = PathConfig(n_tokens=0)
+    assert lib.ds4b200_path_create(C.byref(bad)) is None
+    assert b"geometry" in lib.ds4b200_last_error()
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    from ds4cuda_b200 import _lib
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "nope.so")
+    with pytest.raises(RuntimeError, match="no fallback"):
+        _lib.load()
+
+
+def test_ops_refuse_cpu_tensors():
+    import torch
+    from ds4cuda_b200 import ops
+    with pytest.raises(ValueError, match="CUDA tensors only"):
+        ops.add(torch.zeros(4), torch.zeros(4))

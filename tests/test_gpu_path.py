@@ -1,0 +1,70 @@
+"""GPU tests of the prefill path object: host buffers in, host buffers out,
+checked against the oracle's composition of the same four ops."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import inputs
+from test_gpu_parity import assert_bits, assert_close, bf16_of
+
+pytestmark = pytest.mark.gpu
+
+
+def make_inputs(path, seed=7):
+    g = inputs.rng(seed)
+    c = path.cfg
+    T = c.n_tokens
+    return dict(
+        ids=g.integers(0, c.vocab, T).astype(np.int32), pos=g.permutation(c.n_slots)[:T].astype(np.int32),
+        residual=inputs.normal(g, (T, c.n_embd)), norm_w=inputs.uniform(g, (c.n_embd,), 0.5, 1.5),
+        kv=inputs.normal(g, (T, c.kv_dim), 1.5), gate=inputs.normal(g, (T, c.top_k, c.ff_dim), 2.0),
+        up=inputs.normal(g, (T, c.top_k, c.ff_dim), 2.0), router_w=inputs.router_weights(g, T, c.top_k),
+        hc_logits=inputs.normal(g, (T, 16)), hc_resid=inputs.normal(g, (T, 4, c.n_embd)))
+
+
+@pytest.mark.parametrize("scale_mode,use_graph", [("row_amax", 0), ("block64", 1)])
+def test_path_run_host_matches_oracle(ops, oracle, scale_mode, use_graph):
+    from ds4cuda_b200.path import PrefillPath
+    sm = ops.FP8_ROW_AMAX if scale_mode == "row_amax" else ops.FP8_BLOCK64_POW2
+    osm = oracle.FP8_ROW_AMAX if scale_mode == "row_amax" else oracle.FP8_BLOCK64_POW2
+    rope = oracle.rope_params_explicit(10000.0, 16.0, 4096)
+    path = PrefillPath(n_tokens=96, n_embd=1024, vocab=777, kv_dim=512, n_rot=64, n_slots=4096, ff_dim=256,
+                       top_k=6, max_layers=3, fp8_scale_mode=sm, use_graph=use_graph,
+                       rope=ops.RopeParams(rope.freq_base, rope.theta_scale, rope.freq_scale, rope.ext_factor,
+                                           rope.attn_factor, rope.corr_low, rope.corr_high))
+    table = inputs.q8_0_table(inputs.rng(8), 777, 1024)
+    path.upload_table(table)
+    x = make_inputs(path)
+    n_layers = 3
+    out = path.run_host(x, n_layers)
+    assert out["ms"] > 0
+    rows, nf, _ = oracle.embed_gather_rows(table, oracle.TABLE_Q8_0, x["ids"], 1024, residual=x["residual"],
+                                           norm_w=x["norm_w"])
+    assert_bits(out["residual_out"], rows[:, 0, :], "residual'")
+    got_bf16 = torch.from_numpy(out["normed_bf16"].view(np.int16)).view(torch.bfloat16).float().numpy()
+    assert np.abs(got_bf16 - nf).max() <= 2.0 ** -8 * np.abs(nf).max()
+    c_, s_, t_, rope_rows = oracle.rope_fp8_store_rows(x["kv"], x["pos"], rope, 64, osm)
+    same = (out["kv_scales"] == s_).all(axis=1)
+    assert same.mean() > 0.98
+    diff = out["kv_codes"][same] != c_[same]
+    assert diff.mean() < 2e-3
+    if scale_mode == "block64":
+        assert_close(out["kv_tail"], t_, what="kv tail")
+    want_ffn = oracle.swiglu_rows(x["gate"], x["up"], x["router_w"], oracle.GLU_CLAMP_REF, 10.0, combine=True)
+    assert_close(out["ffn_out"], want_ffn, what="ffn_out")
+    hc = x["hc_resid"]
+    for _ in range(n_layers):
+        hc, _ = oracle.hc_sinkhorn_mix_rows(x["hc_logits"], hc)
+    assert_close(out["hc_out"], hc, rel=3e-5, what="hc after 3 layers")   # three chained mixes
+    # a second call on the same inputs reproduces the first bit for bit
+    again = path.run_host(x, n_layers)
+    for k in ("residual_out", "normed_bf16", "kv_codes", "kv_scales", "ffn_out", "hc_out"):
+        assert_bits(again[k], out[k], k)
+    ms = path.time_device(n_layers, warmup=1, steps=2)
+    per_op, launches = path.profile_ops(n_layers)
+    assert ms > 0 and all(v > 0 for v in per_op) and launches == [n_layers] * 4
+    assert path.launches_per_run(n_layers) == 4 * n_layers
+    assert path.op_bytes(2) == 96 * (2 * 6 * 256 * 4 + 6 * 4 + 256 * 4)
+    path.close()
