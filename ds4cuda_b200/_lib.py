@@ -72,6 +72,7 @@ SIGNATURES = {
     "ds4b200_swiglu_rows_f32": (_I, [_P, _P, _P, _P, _L, _I, _I, _I, _F, _I, _I, _P]),
     "ds4b200_hc_pre_rows_f32": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _F, _P]),
     "ds4b200_hc_post_rows_f32": (_I, [_P, _P, _P, _P, _P, _P, _L, _I, _P]),
+    "ds4b200_hc_sinkhorn_rows_f32": (_I, [_P, _P, _L, _I, _F, _P]),
     "ds4b200_hc_sinkhorn_mix_rows_f32": (_I, [_P, _P, _P, _P, _L, _I, _I, _F, _P]),
     "ds4b200_e4m3_encode_f32": (_I, [_P, _P, _L, _P]),
     "ds4b200_e4m3_decode_f32": (_I, [_P, _P, _L, _P]),
@@ -86,7 +87,7 @@ SIGNATURES = {
     "ds4b200_path_run_device": (_I, [_P, _I]),
     "ds4b200_path_run_host": (_I, [_P, _P, _I, C.POINTER(C.c_float)]),
     "ds4b200_path_time_device": (_I, [_P, _I, _I, _I, C.POINTER(C.c_float)]),
-    "ds4b200_path_profile_ops": (_I, [_P, _I, C.POINTER(C.c_float), C.POINTER(C.c_int)]),
+    "ds4b200_path_profile_ops": (_I, [_P, _I, C.POINTER(C.c_float)]),
     "ds4b200_path_launches_per_run": (_I, [_P, _I]),
     "ds4b200_path_op_bytes": (_L, [_P, _I]),
 }

@@ -203,9 +203,26 @@ int ds4b200_hc_sinkhorn_mix_rows_f32(const float *logits, const float *residual_
     REQUIRE(n_embd > 0 && n_embd % 4 == 0 && n_embd <= 8192,
             "hc_sinkhorn_mix_rows: n_embd must be a multiple of 4, at most 8192");
     REQUIRE(sinkhorn_iters >= 1, "hc_sinkhorn_mix_rows: sinkhorn_iters < 1");
-    ds4b200::hc_post_rows(nullptr, nullptr, residual_hc, nullptr, nullptr, logits, comb_out, out_hc,
-                          n_tokens, n_embd, sinkhorn_iters, eps, STREAM(stream));
+    if (comb_out) {
+        // two launches: all tokens' 4x4 matrices side by side, then pure streaming
+        ds4b200::hc_sinkhorn_rows(logits, comb_out, n_tokens, sinkhorn_iters, eps, STREAM(stream));
+        ds4b200::hc_post_rows(nullptr, nullptr, residual_hc, nullptr, comb_out, nullptr, nullptr,
+                              out_hc, n_tokens, n_embd, 0, 0.0f, STREAM(stream));
+    } else {
+        ds4b200::hc_post_rows(nullptr, nullptr, residual_hc, nullptr, nullptr, logits, nullptr, out_hc,
+                              n_tokens, n_embd, sinkhorn_iters, eps, STREAM(stream));
+    }
     return launched("hc_sinkhorn_mix_rows");
+}
+
+int ds4b200_hc_sinkhorn_rows_f32(const float *logits, float *comb, int64_t n_tokens,
+                                 int sinkhorn_iters, float eps, void *stream) {
+    REQUIRE(n_tokens >= 0, "hc_sinkhorn_rows: n_tokens < 0");
+    if (n_tokens == 0) return 0;
+    REQUIRE(logits && comb, "hc_sinkhorn_rows: null pointer");
+    REQUIRE(sinkhorn_iters >= 1, "hc_sinkhorn_rows: sinkhorn_iters < 1");
+    ds4b200::hc_sinkhorn_rows(logits, comb, n_tokens, sinkhorn_iters, eps, STREAM(stream));
+    return launched("hc_sinkhorn_rows");
 }
 
 int ds4b200_e4m3_encode_f32(const float *x, uint8_t *codes, int64_t n, void *stream) {

@@ -16,24 +16,26 @@ namespace {
 template <bool FAST>
 __device__ __forceinline__ float exp_sel(float x) { return FAST ? __expf(x) : expf(x); }
 
+// One exponential and one division per element: both branches of the
+// reference's sign test use e = exp(-|g|) and divide by (1 + e); only the
+// numerator differs (g or g*e, 1 or e), so selecting the numerator first gives
+// the same bits as evaluating the taken branch.
 template <int MODE, bool FAST>
 __device__ __forceinline__ float glu_one(float g, float u, float clamp) {
+    if (MODE != DS4B200_GLU_PLAIN && clamp > 1.0e-6f) {
+        g = fminf(g, clamp);
+        if (MODE == DS4B200_GLU_CLAMP_SYM) g = fmaxf(g, -clamp);
+        u = fminf(fmaxf(u, -clamp), clamp);
+    }
+    const float e = exp_sel<FAST>(-fabsf(g));
+    const float den = 1.0f + e;
     if (MODE == DS4B200_GLU_PLAIN) {
-        // g * sigmoid_stable(g) * u, cuda/glu.cu:56-75
-        float sg;
-        if (g >= 0.0f) { const float e = exp_sel<FAST>(-g); sg = 1.0f / (1.0f + e); }
-        else           { const float e = exp_sel<FAST>(g);  sg = e / (1.0f + e); }
+        // (g * sigmoid_stable(g)) * u, cuda/glu.cu:56-75
+        const float sg = (g >= 0.0f ? 1.0f : e) / den;
         return (g * sg) * u;
     }
-    if (clamp > 1.0e-6f) {
-        if (g > clamp) g = clamp;
-        if (MODE == DS4B200_GLU_CLAMP_SYM && g < -clamp) g = -clamp;
-        if (u > clamp) u = clamp;
-        if (u < -clamp) u = -clamp;
-    }
-    float s;
-    if (g >= 0.0f) { const float e = exp_sel<FAST>(-g); s = g / (1.0f + e); }
-    else           { const float e = exp_sel<FAST>(g);  s = g * e / (1.0f + e); }
+    // s = g/(1+e) or (g*e)/(1+e), then s*u, cuda/moe_iq2_pair.cu:362-372
+    const float s = (g >= 0.0f ? g : g * e) / den;
     return s * u;
 }
 

@@ -48,6 +48,10 @@ void hc_pre_rows(const float *residual_hc, const uint16_t *hc_fn, const float *h
                  const float *hc_base, float *post, float *comb, float *out, int64_t n_tokens,
                  int n_embd, int iters, float eps, cudaStream_t s);
 
+// comb_out[t][16] = Sinkhorn(logits[t][16]), one thread per token.
+void hc_sinkhorn_rows(const float *logits, float *comb_out, int64_t n_tokens, int iters, float eps,
+                      cudaStream_t s);
+
 // logits != nullptr: comb is produced by Sinkhorn from logits (and stored to
 // comb_out when given); otherwise comb/post are read.
 void hc_post_rows(const float *block_out, const float *block_out2, const float *residual_hc,

@@ -27,7 +27,10 @@ struct ds4b200_path {
     float *residual_out = nullptr, *kv_scales = nullptr, *kv_tail = nullptr, *ffn_out = nullptr;
     uint16_t *normed_bf16 = nullptr;
     uint8_t *kv_codes = nullptr;
+    float *comb = nullptr;             // [T][16] Sinkhorn matrices of the layer in flight
     float *gather_scratch = nullptr;   // [T][kv_dim] rows gathered from the cache for D2H
+    cudaStream_t side = nullptr;       // the Sinkhorn rows run here, beside the other ops
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     // graph cache (one per layer count)
     std::map<int, cudaGraphExec_t> graphs;
     std::vector<cudaEvent_t> events;
@@ -72,11 +75,21 @@ __global__ void gather_rows_kernel(const uint8_t *src, const int32_t *slots, uin
 float *hc_in(ds4b200_path *p, int layer) { return (layer & 1) ? p->hc_b : p->hc_a; }
 float *hc_out(ds4b200_path *p, int layer) { return (layer & 1) ? p->hc_a : p->hc_b; }
 
-// The four fused launches of one layer.  `op` < 0 runs all of them.
+// The launches of one layer.  `op` < 0 runs all of them, with the Sinkhorn rows
+// (which depend only on the logits) forked onto the side stream so that their
+// serial chains of divisions overlap the three streaming kernels before the mix.
+// `op` >= 0 runs one kernel alone on the main stream (profiling).
 void enqueue_layer(ds4b200_path *p, int layer, int op) {
     const ds4b200_path_config &c = p->cfg;
     const int64_t T = c.n_tokens;
     cudaStream_t s = p->stream;
+    if (op < 0) {
+        cudaEventRecord(p->ev_fork, s);
+        cudaStreamWaitEvent(p->side, p->ev_fork, 0);
+        ds4b200::hc_sinkhorn_rows(p->hc_logits, p->comb, T, c.sinkhorn_iters, c.eps, p->side);
+        cudaEventRecord(p->ev_join, p->side);
+    }
+    if (op == 4) ds4b200::hc_sinkhorn_rows(p->hc_logits, p->comb, T, c.sinkhorn_iters, c.eps, s);
     if (op < 0 || op == 0)
         ds4b200::embed_gather_rows(p->table, c.table_dtype, p->ids, 0, T, c.n_embd, p->residual,
                                    p->norm_w, c.eps, p->residual_out, 1, nullptr, p->normed_bf16, s);
@@ -92,9 +105,10 @@ void enqueue_layer(ds4b200_path *p, int layer, int op) {
     if (op < 0 || op == 2)
         ds4b200::swiglu_rows(p->gate, p->up, p->router_w, p->ffn_out, T, c.top_k, c.ff_dim,
                              c.glu_mode, c.clamp, 1, c.glu_fast_exp, s);
+    if (op < 0) cudaStreamWaitEvent(s, p->ev_join, 0);
     if (op < 0 || op == 3)
-        ds4b200::hc_post_rows(nullptr, nullptr, hc_in(p, layer), nullptr, nullptr, p->hc_logits,
-                              nullptr, hc_out(p, layer), T, c.n_embd, c.sinkhorn_iters, c.eps, s);
+        ds4b200::hc_post_rows(nullptr, nullptr, hc_in(p, layer), nullptr, p->comb, nullptr, nullptr,
+                              hc_out(p, layer), T, c.n_embd, 0, 0.0f, s);
 }
 
 int enqueue_run(ds4b200_path *p, int n_layers) {
@@ -168,7 +182,10 @@ ds4b200_path *ds4b200_path_create(const ds4b200_path_config *cfg) {
     cudaGetDevice(&p->device);
     p->n_scales = c.fp8_scale_mode == DS4B200_FP8_BLOCK64_POW2 ? (c.kv_dim - c.n_rot) / 64 : 1;
     const int64_t T = c.n_tokens, L = c.max_layers;
-    bool good = cudaStreamCreateWithFlags(&p->stream, cudaStreamNonBlocking) == cudaSuccess;
+    bool good = cudaStreamCreateWithFlags(&p->stream, cudaStreamNonBlocking) == cudaSuccess &&
+                cudaStreamCreateWithFlags(&p->side, cudaStreamNonBlocking) == cudaSuccess &&
+                cudaEventCreateWithFlags(&p->ev_fork, cudaEventDisableTiming) == cudaSuccess &&
+                cudaEventCreateWithFlags(&p->ev_join, cudaEventDisableTiming) == cudaSuccess;
     if (!good) set_error(-EIO, "path_create: cudaStreamCreate failed");
     good = good && alloc(p, "table", p->table, table_bytes(c));
     good = good && alloc(p, "ids", p->ids, T * 4) && alloc(p, "pos", p->pos, T * 4);
@@ -188,6 +205,7 @@ ds4b200_path *ds4b200_path_create(const ds4b200_path_config *cfg) {
     if (c.fp8_scale_mode == DS4B200_FP8_BLOCK64_POW2)
         good = good && alloc(p, "kv_tail", p->kv_tail, L * c.n_slots * c.n_rot * 4);
     good = good && alloc(p, "ffn_out", p->ffn_out, T * c.ff_dim * 4);
+    good = good && alloc(p, "comb", p->comb, T * 16 * 4);
     good = good && alloc(p, "gather_scratch", p->gather_scratch, T * c.kv_dim * 4);
     if (good) {
         // ids default to 0 so a run before the first upload stays inside the table
@@ -200,7 +218,11 @@ ds4b200_path *ds4b200_path_create(const ds4b200_path_config *cfg) {
 void ds4b200_path_destroy(ds4b200_path *p) {
     if (!p) return;
     if (p->stream) cudaStreamSynchronize(p->stream);
+    if (p->side) cudaStreamSynchronize(p->side);
     for (auto &g : p->graphs) cudaGraphExecDestroy(g.second);
+    if (p->ev_fork) cudaEventDestroy(p->ev_fork);
+    if (p->ev_join) cudaEventDestroy(p->ev_join);
+    if (p->side) cudaStreamDestroy(p->side);
     for (cudaEvent_t e : p->events) cudaEventDestroy(e);
     for (void *d : p->owned) cudaFree(d);
     if (p->stream) cudaStreamDestroy(p->stream);
@@ -297,34 +319,27 @@ int ds4b200_path_time_device(ds4b200_path *p, int n_layers, int warmup, int step
     return 0;
 }
 
-int ds4b200_path_profile_ops(ds4b200_path *p, int n_layers, float *ms_per_op, int *launches_per_op) {
-    if (!p || n_layers < 1 || !ms_per_op) return set_error(-EINVAL, "path_profile_ops: bad argument");
-    const size_t n_ev = (size_t)n_layers * 4 * 2;
-    if (int rc = ensure_events(p, n_ev)) return rc;
-    size_t e = 0;
-    for (int l = 0; l < n_layers; ++l)
-        for (int op = 0; op < 4; ++op) {
-            CUDA_OK(cudaEventRecord(p->events[e++], p->stream), "path_profile_ops: event");
-            enqueue_layer(p, l, op);
-            CUDA_OK(cudaEventRecord(p->events[e++], p->stream), "path_profile_ops: event");
-        }
+int ds4b200_path_profile_ops(ds4b200_path *p, int reps, float *ms_per_launch) {
+    if (!p || reps < 1 || !ms_per_launch) return set_error(-EINVAL, "path_profile_ops: bad argument");
+    if (int rc = ensure_events(p, 2 * DS4B200_PATH_N_KERNELS)) return rc;
+    if (int rc = enqueue_run(p, 1)) return rc;        // valid comb / cache contents, warm caches
+    for (int op = 0; op < DS4B200_PATH_N_KERNELS; ++op) {
+        CUDA_OK(cudaEventRecord(p->events[2 * op], p->stream), "path_profile_ops: event");
+        for (int r = 0; r < reps; ++r) enqueue_layer(p, r, op);
+        CUDA_OK(cudaEventRecord(p->events[2 * op + 1], p->stream), "path_profile_ops: event");
+    }
     CUDA_OK(cudaGetLastError(), "path_profile_ops: launch");
     CUDA_OK(cudaStreamSynchronize(p->stream), "path_profile_ops: sync");
-    for (int op = 0; op < 4; ++op) { ms_per_op[op] = 0.0f; if (launches_per_op) launches_per_op[op] = 0; }
-    e = 0;
-    for (int l = 0; l < n_layers; ++l)
-        for (int op = 0; op < 4; ++op) {
-            float ms = 0.0f;
-            CUDA_OK(cudaEventElapsedTime(&ms, p->events[e], p->events[e + 1]), "path_profile_ops: elapsed");
-            e += 2;
-            ms_per_op[op] += ms;
-            if (launches_per_op) launches_per_op[op] += 1;
-        }
+    for (int op = 0; op < DS4B200_PATH_N_KERNELS; ++op) {
+        float ms = 0.0f;
+        CUDA_OK(cudaEventElapsedTime(&ms, p->events[2 * op], p->events[2 * op + 1]), "path_profile_ops: elapsed");
+        ms_per_launch[op] = ms / (float)reps;
+    }
     return 0;
 }
 
 int ds4b200_path_launches_per_run(ds4b200_path *p, int n_layers) {
-    return p ? 4 * n_layers : 0;
+    return p ? DS4B200_PATH_N_KERNELS * n_layers : 0;
 }
 
 int64_t ds4b200_path_op_bytes(ds4b200_path *p, int op) {
@@ -338,6 +353,7 @@ int64_t ds4b200_path_op_bytes(ds4b200_path *p, int op) {
                         (p->kv_tail ? (int64_t)c.n_rot * 4 : 0));
     case 2: return T * ((int64_t)2 * c.top_k * c.ff_dim * 4 + (int64_t)c.top_k * 4 + (int64_t)c.ff_dim * 4);
     case 3: return T * ((int64_t)2 * 4 * c.n_embd * 4 + 64);
+    case 4: return T * (int64_t)(64 + 64);
     default: return 0;
     }
 }

@@ -18,7 +18,7 @@ __all__ = [
     "FP8_BLOCK64_POW2", "FP8_ROW_AMAX", "GLU_CLAMP_REF", "GLU_CLAMP_SYM", "GLU_PLAIN",
     "TABLE_F16", "TABLE_Q8_0", "RopeParams", "rope_params_for_layer", "rope_params_explicit",
     "add", "rms_norm_rows", "embed_gather_rows", "rope_rows", "fp8_kv_round_trip_rows",
-    "rope_fp8_store_rows", "swiglu_rows", "hc_pre_rows", "hc_post_rows", "hc_sinkhorn_mix_rows",
+    "rope_fp8_store_rows", "swiglu_rows", "hc_pre_rows", "hc_post_rows", "hc_sinkhorn_rows", "hc_sinkhorn_mix_rows",
     "e4m3_encode", "e4m3_decode", "e4m3_selfcheck", "device_status",
 ]
 
@@ -140,6 +140,13 @@ def hc_post_rows(block_out, resid, post, comb, block_out2=None):
     check(_lib.load().ds4b200_hc_post_rows_f32(_p(block_out), _p(block_out2), _p(resid), _p(post),
                                                _p(comb), _p(out), T, n, _s()))
     return out
+
+
+def hc_sinkhorn_rows(logits, iters=20, eps=1e-6):
+    """logits [T, 16] -> comb [T, 16]."""
+    comb = torch.empty_like(logits)
+    check(_lib.load().ds4b200_hc_sinkhorn_rows_f32(_p(logits), _p(comb), logits.shape[0], iters, eps, _s()))
+    return comb
 
 
 def hc_sinkhorn_mix_rows(logits, resid, iters=20, eps=1e-6, want_comb=False):

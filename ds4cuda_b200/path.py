@@ -8,7 +8,7 @@ import numpy as np
 from . import _lib
 from ._lib import FP8_ROW_AMAX, GLU_CLAMP_REF, TABLE_Q8_0, PathConfig, PathIO, RopeParams, check
 
-OPS = ("gather", "kvstore", "swiglu", "hcmix")
+KERNELS = ("gather", "kvstore", "swiglu", "hcmix", "sinkhorn")
 
 
 class PrefillPath:
@@ -94,11 +94,11 @@ class PrefillPath:
         check(self.lib.ds4b200_path_time_device(self.handle, n_layers, warmup, steps, C.byref(ms)))
         return ms.value
 
-    def profile_ops(self, n_layers: int):
-        ms = (C.c_float * 4)()
-        n = (C.c_int * 4)()
-        check(self.lib.ds4b200_path_profile_ops(self.handle, n_layers, ms, n))
-        return list(ms), list(n)
+    def profile_ops(self, reps: int) -> dict:
+        """Average ms per launch of each kernel (back-to-back launches of it alone)."""
+        ms = (C.c_float * len(KERNELS))()
+        check(self.lib.ds4b200_path_profile_ops(self.handle, reps, ms))
+        return dict(zip(KERNELS, ms))
 
     def launches_per_run(self, n_layers: int) -> int:
         return self.lib.ds4b200_path_launches_per_run(self.handle, n_layers)

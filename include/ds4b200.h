@@ -191,10 +191,18 @@ int ds4b200_hc_post_rows_f32(const float *block_out, const float *block_out2,
                              const float *residual_hc, const float *post, const float *comb,
                              float *out_hc, int64_t n_tokens, int n_embd, void *stream);
 
-/* Sinkhorn mixing: logits[t][16] (index src+4*dst) -> row softmax + eps ->
- * `sinkhorn_iters` normalisation sweeps (cuda/hc_sinkhorn.cu:224-289) -> mix
- * the 4 residual streams, out_hc[t][dst] = sum_src comb[dst+4*src]*resid[t][src].
- * comb_out[t][16] nullable. */
+/* The Sinkhorn step alone (cuda/hc_sinkhorn.cu:224-289): logits[t][16] (index
+ * src+4*dst) -> row softmax + eps -> one column pass, then sinkhorn_iters-1
+ * (row, column) passes, each dividing by (sum + eps) -> comb[t][16].  One thread
+ * per token, so every token's serial chain of divisions runs side by side. */
+int ds4b200_hc_sinkhorn_rows_f32(const float *logits, float *comb, int64_t n_tokens,
+                                 int sinkhorn_iters, float eps, void *stream);
+
+/* Sinkhorn mixing: comb as above, then mix the 4 residual streams,
+ * out_hc[t][dst] = sum_src comb[dst+4*src]*resid[t][src].  With comb_out[t][16]
+ * given this is two launches (the Sinkhorn rows, then a pure streaming mix that
+ * reads comb_out); with comb_out NULL it is one kernel that runs each token's
+ * sweeps on one thread of the token's CTA, which is several times slower. */
 int ds4b200_hc_sinkhorn_mix_rows_f32(const float *logits, const float *residual_hc,
                                      float *out_hc, float *comb_out, int64_t n_tokens,
                                      int n_embd, int sinkhorn_iters, float eps, void *stream);

@@ -10,8 +10,9 @@
  *                                                      (ds4b200_rope_fp8_store_rows)
  *   swiglu   clamped SwiGLU x router weight, summed over the top-k experts
  *                                                      (ds4b200_swiglu_rows_f32)
- *   hcmix    4x4 Sinkhorn + mix of the 4 hyper-connection streams
- *                                                      (ds4b200_hc_sinkhorn_mix_rows_f32)
+ *   hcmix    4x4 Sinkhorn (ds4b200_hc_sinkhorn_rows_f32, one thread per token,
+ *            overlapped with the three kernels above) + mix of the 4
+ *            hyper-connection streams                  (ds4b200_hc_post_rows_f32)
  *
  * It is the C/C++ host side the benchmark and the end-to-end tests drive; the
  * reference has no counterpart object (its cuda/forward_batch.cu:264-284 loops
@@ -72,6 +73,10 @@ typedef struct ds4b200_path_io {
 
 typedef struct ds4b200_path ds4b200_path;
 
+/* Kernels one layer launches: gather, kvstore, swiglu, hcmix and the Sinkhorn
+ * rows that feed hcmix (run on a side stream beside the first three). */
+#define DS4B200_PATH_N_KERNELS 5
+
 /* Allocates every device buffer on the current device.  NULL on failure
  * (ds4b200_last_error() says why). */
 ds4b200_path *ds4b200_path_create(const ds4b200_path_config *cfg);
@@ -96,14 +101,16 @@ int ds4b200_path_run_host(ds4b200_path *p, const ds4b200_path_io *host, int n_la
 /* Time `steps` back-to-back device runs after `warmup` untimed ones, with
  * events on the path's stream.  *ms_total = time of all timed steps. */
 int ds4b200_path_time_device(ds4b200_path *p, int n_layers, int warmup, int steps, float *ms_total);
-/* One run with an event pair around every launch: ms_per_op[4] receives the
- * summed device time of gather, kvstore, swiglu, hcmix; launches_per_op[4] the
- * launch counts. */
-int ds4b200_path_profile_ops(ds4b200_path *p, int n_layers, float *ms_per_op, int *launches_per_op);
+/* Average device time of one launch of each kernel, measured with events on
+ * the path's stream around `reps` back-to-back launches of that kernel alone:
+ * ms_per_launch[DS4B200_PATH_N_KERNELS] in the order gather, kvstore, swiglu,
+ * hcmix, sinkhorn. */
+int ds4b200_path_profile_ops(ds4b200_path *p, int reps, float *ms_per_launch);
 /* Kernel launches one device run of n_layers enqueues. */
 int ds4b200_path_launches_per_run(ds4b200_path *p, int n_layers);
-/* Algorithmic HBM bytes of one launch of op i (0 gather, 1 kvstore, 2 swiglu,
- * 3 hcmix): every input row read once, every output row written once. */
+/* Algorithmic HBM bytes of one launch of kernel i (0 gather, 1 kvstore,
+ * 2 swiglu, 3 hcmix, 4 sinkhorn): every input row read once, every output row
+ * written once. */
 int64_t ds4b200_path_op_bytes(ds4b200_path *p, int op);
 
 #ifdef __cplusplus

@@ -360,8 +360,11 @@ def test_rope_fp8_store_two_stage_bit_exactness(ops, oracle, mode):
     # stage (ii)
     c2, s2, t2, r2 = oracle.rope_fp8_store_rows(kv, pos, p, 64, osm, n_slots=n_slots, slots=slots)
     assert_close(host(rope_out), r2, what="rotated row")
+    # ROW_AMAX: when the row maximum sits in the rotated tail the scale inherits the
+    # last-bit difference of cosf/sinf, so scales agree to an ulp, not always bit for bit
+    np.testing.assert_allclose(host(scales)[slots], s2[slots], rtol=1e-5)
     same_scale = (host(scales)[slots] == s2[slots]).all(axis=1)
-    assert same_scale.mean() > 0.99
+    assert same_scale.mean() > (0.99 if mode == "block64" else 0.8)
     a, b = host(codes)[slots][same_scale], c2[slots][same_scale]
     diff = a != b
     assert diff.mean() < 2e-3, f"{diff.sum()} differing codes"
@@ -500,6 +503,13 @@ def test_hc_post_and_sinkhorn_mix_rows(ops, oracle, ref, n_embd, T):
         L.ds4b200_launch_hc_post_f32(*[x.data_ptr() for x in t], mine.data_ptr(), 4, n_embd, None)
         ref.call("hc_post_f32", *t, r, 4, n_embd)
         assert_bits(host(mine), host(r), "hc_post vs reference kernel, bit for bit")
+
+
+def test_reference_kernel_library_present(ref):
+    """The bit-for-bit comparisons above run only with the reference's kernels rebuilt for sm_100a."""
+    if ref is None:
+        pytest.skip("oracle/_ref/libds4ref.so not built: reference-kernel comparisons did not run")
+    assert ref.lib() is not None
 
 
 def test_empty_inputs_are_no_ops(ops):
