@@ -124,3 +124,32 @@ def test_ops_refuse_cpu_tensors():
     from ds4cuda_b200 import ops
     with pytest.raises(ValueError, match="CUDA tensors only"):
         ops.add(torch.zeros(4), torch.zeros(4))
+
+
+REFERENCE = Path("/root/reference")
+CALLERS = ["forward_layer.cu", "forward_token.cu", "forward_batch.cu", "compressor.cu"]
+STAR = ("launch_rms_norm_f32", "launch_rms_norm_batch_f32", "launch_add_f32", "launch_tail_rope_yarn_f32",
+        "launch_tail_rope_yarn_inverse_f32", "launch_fp8_kv_quantize_round_trip_f32", "launch_silu_mul_f32",
+        "launch_embed_token_f16_to_f32", "launch_hc_attn_pre_f32", "launch_hc_attn_pre_v2_f32",
+        "launch_hc_ffn_pre_v2_f32", "launch_hc_post_f32")
+
+
+@pytest.mark.skipif(not (REFERENCE / "cuda" / "forward_layer.cu").exists(), reason="reference tree not mounted")
+def test_reference_callers_resolve_their_launchers_in_our_library(tmp_path):
+    """Compile the reference's own callers (unchanged) and check that every launcher of the
+    path they import, by mangled name, is defined by libds4b200.so: the drop-in is link-compatible."""
+    from ds4cuda_b200 import _lib, build
+    defined = set(subprocess.run(["nm", "-D", "--defined-only", str(_lib.LIB_PATH)], capture_output=True,
+                                 text=True, check=True).stdout.split())
+    wanted = set()
+    for src in CALLERS:
+        obj = tmp_path / (src + ".o")
+        subprocess.run([build.nvcc(), "-O1", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a",
+                        f"-I{REFERENCE}/include", f"-I{REFERENCE}/cuda", "-c", str(REFERENCE / "cuda" / src),
+                        "-o", str(obj)], check=True, capture_output=True)
+        for line in subprocess.run(["nm", "-u", str(obj)], capture_output=True, text=True, check=True).stdout.split():
+            if line.startswith("_ZN7ds4cuda") and any(f"{len(n)}{n}E" in line for n in STAR):
+                wanted.add(line)
+    assert len(wanted) >= 11, wanted          # every launcher of the path is imported by some caller
+    missing = sorted(w for w in wanted if w not in defined)
+    assert not missing, f"reference callers import launchers we do not define: {missing}"

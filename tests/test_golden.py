@@ -1,0 +1,99 @@
+"""CPU test: the oracle against outputs of the REFERENCE's own kernels.
+
+tests/golden/reference_kernels_config1.npz was produced on a B200 by
+tests/golden/make_reference_fixtures.py, which runs the reference's CUDA
+kernels (rebuilt for sm_100a, unmodified sources) on the seeded config-1
+inputs.  This is what pins the oracle to the reference."""
+import ast
+import importlib.util
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+HERE = Path(__file__).resolve().parent
+FIXTURE = HERE / "golden" / "reference_kernels_config1.npz"
+REL_TOL = 1e-5
+
+
+def _load_generator():
+    spec = importlib.util.spec_from_file_location("make_reference_fixtures",
+                                                  HERE / "golden" / "make_reference_fixtures.py")
+    # only golden_inputs()/digest() are used; importing needs torch but no GPU
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+@pytest.fixture(scope="module")
+def golden():
+    gen = _load_generator()
+    fx = np.load(FIXTURE)
+    d = gen.golden_inputs()
+    assert gen.digest(d) == ast.literal_eval(str(fx["__digests__"])), \
+        "seeded inputs no longer reproduce the ones the fixture was made from"
+    return d, fx
+
+
+def close(got, want, rel=REL_TOL):
+    err = np.abs(np.asarray(got, np.float64) - np.asarray(want, np.float64)).max()
+    assert err <= rel * np.abs(want).max(), f"max-abs error {err:.3e} > {rel * np.abs(want).max():.3e}"
+
+
+def test_fixture_is_from_a_b200(golden):
+    _, fx = golden
+    assert "B200" in ast.literal_eval(str(fx["__meta__"]))["gpu"]
+
+
+def test_rms_norm_and_add(oracle, golden):
+    d, fx = golden
+    close(oracle.rms_norm_rows(d["x"], d["w"])[0][0], fx["rms_norm"])
+    close(oracle.rms_norm_rows(d["q"][0])[0], fx["rms_norm_batch_unit"])
+    assert np.array_equal(oracle.add(d["x"][0], d["add_b"]), fx["add"])
+
+
+@pytest.mark.parametrize("il,pos", [(0, 9), (0, 1234), (2, 1234), (3, 4095)])
+def test_rope_forward_and_inverse(oracle, golden, il, pos):
+    d, fx = golden
+    p = oracle.rope_params_for_layer(il)
+    # the reference kernel takes theta_scale from the device's powf; on B200 it has the
+    # same bits as libm's, so the plain f32 bar holds even at position 4095
+    rel = REL_TOL
+    fwd = oracle.rope_rows(d["q"], np.array([pos], np.int32), p)[0]
+    inv = oracle.rope_rows(d["q"], np.array([pos], np.int32), p, inverse=True)[0]
+    close(fwd[:, 448:], fx[f"rope_tail_il{il}_pos{pos}"], rel)
+    close(inv[:, 448:], fx[f"rope_inv_tail_il{il}_pos{pos}"], rel)
+
+
+def test_silu_mul(oracle, golden):
+    d, fx = golden
+    close(oracle.swiglu_rows(d["gate"], d["up"])[0, 0], fx["silu_mul"])
+
+
+def test_fp8_round_trip_bit_exact(oracle, golden):
+    d, fx = golden
+    got = oracle.fp8_kv_round_trip_rows(d["kv"])
+    assert np.array_equal(got.view(np.uint32), fx["fp8_round_trip"].view(np.uint32))
+
+
+def test_gather_and_dequant_bit_exact(oracle, golden):
+    d, fx = golden
+    rows, _, _ = oracle.embed_gather_rows(d["f16_table"], oracle.TABLE_F16, np.array([11], np.int32), 4096)
+    assert np.array_equal(rows[0, 0].view(np.uint32), fx["embed_f16_row11"].view(np.uint32))
+    deq, _, _ = oracle.embed_gather_rows(d["q8_blocks"], oracle.TABLE_Q8_0, np.array([0], np.int32), 64 * 32)
+    assert np.array_equal(deq[0, 0].view(np.uint32), fx["dequant_q8_0"].view(np.uint32))
+
+
+def test_hc_pre_and_post(oracle, golden):
+    d, fx = golden
+    post, comb, out, mix = oracle.hc_pre_rows(d["hc_resid"], d["hc_fn"], d["hc_scale"], d["hc_base"])
+    close(mix[0], fx["hc_pre_mix"])
+    close(post[0], fx["hc_pre_post"])
+    close(comb[0], fx["hc_pre_comb"])
+    close(out[0], fx["hc_pre_out"])
+    # HC post on the reference's own post/comb: same inputs, same order of operations
+    hp = oracle.hc_post_rows(d["hc_block"], d["hc_resid"], fx["hc_pre_post"][None], fx["hc_pre_comb"][None])
+    close(hp[0], fx["hc_post"])
+    # and the Sinkhorn step alone, from the reference's own mix values
+    v = fx["hc_pre_mix"][8:] * d["hc_scale"][2] + d["hc_base"][8:]
+    close(oracle.sinkhorn_4x4(v.astype(np.float32)), fx["hc_pre_comb"])

@@ -252,12 +252,11 @@ def test_rope_drop_in_launchers_match_reference_kernels(ops, oracle, ref, il, po
     L.ds4b200_launch_tail_rope_yarn_inverse_f32(out.data_ptr(), inv.data_ptr(), 64, 512, 64, pos, il, None)
     p = oracle.rope_params_for_layer(il)
     want = oracle.rope_rows(q[None], np.array([pos], np.int32), p)[0]
-    # The launcher evaluates theta_scale with the device's powf, as the reference
-    # kernel does; if that differs from libm's by one ulp the angle of a low pair
-    # moves by about pos * 1.2e-7 rad, so the bound against the CPU oracle grows
-    # with pos.  The bit-for-bit check against the reference kernel below is the
-    # tight one.
-    assert_close(host(out), want, rel=REL_TOL + pos * 1.2e-7, what=f"launcher il={il} pos={pos}")
+    # The launcher evaluates theta_scale with the device's powf, as the reference kernel
+    # does; on B200 that gives libm's bits, so the plain bar holds up to position 4095.
+    # At 65535 one ulp of theta_scale would already move the angle by 8e-3 rad: there the
+    # bit-for-bit check against the reference kernel below is the meaningful one.
+    assert_close(host(out), want, rel=REL_TOL if pos <= 4095 else 1e-2, what=f"launcher il={il} pos={pos}")
     assert_close(host(inv), q, rel=2e-6, what="inverse undoes forward")
     if ref:
         r, ri = torch.empty_like(dq), torch.empty_like(dq)
