@@ -74,6 +74,7 @@ SIGNATURES = {
     "ds4b200_hc_post_rows_f32": (_I, [_P, _P, _P, _P, _P, _P, _L, _I, _P]),
     "ds4b200_hc_sinkhorn_rows_f32": (_I, [_P, _P, _L, _I, _F, _P]),
     "ds4b200_hc_sinkhorn_mix_rows_f32": (_I, [_P, _P, _P, _P, _L, _I, _I, _F, _P]),
+    "ds4b200_hc_sinkhorn_mix_rows_static_f32": (_I, [_P, _P, _P, _L, _I, _I, _F, _P]),
     "ds4b200_e4m3_encode_f32": (_I, [_P, _P, _L, _P]),
     "ds4b200_e4m3_decode_f32": (_I, [_P, _P, _L, _P]),
     "ds4b200_e4m3_selfcheck": (_I, [C.c_uint32, C.c_uint64, _P, _P]),

@@ -207,6 +207,35 @@ int ds4b200_hc_sinkhorn_mix_rows_f32(const float *logits, const float *residual_
                                      float *out_hc, float *comb_out, int64_t n_tokens,
                                      int n_embd, int sinkhorn_iters, float eps, void *stream);
 
+/* Sinkhorn mixing without a caller-provided buffer for the 4x4 matrices and
+ * without any allocation.  This entry point has no counterpart in the reference.
+ *
+ * Who it is for: callers that can pass inputs and outputs but cannot come up
+ * with the [n_tokens][16] intermediate that makes
+ * ds4b200_hc_sinkhorn_mix_rows_f32 fast — an engine whose device memory is one
+ * arena laid out at start-up, a token loop where allocator calls are banned
+ * because cudaMalloc stalls the device and can fail, a binding that only ever
+ * sees the pointers it is given.  The matrices live instead in a fixed array in
+ * device memory inside the library: DS4B200_STATIC_MAX_TOKENS x 16 floats
+ * (1 MiB), present on every GPU that loads the library until the process ends.
+ *
+ * Rules that follow from the shared array:
+ *  - n_tokens > DS4B200_STATIC_MAX_TOKENS is refused with -EINVAL (split the
+ *    batch, or use the variant above with your own comb_out);
+ *  - two calls whose kernels may run at the same time on one GPU (different
+ *    streams, different threads) race on the array: serialise them;
+ *  - the array keeps whatever the last call wrote; every call overwrites the
+ *    rows it reads before reading them, so that is harmless;
+ *  - the first call on each device looks the array's address up
+ *    (cudaGetSymbolAddress) and caches it; make that first call once during
+ *    start-up, before any stream capture begins on that device.
+ * It calls no cudaMalloc / cudaFree and no allocating library routine.
+ * Results are those of ds4b200_hc_sinkhorn_mix_rows_f32 with comb_out given. */
+#define DS4B200_STATIC_MAX_TOKENS 16384
+int ds4b200_hc_sinkhorn_mix_rows_static_f32(const float *logits, const float *residual_hc,
+                                            float *out_hc, int64_t n_tokens, int n_embd,
+                                            int sinkhorn_iters, float eps, void *stream);
+
 /* E4M3FN code of each of n f32 values (sign bit | nearest index, saturating),
  * and its inverse; used to check the encoder exhaustively. */
 int ds4b200_e4m3_encode_f32(const float *x, uint8_t *codes, int64_t n, void *stream);
