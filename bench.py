@@ -36,7 +36,10 @@ FALLBACK_HBM_GBS = 6650.0      # earlier measurement on this pool, used only wit
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel
 # at the benchmark shape, from the ncu capture summarised under profiles/.
-NCU_TRAFFIC_BYTES = {"hcmix": None, "swiglu": None, "gather": None, "kvstore": None, "sinkhorn": None}
+# Captured at 2048 tokens (profiles/ncu_full_set_small_case_2048tok.md) and scaled x2 to the
+# 4096-token launch; reads scale exactly, writes are undercounted by what the L2 still holds.
+NCU_TRAFFIC_BYTES = {"hcmix": 2 * (134375936 + 78468096), "swiglu": 2 * (201396736 + 10977280),
+                     "gather": 2 * (42454528 + 3498240), "kvstore": 2 * 4265216, "sinkhorn": None}
 
 
 def parse_args():
@@ -196,6 +199,60 @@ def cpu_baseline_leg(x, table, budget_s, full_layers):
                       f"scaled to {full_layers} layers"}
 
 
+def reference_kernels_leg(tokens, n_layers):
+    """Baseline leg: the reference's OWN CUDA kernels for these stages, rebuilt unchanged for
+    sm_100a (oracle/_ref), driven the way the reference drives them — one token per launch
+    where it has no batched form — on a bounded sample of tokens, scaled to the full batch.
+    Returns None when oracle/_ref has not been built."""
+    import torch
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import ref_lib
+    if not ref_lib.available():
+        return None
+    sample = min(256, tokens)
+    dev = "cuda"
+    blocks = torch.randint(0, 255, (sample, 128 * 34), dtype=torch.uint8, device=dev)
+    row, row2, row3 = (torch.empty(sample, N_EMBD, device=dev) for _ in range(3))
+    resid, w = torch.randn(sample, N_EMBD, device=dev), torch.rand(N_EMBD, device=dev) + 0.5
+    kv = torch.randn(sample, KV_DIM, device=dev)
+    gate, up = torch.randn(sample * TOP_K * FF_DIM, device=dev), torch.randn(sample * TOP_K * FF_DIM, device=dev)
+    mid = torch.empty_like(gate)
+    hc, hc_out = torch.randn(sample, 4, N_EMBD, device=dev), torch.empty(sample, 4, N_EMBD, device=dev)
+    post, comb, block = torch.rand(4, device=dev), torch.rand(16, device=dev), torch.randn(N_EMBD, device=dev)
+
+    def gather():        # Q8_0 dequant + add + RMSNorm, per token (cuda/dense_q8.cu:75, elementwise.cu:46, norm.cu:109)
+        for t in range(sample):
+            ref_lib.call("dequant_q8_0_to_f32", blocks[t], row[t], 128)
+            ref_lib.call("add_f32", row[t], resid[t], row2[t], N_EMBD)
+            ref_lib.call("rms_norm_f32", row2[t], w, row3[t], N_EMBD, 1e-6)
+
+    def kvstore():       # KV RoPE per token (one pos per launch), FP8 round trip batched over rows
+        for t in range(sample):
+            ref_lib.call("tail_rope_yarn_f32", kv[t], kv[t], 1, KV_DIM, N_ROT, t, 0)
+        ref_lib.call("fp8_kv_quantize_round_trip_f32", kv, kv, sample, KV_DIM, N_ROT)
+
+    def swiglu():        # its elementwise SwiGLU takes any n: one launch over all slots (no clamp, no combine)
+        ref_lib.call("silu_mul_f32", gate, up, mid, sample * TOP_K * FF_DIM)
+
+    def hcmix():         # HC post per token (cuda/hc_sinkhorn.cu:687)
+        for t in range(sample):
+            ref_lib.call("hc_post_f32", block, hc[t], post, comb, hc_out[t], 4, N_EMBD)
+
+    out = {}
+    for name, fn in (("gather", gather), ("kvstore", kvstore), ("swiglu", swiglu), ("hcmix", hcmix)):
+        fn()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        fn()
+        torch.cuda.synchronize()
+        out[name + "_us_per_4096_tokens"] = round((time.perf_counter() - t0) * 1e6 * tokens / sample, 1)
+    layer_us = sum(out.values())
+    out["tokens_per_s"] = tokens / (layer_us * 1e-6 * n_layers)
+    out["sample"] = (f"{sample} tokens, wall clock incl. launch overhead, scaled to {tokens} tokens x {n_layers} layers; "
+                     "single-token launchers looped as the reference does")
+    return out
+
+
 def run_reference_arm(args):
     """The reference's CPU path: the scalar C restatement, all host threads, bounded sample per step."""
     rank = int(os.environ.get("RANK", "0"))
@@ -323,9 +380,10 @@ def run_ours(args):
     sampler.join(timeout=2)
     clocks = sampler.summary()
 
-    cpu = None
+    cpu, ref_kernels = None, None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline_leg(x, table, args.cpu_seconds, args.layers)
+        ref_kernels = reference_kernels_leg(tokens, args.layers)
 
     launches = path.launches_per_run(args.layers) * args.steps
     path.close()
@@ -341,6 +399,7 @@ def run_ours(args):
         "hbm_gbs_per_gpu": round(hbm_gbs_step, 1),
         "hbm_frac_of_peak": round(hbm_gbs_step / peak, 4), "hbm_frac_of_8000": round(hbm_gbs_step / 8000.0, 4),
         "ops": ops_table, "roofline": roofline, "cpu_baseline": cpu,
+        "reference_kernels_sm100a": ref_kernels,
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms_step,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches, "cuda_graph": bool(args.graph), "clocks": clocks,

@@ -1,0 +1,286 @@
+// hc_pre_cluster.cu — the hyper-connection "pre" step for many tokens with the
+// 24 x (4*n_embd) f16 matrix resident on chip.
+//
+// Arithmetic: cuda/hc_sinkhorn.cu:85-305 of the reference (RMS over the token's
+// 4*n_embd residual block, 24 dot products with hc_fn, sigmoid gates, weighted
+// stream sum); the Sinkhorn sweeps over the 16 comb values run afterwards in
+// hc_sinkhorn_rows_kernel.
+//
+// Why a cluster: per token the step reads 64 KiB of activations but needs all
+// 768 KiB of hc_fn.  Re-reading hc_fn per token through L2 costs 12x the HBM
+// traffic of the activations.  Here a thread-block cluster of C CTAs splits the
+// columns: CTA r keeps the slice hc_fn[:, columns of r], converted once to f32 and
+// stored as pairs of output rows (192 KiB), in its shared memory for its whole
+// life, so that one 64-bit shared load feeds a packed two-lane FMA
+// (fma.rn.f32x2) per token, streams the matching column slice of every
+// token through registers exactly once (M tokens at a time, so each weight read
+// from shared memory feeds M tokens), and the C partial results per token
+// (24 dots + sum of squares) are exchanged over distributed shared memory with
+// one cluster barrier per token group.  Every CTA then holds the full sums,
+// computes the gates redundantly and writes its own column slice of `out`.
+#include <cooperative_groups.h>
+
+#include "device_utils.cuh"
+#include "kernels.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace ds4b200 {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kMixN = 24;
+constexpr int kSlots = 32;            // per token: 24 dots, slot 24 = sum of squares, rest unused
+
+
+// Sum 32 per-lane values across the warp; lane l ends with the total of value l.
+__device__ __forceinline__ float warp_transpose_sum32(float (&v)[32]) {
+    const int lane = threadIdx.x & 31;
+#pragma unroll
+    for (int half = 16; half >= 1; half >>= 1) {
+        const bool upper = (lane & half) != 0;
+#pragma unroll
+        for (int i = 0; i < half; ++i) {
+            const float send = upper ? v[i] : v[i + half];
+            const float keep = upper ? v[i + half] : v[i];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, half);
+        }
+    }
+    return v[0];
+}
+
+// Packed FMA on two f32 lanes: d = a * b + c per lane, one instruction on sm_100.
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+    unsigned long long ua = *reinterpret_cast<unsigned long long *>(&a);
+    unsigned long long ub = *reinterpret_cast<unsigned long long *>(&b);
+    unsigned long long uc = *reinterpret_cast<unsigned long long *>(&c), ud;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(ud) : "l"(ua), "l"(ub), "l"(uc));
+    return *reinterpret_cast<float2 *>(&ud);
+}
+
+// C: CTAs per cluster.  VC: float2 columns per thread per stream
+// (n_embd = C * VC * 512).  M: tokens processed together.
+template <int C, int VC, int M>
+__global__ void __launch_bounds__(kThreads, 1)
+hc_pre_cluster_kernel(const float *__restrict__ residual_hc, const uint16_t *__restrict__ hc_fn,
+                      const float *__restrict__ hc_scale, const float *__restrict__ hc_base,
+                      float *__restrict__ post_out, float *__restrict__ comb_out,
+                      float *__restrict__ out, int64_t n_tokens, int n_embd, float eps) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int kWPairs = (kMixN / 2) * 4 * VC * 2 * kThreads;       // float2 {row 2p, row 2p+1} entries
+    float2 *w_s = reinterpret_cast<float2 *>(smem_raw);
+    float *part = reinterpret_cast<float *>(w_s + kWPairs);            // [kWarps][M*32]
+    float *cl_part = part + kWarps * M * kSlots;                       // [2][C][M*32]
+    float *tot = cl_part + 2 * C * M * kSlots;                         // [M*32]
+    float *pre_s = tot + M * kSlots;                                   // [M][4]
+
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank();
+    const int64_t cluster_id = blockIdx.x / C, n_clusters = gridDim.x / C;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int cols = n_embd / C;                                       // floats per stream owned by this CTA
+    const int64_t hc_dim = 4 * (int64_t)n_embd;
+    const int col0 = rank * cols;
+
+    // resident slice of hc_fn: entry (((p*4+h)*VC+v)*2+c)*256+tid = rows 2p, 2p+1 at column
+    // col0 + 2*(v*256+tid) + c of stream h
+    for (int p = 0; p < kMixN / 2; ++p)
+#pragma unroll
+        for (int h = 0; h < 4; ++h)
+#pragma unroll
+            for (int v = 0; v < VC; ++v) {
+                const int64_t off = (int64_t)h * n_embd + col0 + 2 * (v * kThreads + tid);
+                const float2 lo = f16x2_bits_to_f32(__ldg(reinterpret_cast<const uint32_t *>(hc_fn + (2 * p) * hc_dim + off)));
+                const float2 hi = f16x2_bits_to_f32(__ldg(reinterpret_cast<const uint32_t *>(hc_fn + (2 * p + 1) * hc_dim + off)));
+                w_s[(((p * 4 + h) * VC + v) * 2 + 0) * kThreads + tid] = make_float2(lo.x, hi.x);
+                w_s[(((p * 4 + h) * VC + v) * 2 + 1) * kThreads + tid] = make_float2(lo.y, hi.y);
+            }
+    __syncthreads();
+
+    const int64_t n_groups = (n_tokens + M - 1) / M;
+    float2 xn[M][4][VC];
+    auto load_group = [&](int64_t g) {
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const int64_t t = g * M + m;
+#pragma unroll
+            for (int h = 0; h < 4; ++h)
+#pragma unroll
+                for (int v = 0; v < VC; ++v)
+                    xn[m][h][v] = (t < n_tokens)
+                        ? __ldcs(reinterpret_cast<const float2 *>(residual_hc + t * hc_dim + (int64_t)h * n_embd +
+                                                                   col0 + 2 * (v * kThreads + tid)))
+                        : make_float2(0.f, 0.f);
+        }
+    };
+    if (cluster_id < n_groups) load_group(cluster_id);
+
+    int buf = 0;
+    for (int64_t g = cluster_id; g < n_groups; g += n_clusters, buf ^= 1) {
+        float2 x[M][4][VC];
+#pragma unroll
+        for (int m = 0; m < M; ++m)
+#pragma unroll
+            for (int h = 0; h < 4; ++h)
+#pragma unroll
+                for (int v = 0; v < VC; ++v) x[m][h][v] = xn[m][h][v];
+        if (g + n_clusters < n_groups) load_group(g + n_clusters);     // next group's loads fly during the math
+
+        // ---- this thread's partial sums: pair p of token m holds rows 2p and 2p+1
+        float2 acc2[M][kMixN / 2];
+        float ss[M];
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            ss[m] = 0.0f;
+#pragma unroll
+            for (int p = 0; p < kMixN / 2; ++p) acc2[m][p] = make_float2(0.f, 0.f);
+        }
+#pragma unroll
+        for (int h = 0; h < 4; ++h)
+#pragma unroll
+            for (int v = 0; v < VC; ++v) {
+                float2 xx[M], xy[M];
+#pragma unroll
+                for (int m = 0; m < M; ++m) {
+                    xx[m] = make_float2(x[m][h][v].x, x[m][h][v].x);
+                    xy[m] = make_float2(x[m][h][v].y, x[m][h][v].y);
+                    ss[m] += x[m][h][v].x * x[m][h][v].x + x[m][h][v].y * x[m][h][v].y;
+                }
+#pragma unroll
+                for (int p = 0; p < kMixN / 2; ++p) {
+                    const float2 w0 = w_s[(((p * 4 + h) * VC + v) * 2 + 0) * kThreads + tid];
+                    const float2 w1 = w_s[(((p * 4 + h) * VC + v) * 2 + 1) * kThreads + tid];
+#pragma unroll
+                    for (int m = 0; m < M; ++m) {
+                        acc2[m][p] = ffma2(w0, xx[m], acc2[m][p]);
+                        acc2[m][p] = ffma2(w1, xy[m], acc2[m][p]);
+                    }
+                }
+            }
+        float acc[M][kSlots];
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+#pragma unroll
+            for (int p = 0; p < kMixN / 2; ++p) { acc[m][2 * p] = acc2[m][p].x; acc[m][2 * p + 1] = acc2[m][p].y; }
+            acc[m][kMixN] = ss[m];
+#pragma unroll
+            for (int k = kMixN + 1; k < kSlots; ++k) acc[m][k] = 0.0f;
+        }
+
+        // ---- CTA reduction, then exchange with the other CTAs of the cluster
+#pragma unroll
+        for (int m = 0; m < M; ++m) part[warp * M * kSlots + m * kSlots + lane] = warp_transpose_sum32(acc[m]);
+        __syncthreads();
+        if (tid < M * kSlots) {
+            float s = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) s += part[w * M * kSlots + tid];
+            float *mine = cl_part + (buf * C + rank) * M * kSlots + tid;
+#pragma unroll
+            for (int r = 0; r < C; ++r) *cluster.map_shared_rank(mine, r) = s;
+        }
+        cluster.sync();
+        if (tid < M * kSlots) {
+            float s = 0.0f;
+#pragma unroll
+            for (int r = 0; r < C; ++r) s += cl_part[(buf * C + r) * M * kSlots + tid];   // same order everywhere
+            tot[tid] = s;
+        }
+        __syncthreads();
+
+        // ---- gates (every CTA, identical results); rank 0 writes the small outputs
+        if (tid < 4 * M) {
+            const int m = tid >> 2, h = tid & 3;
+            const int64_t t = g * M + m;
+            const float rms = rms_scale(tot[m * kSlots + kMixN], (float)hc_dim, eps);
+            const float zp = (tot[m * kSlots + h] * rms) * hc_scale[0] + hc_base[h];
+            pre_s[m * 4 + h] = 1.0f / (1.0f + expf(-zp)) + eps;
+            if (rank == 0 && t < n_tokens) {
+                const float zq = (tot[m * kSlots + 4 + h] * rms) * hc_scale[1] + hc_base[4 + h];
+                post_out[t * 4 + h] = 2.0f / (1.0f + expf(-zq));
+            }
+        } else if (rank == 0 && tid >= 64 && tid < 64 + 16 * M) {
+            const int m = (tid - 64) >> 4, i = (tid - 64) & 15;
+            const int64_t t = g * M + m;
+            if (t < n_tokens) {
+                const float rms = rms_scale(tot[m * kSlots + kMixN], (float)hc_dim, eps);
+                comb_out[t * 16 + i] = (tot[m * kSlots + 8 + i] * rms) * hc_scale[2] + hc_base[8 + i];
+            }
+        }
+        __syncthreads();
+
+        // ---- weighted stream sum for this CTA's columns
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const int64_t t = g * M + m;
+            if (t >= n_tokens) continue;
+            const float p0 = pre_s[m * 4], p1 = pre_s[m * 4 + 1], p2 = pre_s[m * 4 + 2], p3 = pre_s[m * 4 + 3];
+#pragma unroll
+            for (int v = 0; v < VC; ++v) {
+                float2 o2;
+                o2.x = x[m][0][v].x * p0 + x[m][1][v].x * p1 + x[m][2][v].x * p2 + x[m][3][v].x * p3;
+                o2.y = x[m][0][v].y * p0 + x[m][1][v].y * p1 + x[m][2][v].y * p2 + x[m][3][v].y * p3;
+                __stcs(reinterpret_cast<float2 *>(out + t * n_embd + col0 + 2 * (v * kThreads + tid)), o2);
+            }
+        }
+    }
+    cluster.sync();     // nobody leaves while a neighbour may still address its shared memory
+}
+
+template <int C, int VC, int M>
+size_t smem_bytes() {
+    return sizeof(float2) * (kMixN / 2) * 4 * VC * 2 * kThreads +
+           sizeof(float) * (kWarps * M * kSlots + 2 * C * M * kSlots + M * kSlots + M * 4);
+}
+
+template <int C, int VC, int M>
+bool launch(const float *residual_hc, const uint16_t *hc_fn, const float *hc_scale, const float *hc_base,
+            float *post, float *comb, float *out, int64_t n_tokens, int n_embd, float eps, cudaStream_t s) {
+    auto kernel = hc_pre_cluster_kernel<C, VC, M>;
+    const size_t smem = smem_bytes<C, VC, M>();
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    cudaLaunchConfig_t cfg{};
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = C;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    cfg.gridDim = dim3(C);
+    int max_clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg) != cudaSuccess || max_clusters < 1) {
+        cudaGetLastError();
+        return false;
+    }
+    const int64_t n_groups = (n_tokens + M - 1) / M;
+    const int64_t clusters = n_groups < max_clusters ? n_groups : max_clusters;
+    cfg.gridDim = dim3((unsigned)(clusters * C));
+    return cudaLaunchKernelEx(&cfg, kernel, residual_hc, hc_fn, hc_scale, hc_base, post, comb, out, n_tokens,
+                              n_embd, eps) == cudaSuccess;
+}
+
+}  // namespace
+
+// Returns false when the shape has no cluster variant or the launch could not
+// be configured; the caller then uses the one-CTA-per-token kernel.
+bool hc_pre_rows_cluster(const float *residual_hc, const uint16_t *hc_fn, const float *hc_scale,
+                         const float *hc_base, float *post, float *comb, float *out, int64_t n_tokens,
+                         int n_embd, float eps, cudaStream_t s) {
+    if (!aligned8(residual_hc) || !aligned8(out) || (reinterpret_cast<uintptr_t>(hc_fn) & 3u)) return false;
+    // the f32 slice is 24 x 2048 x 4 B = 192 KiB per CTA whatever C is: n_embd = C * 512
+    if (n_embd == 8 * 512)
+        return launch<8, 1, 4>(residual_hc, hc_fn, hc_scale, hc_base, post, comb, out, n_tokens, n_embd, eps, s);
+    if (n_embd == 4 * 512)
+        return launch<4, 1, 4>(residual_hc, hc_fn, hc_scale, hc_base, post, comb, out, n_tokens, n_embd, eps, s);
+    return false;
+}
+
+}  // namespace ds4b200

@@ -48,6 +48,12 @@ void hc_pre_rows(const float *residual_hc, const uint16_t *hc_fn, const float *h
                  const float *hc_base, float *post, float *comb, float *out, int64_t n_tokens,
                  int n_embd, int iters, float eps, cudaStream_t s);
 
+// Cluster variant of the pre step without the Sinkhorn sweeps (comb receives the 16
+// pre-softmax values); false = shape not covered, nothing launched.
+bool hc_pre_rows_cluster(const float *residual_hc, const uint16_t *hc_fn, const float *hc_scale,
+                         const float *hc_base, float *post, float *comb, float *out, int64_t n_tokens,
+                         int n_embd, float eps, cudaStream_t s);
+
 // comb_out[t][16] = Sinkhorn(logits[t][16]), one thread per token.
 void hc_sinkhorn_rows(const float *logits, float *comb_out, int64_t n_tokens, int iters, float eps,
                       cudaStream_t s);
