@@ -221,22 +221,16 @@ def reference_kernels_leg(tokens, n_layers):
     post, comb, block = torch.rand(4, device=dev), torch.rand(16, device=dev), torch.randn(N_EMBD, device=dev)
 
     def gather():        # Q8_0 dequant + add + RMSNorm, per token (cuda/dense_q8.cu:75, elementwise.cu:46, norm.cu:109)
-        for t in range(sample):
-            ref_lib.call("dequant_q8_0_to_f32", blocks[t], row[t], 128)
-            ref_lib.call("add_f32", row[t], resid[t], row2[t], N_EMBD)
-            ref_lib.call("rms_norm_f32", row2[t], w, row3[t], N_EMBD, 1e-6)
+        ref_lib.call("loop_q8_gather_add_norm", blocks, resid, w, row, row2, row3, sample, N_EMBD, 1e-6)
 
     def kvstore():       # KV RoPE per token (one pos per launch), FP8 round trip batched over rows
-        for t in range(sample):
-            ref_lib.call("tail_rope_yarn_f32", kv[t], kv[t], 1, KV_DIM, N_ROT, t, 0)
-        ref_lib.call("fp8_kv_quantize_round_trip_f32", kv, kv, sample, KV_DIM, N_ROT)
+        ref_lib.call("loop_kv_rope_fp8", kv, sample, KV_DIM, N_ROT, 0)
 
     def swiglu():        # its elementwise SwiGLU takes any n: one launch over all slots (no clamp, no combine)
         ref_lib.call("silu_mul_f32", gate, up, mid, sample * TOP_K * FF_DIM)
 
     def hcmix():         # HC post per token (cuda/hc_sinkhorn.cu:687)
-        for t in range(sample):
-            ref_lib.call("hc_post_f32", block, hc[t], post, comb, hc_out[t], 4, N_EMBD)
+        ref_lib.call("loop_hc_post", block, hc, post, comb, hc_out, sample, N_EMBD)
 
     out = {}
     for name, fn in (("gather", gather), ("kvstore", kvstore), ("swiglu", swiglu), ("hcmix", hcmix)):
@@ -249,7 +243,7 @@ def reference_kernels_leg(tokens, n_layers):
     layer_us = sum(out.values())
     out["tokens_per_s"] = tokens / (layer_us * 1e-6 * n_layers)
     out["sample"] = (f"{sample} tokens, wall clock incl. launch overhead, scaled to {tokens} tokens x {n_layers} layers; "
-                     "single-token launchers looped as the reference does")
+                     "single-token launchers looped from C++ as the reference's forward pass does")
     return out
 
 

@@ -176,6 +176,16 @@ __global__ void embed_gather_scalar_kernel(EmbedArgs a, int q8) {
     }
 }
 
+// One F16 row to f32 and nothing else (the single-token launcher): 64-thread CTAs, one
+// 64-bit load and one 128-bit store per thread, so the row is spread over many SMs.
+__global__ void embed_f16_row_kernel(const uint16_t *__restrict__ row, float *__restrict__ out, int n4) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n4) return;
+    const uint2 h = __ldg(reinterpret_cast<const uint2 *>(row + 4 * i));
+    const float2 lo = f16x2_bits_to_f32(h.x), hi = f16x2_bits_to_f32(h.y);
+    *reinterpret_cast<float4 *>(out + 4 * i) = make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+
 template <bool Q8, bool BULK>
 void launch_vec(const EmbedArgs &a, int64_t n_tokens, cudaStream_t s) {
     const int vpt = ((a.n_embd >> 2) + kThreads - 1) / kThreads;
@@ -204,7 +214,11 @@ void embed_gather_rows(const void *table, int table_dtype, const int32_t *ids, i
         embed_gather_scalar_kernel<<<(unsigned)n_tokens, kThreads, 0, s>>>(a, q8 ? 1 : 0);
         return;
     }
-    if (!q8) {
+    if (!q8 && n_tokens == 1 && !ids && !residual_in && !norm_w && n_replicas == 1) {
+        const int n4 = n_embd >> 2;
+        embed_f16_row_kernel<<<(n4 + 63) / 64, 64, 0, s>>>(
+            static_cast<const uint16_t *>(table) + (int64_t)single_id * n_embd, out_rows, n4);
+    } else if (!q8) {
         launch_vec<false, false>(a, n_tokens, s);
     } else if (aligned16(table) && ((n_embd / 32 * 34) & 15) == 0) {
         launch_vec<true, true>(a, n_tokens, s);    // every row starts on 16 B: bulk copy

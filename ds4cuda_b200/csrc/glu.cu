@@ -120,10 +120,14 @@ void launch_mode(const float *gate, const float *up, const float *weights, float
                  int64_t n_tokens, int k, int n, float clamp, int combine, cudaStream_t s) {
     constexpr int kThreads = 256;
     const bool vec = (n & 3) == 0 && aligned16(gate) && aligned16(up) && aligned16(out);
-    if (!vec) {
-        int64_t blocks = (n_tokens * n + kThreads - 1) / kThreads;
+    // A single decode row (a few thousand elements) is latency-bound: one element per
+    // thread over many small CTAs finishes sooner than four per thread over two CTAs.
+    const bool tiny = n_tokens * (int64_t)n <= 8192;
+    if (!vec || tiny) {
+        const int threads = tiny ? 128 : kThreads;
+        int64_t blocks = (n_tokens * n + threads - 1) / threads;
         if (blocks > 148 * 32) blocks = 148 * 32;
-        swiglu_scalar_kernel<MODE, FAST><<<(unsigned)blocks, kThreads, 0, s>>>(
+        swiglu_scalar_kernel<MODE, FAST><<<(unsigned)blocks, threads, 0, s>>>(
             gate, up, weights, out, n_tokens, k, n, clamp, combine);
         return;
     }

@@ -70,4 +70,28 @@ void ds4ref_hc_post_f32(const float *block_out, const float *residual_hc, const 
     launch_hc_post_f32(block_out, residual_hc, post, comb, out_hc, n_hc, n_embd, S(s));
 }
 
+// ---- per-token loops, issued from C++ the way the reference's forward pass issues them
+// (cuda/forward_batch.cu:264-284 calls the single-token launchers once per token) ----------
+
+void ds4ref_loop_q8_gather_add_norm(const void *blocks, const float *resid, const float *w, float *row,
+                                    float *sum, float *normed, int n_tokens, int n_embd, float eps, void *s) {
+    const int nb = n_embd / 32;
+    for (int t = 0; t < n_tokens; ++t) {
+        launch_dequant_q8_0_to_f32(static_cast<const block_q8_0 *>(blocks) + (size_t)t * nb, row + (size_t)t * n_embd, nb, S(s));
+        launch_add_f32(row + (size_t)t * n_embd, resid + (size_t)t * n_embd, sum + (size_t)t * n_embd, n_embd, S(s));
+        launch_rms_norm_f32(sum + (size_t)t * n_embd, w, normed + (size_t)t * n_embd, n_embd, eps, S(s));
+    }
+}
+void ds4ref_loop_kv_rope_fp8(float *kv, int n_tokens, int head_dim, int n_rot, int il, void *s) {
+    for (int t = 0; t < n_tokens; ++t)
+        launch_tail_rope_yarn_f32(kv + (size_t)t * head_dim, kv + (size_t)t * head_dim, 1, head_dim, n_rot, t, il, S(s));
+    launch_fp8_kv_quantize_round_trip_f32(kv, kv, n_tokens, head_dim, n_rot, S(s));
+}
+void ds4ref_loop_hc_post(const float *block_out, const float *residual_hc, const float *post, const float *comb,
+                         float *out_hc, int n_tokens, int n_embd, void *s) {
+    for (int t = 0; t < n_tokens; ++t)
+        launch_hc_post_f32(block_out, residual_hc + (size_t)t * 4 * n_embd, post, comb,
+                           out_hc + (size_t)t * 4 * n_embd, 4, n_embd, S(s));
+}
+
 }  // extern "C"
