@@ -53,6 +53,7 @@ def parse_args():
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
     ap.add_argument("--graph", type=int, default=1, help="replay the layer chain from a CUDA graph")
     ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--e2e-chunks", type=int, default=8, help="row slices pipelined over H2D / compute / D2H")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU work budget of the baseline sample")
     return ap.parse_args()
@@ -357,13 +358,13 @@ def run_ours(args):
                   for k, (s, d) in out_shapes.items() if k != "kv_tail"}
     h2d = sum(t.numel() * t.element_size() for t in pinned_in.values())
     d2h = sum(t.numel() * t.element_size() for t in pinned_out.values())
-    path.run_host(pinned_in, args.layers, pinned_out)            # warm-up
+    path.run_host(pinned_in, args.layers, pinned_out, n_chunks=args.e2e_chunks)            # warm-up
     torch.cuda.synchronize()
     shard.barrier()
     sampler.under_load = True
     e2e_ms = 0.0
     for _ in range(max(1, args.e2e_steps)):
-        e2e_ms += path.run_host(pinned_in, args.layers, pinned_out)["ms"]
+        e2e_ms += path.run_host(pinned_in, args.layers, pinned_out, n_chunks=args.e2e_chunks)["ms"]
     sampler.under_load = False
     torch.cuda.synchronize()
     shard.barrier()
@@ -395,7 +396,8 @@ def run_ours(args):
         "ops": ops_table, "roofline": roofline, "cpu_baseline": cpu,
         "reference_kernels_sm100a": ref_kernels,
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms_step,
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "pipeline": f"{args.e2e_chunks} row slices over copy-in / compute / copy-out streams"},
         "gpu_launches": launches, "cuda_graph": bool(args.graph), "clocks": clocks,
     }
     print(json.dumps(line), flush=True)

@@ -78,6 +78,7 @@ SIGNATURES = {
     "ds4b200_e4m3_encode_f32": (_I, [_P, _P, _L, _P]),
     "ds4b200_e4m3_decode_f32": (_I, [_P, _P, _L, _P]),
     "ds4b200_e4m3_selfcheck": (_I, [C.c_uint32, C.c_uint64, _P, _P]),
+    "ds4b200_div_selfcheck": (_I, [C.c_uint64, C.c_uint64, _P, _P]),
     # prefill path object (include/ds4b200_path.h)
     "ds4b200_path_create": (_P, [_P]),
     "ds4b200_path_destroy": (None, [_P]),
@@ -87,6 +88,7 @@ SIGNATURES = {
     "ds4b200_path_stream": (_P, [_P]),
     "ds4b200_path_run_device": (_I, [_P, _I]),
     "ds4b200_path_run_host": (_I, [_P, _P, _I, C.POINTER(C.c_float)]),
+    "ds4b200_path_run_host_chunked": (_I, [_P, _P, _I, _I, C.POINTER(C.c_float)]),
     "ds4b200_path_time_device": (_I, [_P, _I, _I, _I, C.POINTER(C.c_float)]),
     "ds4b200_path_profile_ops": (_I, [_P, _I, C.POINTER(C.c_float)]),
     "ds4b200_path_launches_per_run": (_I, [_P, _I]),

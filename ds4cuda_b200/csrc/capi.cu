@@ -241,6 +241,12 @@ int ds4b200_e4m3_decode_f32(const uint8_t *codes, float *x, int64_t n, void *str
     return launched("e4m3_decode");
 }
 
+int ds4b200_div_selfcheck(uint64_t first, uint64_t count, unsigned long long *mismatches, void *stream) {
+    REQUIRE(mismatches, "div_selfcheck: null pointer");
+    ds4b200::div_selfcheck(first, count, mismatches, STREAM(stream));
+    return launched("div_selfcheck");
+}
+
 int ds4b200_e4m3_selfcheck(uint32_t first_bits, uint64_t count, unsigned long long *mismatches,
                            void *stream) {
     REQUIRE(mismatches, "e4m3_selfcheck: null pointer");

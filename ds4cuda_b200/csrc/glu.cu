@@ -31,12 +31,22 @@ __device__ __forceinline__ float glu_one(float g, float u, float clamp) {
     const float den = 1.0f + e;
     if (MODE == DS4B200_GLU_PLAIN) {
         // (g * sigmoid_stable(g)) * u, cuda/glu.cu:56-75
-        const float sg = (g >= 0.0f ? 1.0f : e) / den;
+        const float sg = div_by_1to2(g >= 0.0f ? 1.0f : e, den);
         return (g * sg) * u;
     }
     // s = g/(1+e) or (g*e)/(1+e), then s*u, cuda/moe_iq2_pair.cu:362-372
-    const float s = (g >= 0.0f ? g : g * e) / den;
+    const float s = div_by_1to2(g >= 0.0f ? g : g * e, den);
     return s * u;
+}
+
+// The reference rounds s*u*w to f32 (it is stored to memory) before the slot sum
+// (cuda/moe_iq2_pair.cu:372, cuda/moe_q2k_sum6.cu:159-181): keep the multiply and the add
+// as two roundings in every code path, never one fused multiply-add.
+__device__ __forceinline__ float4 mul4_rn(float4 v, float w) {
+    return make_float4(__fmul_rn(v.x, w), __fmul_rn(v.y, w), __fmul_rn(v.z, w), __fmul_rn(v.w, w));
+}
+__device__ __forceinline__ float4 add4_rn(float4 a, float4 b) {
+    return make_float4(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y), __fadd_rn(a.z, b.z), __fadd_rn(a.w, b.w));
 }
 
 template <int MODE, bool FAST>
@@ -71,9 +81,9 @@ swiglu_vec_kernel(const float *__restrict__ gate, const float *__restrict__ up,
                 float4 v = glu4<MODE, FAST>(g[s], u[s], clamp);
                 if (weights) {
                     const float w = __ldg(weights + t * k + s);
-                    v.x *= w; v.y *= w; v.z *= w; v.w *= w;
+                    v = mul4_rn(v, w);
                 }
-                if (combine) acc = (s == 0) ? v : add4(acc, v);
+                if (combine) acc = (s == 0) ? v : add4_rn(acc, v);
                 else st_stream4(out + 4 * (base + (int64_t)s * n4), v);
             }
             if (combine) st_stream4(out + 4 * gid, acc);
@@ -84,9 +94,9 @@ swiglu_vec_kernel(const float *__restrict__ gate, const float *__restrict__ up,
                                             ld_stream4(up + 4 * (base + (int64_t)s * n4)), clamp);
                 if (weights) {
                     const float w = __ldg(weights + t * k + s);
-                    v.x *= w; v.y *= w; v.z *= w; v.w *= w;
+                    v = mul4_rn(v, w);
                 }
-                if (combine) acc = (s == 0) ? v : add4(acc, v);
+                if (combine) acc = (s == 0) ? v : add4_rn(acc, v);
                 else st_stream4(out + 4 * (base + (int64_t)s * n4), v);
             }
             if (combine) st_stream4(out + 4 * gid, acc);
@@ -107,12 +117,32 @@ __global__ void swiglu_scalar_kernel(const float *gate, const float *up, const f
         for (int s = 0; s < k; ++s) {
             const int64_t idx = (t * k + s) * (int64_t)n + j;
             float v = glu_one<MODE, FAST>(gate[idx], up[idx], clamp);
-            if (weights) v *= weights[t * k + s];
-            if (combine) acc = (s == 0) ? v : acc + v;
+            if (weights) v = __fmul_rn(v, weights[t * k + s]);
+            if (combine) acc = (s == 0) ? v : __fadd_rn(acc, v);
             else out[idx] = v;
         }
         if (combine) out[gid] = acc;
     }
+}
+
+// Counts (n, d) pairs, d in [1, 2], n spread over +-2^-40..2^40 and signs, for which
+// div_by_1to2 differs from the IEEE division.  Pairs come from a counter-based hash.
+__global__ void div_selfcheck_kernel(uint64_t first, uint64_t count, unsigned long long *mismatches) {
+    unsigned bad = 0;
+    for (uint64_t k = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; k < count;
+         k += (uint64_t)gridDim.x * blockDim.x) {
+        uint64_t z = (first + k) * 0x9E3779B97F4A7C15ull;
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+        z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+        z ^= z >> 31;
+        const float d = __uint_as_float(0x3f800000u | (uint32_t)(z & 0x7fffffu));          // [1, 2)
+        const uint32_t ne = 87u + (uint32_t)((z >> 23) % 81u);                               // exponent 2^-40..2^40
+        const float n = __uint_as_float(((uint32_t)(z >> 63) << 31) | (ne << 23) | (uint32_t)((z >> 32) & 0x7fffffu));
+        const float dd = (k & 1023u) == 0 ? 2.0f : d;                                         // include the end point
+        bad += (__float_as_uint(div_by_1to2(n, dd)) != __float_as_uint(n / dd));
+    }
+    bad = __reduce_add_sync(0xffffffffu, bad);
+    if ((threadIdx.x & 31) == 0 && bad) atomicAdd(mismatches, (unsigned long long)bad);
 }
 
 template <int MODE, bool FAST>
@@ -144,6 +174,10 @@ void launch_mode(const float *gate, const float *up, const float *weights, float
 }
 
 }  // namespace
+
+void div_selfcheck(uint64_t first, uint64_t count, unsigned long long *mismatches, cudaStream_t s) {
+    if (count > 0) div_selfcheck_kernel<<<148 * 16, 256, 0, s>>>(first, count, mismatches);
+}
 
 void swiglu_rows(const float *gate, const float *up, const float *weights, float *out,
                  int64_t n_tokens, int k, int n, int mode, float clamp, int combine,

@@ -65,6 +65,7 @@ void hc_post_rows(const float *block_out, const float *block_out2, const float *
                   float *out_hc, int64_t n_tokens, int n_embd, int iters, float eps,
                   cudaStream_t s);
 
+void div_selfcheck(uint64_t first, uint64_t count, unsigned long long *mismatches, cudaStream_t s);
 void e4m3_encode(const float *x, uint8_t *codes, int64_t n, cudaStream_t s);
 void e4m3_decode(const uint8_t *codes, float *x, int64_t n, cudaStream_t s);
 void e4m3_selfcheck(uint32_t first_bits, uint64_t count, unsigned long long *mismatches,

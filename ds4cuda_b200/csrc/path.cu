@@ -31,6 +31,8 @@ struct ds4b200_path {
     float *gather_scratch = nullptr;   // [T][kv_dim] rows gathered from the cache for D2H
     cudaStream_t side = nullptr;       // the Sinkhorn rows run here, beside the other ops
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;   // chunked host calls: H2D / D2H beside compute
+    std::vector<cudaEvent_t> chunk_events;
     // graph cache (one per layer count)
     std::map<int, cudaGraphExec_t> graphs;
     std::vector<cudaEvent_t> events;
@@ -76,39 +78,48 @@ float *hc_in(ds4b200_path *p, int layer) { return (layer & 1) ? p->hc_b : p->hc_
 float *hc_out(ds4b200_path *p, int layer) { return (layer & 1) ? p->hc_a : p->hc_b; }
 
 // The launches of one layer.  `op` < 0 runs all of them, with the Sinkhorn rows
-// (which depend only on the logits) forked onto the side stream so that their
-// serial chains of divisions overlap the three streaming kernels before the mix.
+// (which depend only on the logits) and the KV store (10 MB, launch-bound) forked
+// onto the side stream so that they overlap the streaming kernels before the mix.
 // `op` >= 0 runs one kernel alone on the main stream (profiling).
-void enqueue_layer(ds4b200_path *p, int layer, int op) {
+void enqueue_layer(ds4b200_path *p, int layer, int op, int64_t t0 = 0, int64_t n = -1) {
     const ds4b200_path_config &c = p->cfg;
-    const int64_t T = c.n_tokens;
+    const int64_t T = n < 0 ? c.n_tokens : n;          // rows [t0, t0 + T)
     cudaStream_t s = p->stream;
-    if (op < 0) {
-        cudaEventRecord(p->ev_fork, s);
-        cudaStreamWaitEvent(p->side, p->ev_fork, 0);
-        ds4b200::hc_sinkhorn_rows(p->hc_logits, p->comb, T, c.sinkhorn_iters, c.eps, p->side);
-        cudaEventRecord(p->ev_join, p->side);
-    }
-    if (op == 4) ds4b200::hc_sinkhorn_rows(p->hc_logits, p->comb, T, c.sinkhorn_iters, c.eps, s);
-    if (op < 0 || op == 0)
-        ds4b200::embed_gather_rows(p->table, c.table_dtype, p->ids, 0, T, c.n_embd, p->residual,
-                                   p->norm_w, c.eps, p->residual_out, 1, nullptr, p->normed_bf16, s);
-    if (op < 0 || op == 1) {
+    const int64_t E = c.n_embd;
+    float *comb = p->comb + t0 * 16;
+    const float *logits = p->hc_logits + t0 * 16;
+    auto kvstore = [&](cudaStream_t st) {
         const int64_t l = layer % c.max_layers;
-        ds4b200::rope_fp8_store_rows(p->kv, T, c.kv_dim, c.n_rot, p->pos, &c.rope, nullptr, c.eps,
-                                     c.fp8_scale_mode, p->pos,
+        ds4b200::rope_fp8_store_rows(p->kv + t0 * c.kv_dim, T, c.kv_dim, c.n_rot, p->pos + t0, &c.rope, nullptr,
+                                     c.eps, c.fp8_scale_mode, p->pos + t0,
                                      p->kv_codes + l * (int64_t)c.n_slots * c.kv_dim,
                                      p->kv_scales + l * (int64_t)c.n_slots * p->n_scales,
                                      p->kv_tail ? p->kv_tail + l * (int64_t)c.n_slots * c.n_rot : nullptr,
-                                     nullptr, s);
+                                     nullptr, st);
+    };
+    if (op < 0) {
+        // side stream: the two small latency-bound kernels (Sinkhorn rows, KV store); they
+        // share no buffer with the streaming kernels on the main stream
+        cudaEventRecord(p->ev_fork, s);
+        cudaStreamWaitEvent(p->side, p->ev_fork, 0);
+        ds4b200::hc_sinkhorn_rows(logits, comb, T, c.sinkhorn_iters, c.eps, p->side);
+        kvstore(p->side);
+        cudaEventRecord(p->ev_join, p->side);
     }
+    if (op == 4) ds4b200::hc_sinkhorn_rows(logits, comb, T, c.sinkhorn_iters, c.eps, s);
+    if (op == 1) kvstore(s);
+    if (op < 0 || op == 0)
+        ds4b200::embed_gather_rows(p->table, c.table_dtype, p->ids + t0, 0, T, c.n_embd, p->residual + t0 * E,
+                                   p->norm_w, c.eps, p->residual_out + t0 * E, 1, nullptr,
+                                   p->normed_bf16 + t0 * E, s);
     if (op < 0 || op == 2)
-        ds4b200::swiglu_rows(p->gate, p->up, p->router_w, p->ffn_out, T, c.top_k, c.ff_dim,
+        ds4b200::swiglu_rows(p->gate + t0 * c.top_k * c.ff_dim, p->up + t0 * c.top_k * c.ff_dim,
+                             p->router_w + t0 * c.top_k, p->ffn_out + t0 * c.ff_dim, T, c.top_k, c.ff_dim,
                              c.glu_mode, c.clamp, 1, c.glu_fast_exp, s);
     if (op < 0) cudaStreamWaitEvent(s, p->ev_join, 0);
     if (op < 0 || op == 3)
-        ds4b200::hc_post_rows(nullptr, nullptr, hc_in(p, layer), nullptr, p->comb, nullptr, nullptr,
-                              hc_out(p, layer), T, c.n_embd, 0, 0.0f, s);
+        ds4b200::hc_post_rows(nullptr, nullptr, hc_in(p, layer) + t0 * 4 * E, nullptr, comb, nullptr, nullptr,
+                              hc_out(p, layer) + t0 * 4 * E, T, c.n_embd, 0, 0.0f, s);
 }
 
 int enqueue_run(ds4b200_path *p, int n_layers) {
@@ -184,6 +195,8 @@ ds4b200_path *ds4b200_path_create(const ds4b200_path_config *cfg) {
     const int64_t T = c.n_tokens, L = c.max_layers;
     bool good = cudaStreamCreateWithFlags(&p->stream, cudaStreamNonBlocking) == cudaSuccess &&
                 cudaStreamCreateWithFlags(&p->side, cudaStreamNonBlocking) == cudaSuccess &&
+                cudaStreamCreateWithFlags(&p->copy_in, cudaStreamNonBlocking) == cudaSuccess &&
+                cudaStreamCreateWithFlags(&p->copy_out, cudaStreamNonBlocking) == cudaSuccess &&
                 cudaEventCreateWithFlags(&p->ev_fork, cudaEventDisableTiming) == cudaSuccess &&
                 cudaEventCreateWithFlags(&p->ev_join, cudaEventDisableTiming) == cudaSuccess;
     if (!good) set_error(-EIO, "path_create: cudaStreamCreate failed");
@@ -223,6 +236,9 @@ void ds4b200_path_destroy(ds4b200_path *p) {
     if (p->ev_fork) cudaEventDestroy(p->ev_fork);
     if (p->ev_join) cudaEventDestroy(p->ev_join);
     if (p->side) cudaStreamDestroy(p->side);
+    for (cudaEvent_t e : p->chunk_events) cudaEventDestroy(e);
+    if (p->copy_in) { cudaStreamSynchronize(p->copy_in); cudaStreamDestroy(p->copy_in); }
+    if (p->copy_out) { cudaStreamSynchronize(p->copy_out); cudaStreamDestroy(p->copy_out); }
     for (cudaEvent_t e : p->events) cudaEventDestroy(e);
     for (void *d : p->owned) cudaFree(d);
     if (p->stream) cudaStreamDestroy(p->stream);
@@ -300,6 +316,90 @@ int ds4b200_path_run_host(ds4b200_path *p, const ds4b200_path_io *h, int n_layer
     CUDA_OK(cudaEventRecord(p->events[1], s), "path_run_host: event");
     CUDA_OK(cudaStreamSynchronize(s), "path_run_host: sync");
     if (ms) CUDA_OK(cudaEventElapsedTime(ms, p->events[0], p->events[1]), "path_run_host: elapsed");
+    return 0;
+}
+
+int ds4b200_path_run_host_chunked(ds4b200_path *p, const ds4b200_path_io *h, int n_layers, int n_chunks,
+                                  float *ms) {
+    if (!p || !h || n_layers < 1 || n_chunks < 1) return set_error(-EINVAL, "path_run_host_chunked: bad argument");
+    const ds4b200_path_config &c = p->cfg;
+    const int64_t T = c.n_tokens, E = c.n_embd;
+    if (n_chunks > T) n_chunks = (int)T;
+    if (int rc = ensure_events(p, 2)) return rc;
+    while (p->chunk_events.size() < (size_t)2 * n_chunks + 1) {
+        cudaEvent_t e;
+        CUDA_OK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreate");
+        p->chunk_events.push_back(e);
+    }
+    cudaStream_t s = p->stream, in = p->copy_in, out = p->copy_out;
+    CUDA_OK(cudaEventRecord(p->events[0], s), "path_run_host_chunked: event");
+    CUDA_OK(cudaStreamWaitEvent(in, p->events[0], 0), "path_run_host_chunked: wait");
+    CUDA_OK(cudaStreamWaitEvent(out, p->events[0], 0), "path_run_host_chunked: wait");
+    const int last = n_layers - 1;
+    const int64_t l = last % c.max_layers;
+    uint8_t *scratch = reinterpret_cast<uint8_t *>(p->gather_scratch);
+#define H2D(dev, host, off, cnt, esz) \
+    if (host) CUDA_OK(cudaMemcpyAsync((char *)(dev) + (off) * (esz), (const char *)(host) + (off) * (esz), \
+                                      (size_t)((cnt) * (esz)), cudaMemcpyHostToDevice, in), "path_run_host_chunked: H2D")
+#define D2H(host, dev, off, cnt, esz) \
+    if (host) CUDA_OK(cudaMemcpyAsync((char *)(host) + (off) * (esz), (const char *)(dev) + (off) * (esz), \
+                                      (size_t)((cnt) * (esz)), cudaMemcpyDeviceToHost, out), "path_run_host_chunked: D2H")
+    for (int k = 0; k < n_chunks; ++k) {
+        const int64_t t0 = T * k / n_chunks, n = T * (k + 1) / n_chunks - t0;
+        cudaEvent_t in_ready = p->chunk_events[2 * k], done = p->chunk_events[2 * k + 1];
+        // ---- inputs of this chunk, on the copy-in stream
+        if (k == 0) H2D(p->norm_w, h->norm_w, 0, E, 4);
+        H2D(p->ids, h->ids, t0, n, 4);
+        H2D(p->pos, h->pos, t0, n, 4);
+        H2D(p->residual, h->residual, t0 * E, n * E, 4);
+        H2D(p->kv, h->kv, t0 * c.kv_dim, n * c.kv_dim, 4);
+        H2D(p->gate, h->gate, t0 * c.top_k * c.ff_dim, n * c.top_k * c.ff_dim, 4);
+        H2D(p->up, h->up, t0 * c.top_k * c.ff_dim, n * c.top_k * c.ff_dim, 4);
+        H2D(p->router_w, h->router_w, t0 * c.top_k, n * c.top_k, 4);
+        H2D(p->hc_logits, h->hc_logits, t0 * 16, n * 16, 4);
+        H2D(p->hc_a, h->hc_resid, t0 * 4 * E, n * 4 * E, 4);
+        CUDA_OK(cudaEventRecord(in_ready, in), "path_run_host_chunked: event");
+        // ---- the layer chain over this chunk's rows
+        CUDA_OK(cudaStreamWaitEvent(s, in_ready, 0), "path_run_host_chunked: wait");
+        for (int layer = 0; layer < n_layers; ++layer) enqueue_layer(p, layer, -1, t0, n);
+        CUDA_OK(cudaGetLastError(), "path_run_host_chunked: launch");
+        CUDA_OK(cudaEventRecord(done, s), "path_run_host_chunked: event");
+        // ---- outputs of this chunk, on the copy-out stream
+        CUDA_OK(cudaStreamWaitEvent(out, done, 0), "path_run_host_chunked: wait");
+        D2H(h->residual_out, p->residual_out, t0 * E, n * E, 4);
+        D2H(h->normed_bf16, p->normed_bf16, t0 * E, n * E, 2);
+        D2H(h->ffn_out, p->ffn_out, t0 * c.ff_dim, n * c.ff_dim, 4);
+        D2H(h->hc_out, hc_out(p, last), t0 * 4 * E, n * 4 * E, 4);
+        if (h->kv_codes) {
+            gather_rows_kernel<<<(unsigned)n, 128, 0, out>>>(p->kv_codes + l * (int64_t)c.n_slots * c.kv_dim,
+                                                             p->pos + t0, scratch, c.kv_dim, n);
+            CUDA_OK(cudaMemcpyAsync(h->kv_codes + t0 * c.kv_dim, scratch, (size_t)(n * c.kv_dim),
+                                    cudaMemcpyDeviceToHost, out), "path_run_host_chunked: D2H");
+        }
+        if (h->kv_scales) {
+            gather_rows_kernel<<<(unsigned)n, 32, 0, out>>>(
+                reinterpret_cast<uint8_t *>(p->kv_scales + l * (int64_t)c.n_slots * p->n_scales), p->pos + t0,
+                scratch, p->n_scales * 4, n);
+            CUDA_OK(cudaMemcpyAsync(h->kv_scales + t0 * p->n_scales, scratch, (size_t)(n * p->n_scales * 4),
+                                    cudaMemcpyDeviceToHost, out), "path_run_host_chunked: D2H");
+        }
+        if (h->kv_tail && p->kv_tail) {
+            gather_rows_kernel<<<(unsigned)n, 64, 0, out>>>(
+                reinterpret_cast<uint8_t *>(p->kv_tail + l * (int64_t)c.n_slots * c.n_rot), p->pos + t0, scratch,
+                c.n_rot * 4, n);
+            CUDA_OK(cudaMemcpyAsync(h->kv_tail + t0 * c.n_rot, scratch, (size_t)(n * c.n_rot * 4),
+                                    cudaMemcpyDeviceToHost, out), "path_run_host_chunked: D2H");
+        }
+    }
+#undef H2D
+#undef D2H
+    // join: the main stream waits for the last copy-out, then closes the timed region
+    cudaEvent_t all_out = p->chunk_events[2 * n_chunks];
+    CUDA_OK(cudaEventRecord(all_out, out), "path_run_host_chunked: event");
+    CUDA_OK(cudaStreamWaitEvent(s, all_out, 0), "path_run_host_chunked: wait");
+    CUDA_OK(cudaEventRecord(p->events[1], s), "path_run_host_chunked: event");
+    CUDA_OK(cudaStreamSynchronize(s), "path_run_host_chunked: sync");
+    if (ms) CUDA_OK(cudaEventElapsedTime(ms, p->events[0], p->events[1]), "path_run_host_chunked: elapsed");
     return 0;
 }
 

@@ -19,7 +19,7 @@ __all__ = [
     "TABLE_F16", "TABLE_Q8_0", "RopeParams", "rope_params_for_layer", "rope_params_explicit",
     "add", "rms_norm_rows", "embed_gather_rows", "rope_rows", "fp8_kv_round_trip_rows",
     "rope_fp8_store_rows", "swiglu_rows", "hc_pre_rows", "hc_post_rows", "hc_sinkhorn_rows", "hc_sinkhorn_mix_rows",
-    "e4m3_encode", "e4m3_decode", "e4m3_selfcheck", "device_status",
+    "e4m3_encode", "e4m3_decode", "e4m3_selfcheck", "div_selfcheck", "device_status",
 ]
 
 
@@ -174,4 +174,11 @@ def e4m3_selfcheck(first_bits: int, count: int) -> int:
     """Number of f32 bit patterns in the range whose hardware code differs from the table rule."""
     bad = torch.zeros(1, dtype=torch.int64, device="cuda")
     check(_lib.load().ds4b200_e4m3_selfcheck(first_bits, count, _p(bad), _s()))
+    return int(bad.item())
+
+
+def div_selfcheck(first: int, count: int) -> int:
+    """Pairs (n, d in [1, 2]) for which the kernels' branch-free division differs from n / d."""
+    bad = torch.zeros(1, dtype=torch.int64, device="cuda")
+    check(_lib.load().ds4b200_div_selfcheck(first, count, _p(bad), _s()))
     return int(bad.item())

@@ -76,15 +76,19 @@ class PrefillPath:
                 "kv_tail": ((T, c.n_rot), np.float32), "ffn_out": ((T, c.ff_dim), np.float32),
                 "hc_out": ((T, 4, c.n_embd), np.float32)}
 
-    def run_host(self, inputs: dict, n_layers: int, outputs: dict | None = None) -> dict:
-        """One end-to-end call on host arrays (numpy, or pinned torch tensors)."""
+    def run_host(self, inputs: dict, n_layers: int, outputs: dict | None = None, n_chunks: int = 1) -> dict:
+        """One end-to-end call on host arrays (numpy, or pinned torch tensors).
+        n_chunks > 1 pipelines copy-in, compute and copy-out over row slices."""
         keep = {k: (v if hasattr(v, "data_ptr") else np.ascontiguousarray(v)) for k, v in inputs.items()}
         if outputs is None:
             outputs = {k: np.empty(s, dtype=d) for k, (s, d) in self.output_shapes().items()
                        if k != "kv_tail" or self.cfg.fp8_scale_mode == _lib.FP8_BLOCK64_POW2}
         io = self._io({**keep, **outputs})
         ms = C.c_float()
-        check(self.lib.ds4b200_path_run_host(self.handle, C.byref(io), n_layers, C.byref(ms)))
+        if n_chunks > 1:
+            check(self.lib.ds4b200_path_run_host_chunked(self.handle, C.byref(io), n_layers, n_chunks, C.byref(ms)))
+        else:
+            check(self.lib.ds4b200_path_run_host(self.handle, C.byref(io), n_layers, C.byref(ms)))
         res = dict(outputs)
         res["ms"] = ms.value
         return res

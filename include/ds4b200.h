@@ -246,6 +246,12 @@ int ds4b200_e4m3_decode_f32(const uint8_t *codes, float *x, int64_t n, void *str
 int ds4b200_e4m3_selfcheck(uint32_t first_bits, uint64_t count,
                            unsigned long long *mismatches, void *stream);
 
+/* Counts, over `count` hashed (n, d) pairs with d in [1, 2], the pairs for which the
+ * branch-free division the SwiGLU kernels use differs from the IEEE quotient n / d.
+ * *mismatches is a device uint64 the caller zeroes. */
+int ds4b200_div_selfcheck(uint64_t first, uint64_t count, unsigned long long *mismatches,
+                          void *stream);
+
 #ifdef __cplusplus
 }
 #endif

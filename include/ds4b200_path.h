@@ -98,6 +98,13 @@ int ds4b200_path_run_device(ds4b200_path *p, int n_layers);
  * n_layers, copy the non-NULL outputs out, wait.  *ms (nullable) receives the
  * device time of the whole call measured with events on the path's stream. */
 int ds4b200_path_run_host(ds4b200_path *p, const ds4b200_path_io *host, int n_layers, float *ms);
+/* The same end-to-end call with the token rows cut into n_chunks slices that are
+ * pipelined over three streams: while slice k runs the layer chain, slice k+1 is
+ * copied in and slice k-1 is copied out (PCIe is full duplex).  Every row is
+ * independent, so results equal ds4b200_path_run_host.  Launches are issued
+ * eagerly (no graph).  The pos/slot values of different slices must not collide. */
+int ds4b200_path_run_host_chunked(ds4b200_path *p, const ds4b200_path_io *host, int n_layers,
+                                  int n_chunks, float *ms);
 /* Time `steps` back-to-back device runs after `warmup` untimed ones, with
  * events on the path's stream.  *ms_total = time of all timed steps. */
 int ds4b200_path_time_device(ds4b200_path *p, int n_layers, int warmup, int steps, float *ms_total);

@@ -421,6 +421,11 @@ def test_swiglu_rows(ops, oracle, mode, k, n):
     assert_close(host(fast), oracle.swiglu_rows(gate, up, w, om, 10.0, True), what="fast-exp variant")
 
 
+def test_swiglu_division_is_the_ieee_quotient(ops):
+    # 2^31 hashed (numerator, divisor in [1, 2]) pairs: the branch-free division must give n / d bit for bit
+    assert ops.div_selfcheck(0, 1 << 31) == 0
+
+
 def test_silu_mul_drop_in_and_reference_kernel(ops, oracle, ref):
     from ds4cuda_b200 import _lib
     L = _lib.load()

@@ -63,6 +63,10 @@ def test_path_run_host_matches_oracle(ops, oracle, scale_mode, use_graph):
     again = path.run_host(x, n_layers)
     for k in ("residual_out", "normed_bf16", "kv_codes", "kv_scales", "ffn_out", "hc_out"):
         assert_bits(again[k], out[k], k)
+    # row slices pipelined over copy-in / compute / copy-out streams: same bits
+    chunked = path.run_host(x, n_layers, n_chunks=3)
+    for k in ("residual_out", "normed_bf16", "kv_codes", "kv_scales", "ffn_out", "hc_out"):
+        assert_bits(chunked[k], out[k], "chunked " + k)
     ms = path.time_device(n_layers, warmup=1, steps=2)
     per_kernel = path.profile_ops(3)
     assert ms > 0 and len(per_kernel) == 5 and all(v > 0 for v in per_kernel.values())
