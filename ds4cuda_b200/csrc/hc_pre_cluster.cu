@@ -60,8 +60,9 @@ __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
 }
 
 // C: CTAs per cluster.  VC: float2 columns per thread per stream
-// (n_embd = C * VC * 512).  M: tokens processed together.
-template <int C, int VC, int M>
+// (n_embd = C * VC * 512).  M: tokens held in registers together.  S: sub-batches of M
+// tokens per exchange over the cluster.
+template <int C, int VC, int M, int S>
 __global__ void __launch_bounds__(kThreads, 1)
 hc_pre_cluster_kernel(const float *__restrict__ residual_hc, const uint16_t *__restrict__ hc_fn,
                       const float *__restrict__ hc_scale, const float *__restrict__ hc_base,
@@ -70,10 +71,10 @@ hc_pre_cluster_kernel(const float *__restrict__ residual_hc, const uint16_t *__r
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int kWPairs = (kMixN / 2) * 4 * VC * 2 * kThreads;       // float2 {row 2p, row 2p+1} entries
     float2 *w_s = reinterpret_cast<float2 *>(smem_raw);
-    float *part = reinterpret_cast<float *>(w_s + kWPairs);            // [kWarps][M*32]
-    float *cl_part = part + kWarps * M * kSlots;                       // [2][C][M*32]
-    float *tot = cl_part + 2 * C * M * kSlots;                         // [M*32]
-    float *pre_s = tot + M * kSlots;                                   // [M][4]
+    float *part = reinterpret_cast<float *>(w_s + kWPairs);            // [kWarps][S*M][32]
+    float *cl_part = part + kWarps * S * M * kSlots;                   // [C][S*M][32]
+    float *tot = cl_part + C * S * M * kSlots;                         // [S*M][32]
+    float *pre_s = tot + S * M * kSlots;                               // [S*M][4]
 
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank();
@@ -98,101 +99,113 @@ hc_pre_cluster_kernel(const float *__restrict__ residual_hc, const uint16_t *__r
             }
     __syncthreads();
 
-    const int64_t n_groups = (n_tokens + M - 1) / M;
+    // A super-group is S sub-batches of M tokens: the dot products run sub-batch by
+    // sub-batch (registers hold M tokens), the exchange over the cluster and its barriers
+    // happen once per super-group, and the weighted sum re-reads the rows, which are then
+    // still in L2 (G * 64 KiB per cluster).
+    constexpr int G = S * M;
+    const int64_t n_super = (n_tokens + G - 1) / G;
+    const int64_t n_sub = n_super * S;                                  // sub-batch index q covers tokens q*M..
+    auto x_ptr = [&](int64_t t, int h, int v) {
+        return reinterpret_cast<const float2 *>(residual_hc + t * hc_dim + (int64_t)h * n_embd + col0 +
+                                                2 * (v * kThreads + tid));
+    };
     float2 xn[M][4][VC];
-    auto load_group = [&](int64_t g) {
+    auto load_sub = [&](int64_t q) {
 #pragma unroll
         for (int m = 0; m < M; ++m) {
-            const int64_t t = g * M + m;
+            const int64_t t = q * M + m;
 #pragma unroll
             for (int h = 0; h < 4; ++h)
 #pragma unroll
                 for (int v = 0; v < VC; ++v)
-                    xn[m][h][v] = (t < n_tokens)
-                        ? __ldcs(reinterpret_cast<const float2 *>(residual_hc + t * hc_dim + (int64_t)h * n_embd +
-                                                                   col0 + 2 * (v * kThreads + tid)))
-                        : make_float2(0.f, 0.f);
+                    xn[m][h][v] = (t < n_tokens) ? __ldg(x_ptr(t, h, v)) : make_float2(0.f, 0.f);
         }
     };
-    if (cluster_id < n_groups) load_group(cluster_id);
+    if (cluster_id < n_super) load_sub(cluster_id * S);
 
-    int buf = 0;
-    for (int64_t g = cluster_id; g < n_groups; g += n_clusters, buf ^= 1) {
-        float2 x[M][4][VC];
+    for (int64_t sg = cluster_id; sg < n_super; sg += n_clusters) {
+#pragma unroll 1
+        for (int sb = 0; sb < S; ++sb) {
+            float2 x[M][4][VC];
 #pragma unroll
-        for (int m = 0; m < M; ++m)
+            for (int m = 0; m < M; ++m)
+#pragma unroll
+                for (int h = 0; h < 4; ++h)
+#pragma unroll
+                    for (int v = 0; v < VC; ++v) x[m][h][v] = xn[m][h][v];
+            // the next sub-batch's loads fly during the math
+            const int64_t q_next = (sb + 1 < S) ? sg * S + sb + 1 : (sg + n_clusters) * S;
+            if (q_next < n_sub) load_sub(q_next);
+
+            // ---- this thread's partial sums: pair p of token m holds rows 2p and 2p+1
+            float2 acc2[M][kMixN / 2];
+            float ss[M];
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                ss[m] = 0.0f;
+#pragma unroll
+                for (int p = 0; p < kMixN / 2; ++p) acc2[m][p] = make_float2(0.f, 0.f);
+            }
 #pragma unroll
             for (int h = 0; h < 4; ++h)
 #pragma unroll
-                for (int v = 0; v < VC; ++v) x[m][h][v] = xn[m][h][v];
-        if (g + n_clusters < n_groups) load_group(g + n_clusters);     // next group's loads fly during the math
-
-        // ---- this thread's partial sums: pair p of token m holds rows 2p and 2p+1
-        float2 acc2[M][kMixN / 2];
-        float ss[M];
-#pragma unroll
-        for (int m = 0; m < M; ++m) {
-            ss[m] = 0.0f;
-#pragma unroll
-            for (int p = 0; p < kMixN / 2; ++p) acc2[m][p] = make_float2(0.f, 0.f);
-        }
-#pragma unroll
-        for (int h = 0; h < 4; ++h)
-#pragma unroll
-            for (int v = 0; v < VC; ++v) {
-                float2 xx[M], xy[M];
-#pragma unroll
-                for (int m = 0; m < M; ++m) {
-                    xx[m] = make_float2(x[m][h][v].x, x[m][h][v].x);
-                    xy[m] = make_float2(x[m][h][v].y, x[m][h][v].y);
-                    ss[m] += x[m][h][v].x * x[m][h][v].x + x[m][h][v].y * x[m][h][v].y;
-                }
-#pragma unroll
-                for (int p = 0; p < kMixN / 2; ++p) {
-                    const float2 w0 = w_s[(((p * 4 + h) * VC + v) * 2 + 0) * kThreads + tid];
-                    const float2 w1 = w_s[(((p * 4 + h) * VC + v) * 2 + 1) * kThreads + tid];
+                for (int v = 0; v < VC; ++v) {
+                    float2 xx[M], xy[M];
 #pragma unroll
                     for (int m = 0; m < M; ++m) {
-                        acc2[m][p] = ffma2(w0, xx[m], acc2[m][p]);
-                        acc2[m][p] = ffma2(w1, xy[m], acc2[m][p]);
+                        xx[m] = make_float2(x[m][h][v].x, x[m][h][v].x);
+                        xy[m] = make_float2(x[m][h][v].y, x[m][h][v].y);
+                        ss[m] += x[m][h][v].x * x[m][h][v].x + x[m][h][v].y * x[m][h][v].y;
+                    }
+#pragma unroll
+                    for (int p = 0; p < kMixN / 2; ++p) {
+                        const float2 w0 = w_s[(((p * 4 + h) * VC + v) * 2 + 0) * kThreads + tid];
+                        const float2 w1 = w_s[(((p * 4 + h) * VC + v) * 2 + 1) * kThreads + tid];
+#pragma unroll
+                        for (int m = 0; m < M; ++m) {
+                            acc2[m][p] = ffma2(w0, xx[m], acc2[m][p]);
+                            acc2[m][p] = ffma2(w1, xy[m], acc2[m][p]);
+                        }
                     }
                 }
+            float acc[M][kSlots];
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+#pragma unroll
+                for (int p = 0; p < kMixN / 2; ++p) { acc[m][2 * p] = acc2[m][p].x; acc[m][2 * p + 1] = acc2[m][p].y; }
+                acc[m][kMixN] = ss[m];
+#pragma unroll
+                for (int k = kMixN + 1; k < kSlots; ++k) acc[m][k] = 0.0f;
             }
-        float acc[M][kSlots];
 #pragma unroll
-        for (int m = 0; m < M; ++m) {
-#pragma unroll
-            for (int p = 0; p < kMixN / 2; ++p) { acc[m][2 * p] = acc2[m][p].x; acc[m][2 * p + 1] = acc2[m][p].y; }
-            acc[m][kMixN] = ss[m];
-#pragma unroll
-            for (int k = kMixN + 1; k < kSlots; ++k) acc[m][k] = 0.0f;
+            for (int m = 0; m < M; ++m)
+                part[(warp * G + sb * M + m) * kSlots + lane] = warp_transpose_sum32(acc[m]);
         }
-
-        // ---- CTA reduction, then exchange with the other CTAs of the cluster
-#pragma unroll
-        for (int m = 0; m < M; ++m) part[warp * M * kSlots + m * kSlots + lane] = warp_transpose_sum32(acc[m]);
         __syncthreads();
-        if (tid < M * kSlots) {
+
+        // ---- CTA totals, pushed into every CTA of the cluster over DSMEM
+        for (int i = tid; i < G * kSlots; i += kThreads) {
             float s = 0.0f;
 #pragma unroll
-            for (int w = 0; w < kWarps; ++w) s += part[w * M * kSlots + tid];
-            float *mine = cl_part + (buf * C + rank) * M * kSlots + tid;
+            for (int w = 0; w < kWarps; ++w) s += part[w * G * kSlots + i];
+            float *mine = cl_part + rank * G * kSlots + i;
 #pragma unroll
             for (int r = 0; r < C; ++r) *cluster.map_shared_rank(mine, r) = s;
         }
         cluster.sync();
-        if (tid < M * kSlots) {
+        for (int i = tid; i < G * kSlots; i += kThreads) {
             float s = 0.0f;
 #pragma unroll
-            for (int r = 0; r < C; ++r) s += cl_part[(buf * C + r) * M * kSlots + tid];   // same order everywhere
-            tot[tid] = s;
+            for (int r = 0; r < C; ++r) s += cl_part[r * G * kSlots + i];          // same order everywhere
+            tot[i] = s;
         }
         __syncthreads();
 
         // ---- gates (every CTA, identical results); rank 0 writes the small outputs
-        if (tid < 4 * M) {
-            const int m = tid >> 2, h = tid & 3;
-            const int64_t t = g * M + m;
+        for (int i = tid; i < 4 * G; i += kThreads) {
+            const int m = i >> 2, h = i & 3;
+            const int64_t t = sg * G + m;
             const float rms = rms_scale(tot[m * kSlots + kMixN], (float)hc_dim, eps);
             const float zp = (tot[m * kSlots + h] * rms) * hc_scale[0] + hc_base[h];
             pre_s[m * 4 + h] = 1.0f / (1.0f + expf(-zp)) + eps;
@@ -200,45 +213,62 @@ hc_pre_cluster_kernel(const float *__restrict__ residual_hc, const uint16_t *__r
                 const float zq = (tot[m * kSlots + 4 + h] * rms) * hc_scale[1] + hc_base[4 + h];
                 post_out[t * 4 + h] = 2.0f / (1.0f + expf(-zq));
             }
-        } else if (rank == 0 && tid >= 64 && tid < 64 + 16 * M) {
-            const int m = (tid - 64) >> 4, i = (tid - 64) & 15;
-            const int64_t t = g * M + m;
-            if (t < n_tokens) {
-                const float rms = rms_scale(tot[m * kSlots + kMixN], (float)hc_dim, eps);
-                comb_out[t * 16 + i] = (tot[m * kSlots + 8 + i] * rms) * hc_scale[2] + hc_base[8 + i];
+        }
+        if (rank == 0) {
+            for (int i = tid; i < 16 * G; i += kThreads) {
+                const int m = i >> 4, k = i & 15;
+                const int64_t t = sg * G + m;
+                if (t < n_tokens) {
+                    const float rms = rms_scale(tot[m * kSlots + kMixN], (float)hc_dim, eps);
+                    comb_out[t * 16 + k] = (tot[m * kSlots + 8 + k] * rms) * hc_scale[2] + hc_base[8 + k];
+                }
             }
         }
         __syncthreads();
 
-        // ---- weighted stream sum for this CTA's columns
+        // ---- weighted stream sum for this CTA's columns; the rows come back from L2
+#pragma unroll 1
+        for (int m0 = 0; m0 < G; m0 += M) {
+            float2 xr[M][4][VC];
 #pragma unroll
-        for (int m = 0; m < M; ++m) {
-            const int64_t t = g * M + m;
-            if (t >= n_tokens) continue;
-            const float p0 = pre_s[m * 4], p1 = pre_s[m * 4 + 1], p2 = pre_s[m * 4 + 2], p3 = pre_s[m * 4 + 3];
+            for (int m = 0; m < M; ++m) {
+                const int64_t t = sg * G + m0 + m;
 #pragma unroll
-            for (int v = 0; v < VC; ++v) {
-                float2 o2;
-                o2.x = x[m][0][v].x * p0 + x[m][1][v].x * p1 + x[m][2][v].x * p2 + x[m][3][v].x * p3;
-                o2.y = x[m][0][v].y * p0 + x[m][1][v].y * p1 + x[m][2][v].y * p2 + x[m][3][v].y * p3;
-                __stcs(reinterpret_cast<float2 *>(out + t * n_embd + col0 + 2 * (v * kThreads + tid)), o2);
+                for (int h = 0; h < 4; ++h)
+#pragma unroll
+                    for (int v = 0; v < VC; ++v)
+                        xr[m][h][v] = (t < n_tokens) ? __ldcs(x_ptr(t, h, v)) : make_float2(0.f, 0.f);
+            }
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                const int64_t t = sg * G + m0 + m;
+                if (t >= n_tokens) continue;
+                const float *pm = pre_s + (m0 + m) * 4;
+                const float p0 = pm[0], p1 = pm[1], p2 = pm[2], p3 = pm[3];
+#pragma unroll
+                for (int v = 0; v < VC; ++v) {
+                    float2 o2;
+                    o2.x = xr[m][0][v].x * p0 + xr[m][1][v].x * p1 + xr[m][2][v].x * p2 + xr[m][3][v].x * p3;
+                    o2.y = xr[m][0][v].y * p0 + xr[m][1][v].y * p1 + xr[m][2][v].y * p2 + xr[m][3][v].y * p3;
+                    __stcs(reinterpret_cast<float2 *>(out + t * n_embd + col0 + 2 * (v * kThreads + tid)), o2);
+                }
             }
         }
+        cluster.sync();     // cl_part is reused by the next super-group; also the exit barrier
     }
-    cluster.sync();     // nobody leaves while a neighbour may still address its shared memory
 }
 
-template <int C, int VC, int M>
+template <int C, int VC, int M, int S>
 size_t smem_bytes() {
     return sizeof(float2) * (kMixN / 2) * 4 * VC * 2 * kThreads +
-           sizeof(float) * (kWarps * M * kSlots + 2 * C * M * kSlots + M * kSlots + M * 4);
+           sizeof(float) * (kWarps * S * M * kSlots + C * S * M * kSlots + S * M * kSlots + S * M * 4);
 }
 
-template <int C, int VC, int M>
+template <int C, int VC, int M, int S>
 bool launch(const float *residual_hc, const uint16_t *hc_fn, const float *hc_scale, const float *hc_base,
             float *post, float *comb, float *out, int64_t n_tokens, int n_embd, float eps, cudaStream_t s) {
-    auto kernel = hc_pre_cluster_kernel<C, VC, M>;
-    const size_t smem = smem_bytes<C, VC, M>();
+    auto kernel = hc_pre_cluster_kernel<C, VC, M, S>;
+    const size_t smem = smem_bytes<C, VC, M, S>();
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
         cudaGetLastError();
         return false;
@@ -260,8 +290,8 @@ bool launch(const float *residual_hc, const uint16_t *hc_fn, const float *hc_sca
         cudaGetLastError();
         return false;
     }
-    const int64_t n_groups = (n_tokens + M - 1) / M;
-    const int64_t clusters = n_groups < max_clusters ? n_groups : max_clusters;
+    const int64_t n_super = (n_tokens + S * M - 1) / (S * M);
+    const int64_t clusters = n_super < max_clusters ? n_super : max_clusters;
     cfg.gridDim = dim3((unsigned)(clusters * C));
     return cudaLaunchKernelEx(&cfg, kernel, residual_hc, hc_fn, hc_scale, hc_base, post, comb, out, n_tokens,
                               n_embd, eps) == cudaSuccess;
@@ -276,10 +306,15 @@ bool hc_pre_rows_cluster(const float *residual_hc, const uint16_t *hc_fn, const 
                          int n_embd, float eps, cudaStream_t s) {
     if (!aligned8(residual_hc) || !aligned8(out) || (reinterpret_cast<uintptr_t>(hc_fn) & 3u)) return false;
     // the f32 slice is 24 x 2048 x 4 B = 192 KiB per CTA whatever C is: n_embd = C * 512
+    // few tokens: one sub-batch per exchange (lowest latency); batches: four
     if (n_embd == 8 * 512)
-        return launch<8, 1, 4>(residual_hc, hc_fn, hc_scale, hc_base, post, comb, out, n_tokens, n_embd, eps, s);
+        return n_tokens <= 64
+            ? launch<8, 1, 4, 1>(residual_hc, hc_fn, hc_scale, hc_base, post, comb, out, n_tokens, n_embd, eps, s)
+            : launch<8, 1, 4, 4>(residual_hc, hc_fn, hc_scale, hc_base, post, comb, out, n_tokens, n_embd, eps, s);
     if (n_embd == 4 * 512)
-        return launch<4, 1, 4>(residual_hc, hc_fn, hc_scale, hc_base, post, comb, out, n_tokens, n_embd, eps, s);
+        return n_tokens <= 64
+            ? launch<4, 1, 4, 1>(residual_hc, hc_fn, hc_scale, hc_base, post, comb, out, n_tokens, n_embd, eps, s)
+            : launch<4, 1, 4, 4>(residual_hc, hc_fn, hc_scale, hc_base, post, comb, out, n_tokens, n_embd, eps, s);
     return false;
 }
 
