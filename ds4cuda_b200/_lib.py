@@ -62,15 +62,22 @@ SIGNATURES = {
     "ds4b200_launch_hc_attn_pre_f32": (None, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _P]),
     "ds4b200_launch_hc_attn_pre_v2_f32": (None, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _P, _P, _P]),
     "ds4b200_launch_hc_post_f32": (None, [_P, _P, _P, _P, _P, _I, _I, _P]),
+    "ds4b200_launch_output_hc_head_f32": (None, [_P, _P, _P, _P, _P, _I, _I, _F, _P]),
     # batched siblings
     "ds4b200_add_f32": (_I, [_P, _P, _P, _L, _P]),
     "ds4b200_rms_norm_rows_f32": (_I, [_P, _P, _P, _L, _P, _P, _P, _L, _I, _F, _P]),
+    "ds4b200_rms_norm_q8_0_rows_f32": (_I, [_P, _P, _P, _L, _P, _P, _P, _P, _L, _I, _F, _P]),
+    "ds4b200_quantize_q8_0_rows_f32": (_I, [_P, _P, _P, _L, _P]),
+    "ds4b200_quantize_q8_K_rows_f32": (_I, [_P, _P, _P, _P, _L, _P]),
     "ds4b200_embed_gather_rows": (_I, [_P, _I, _P, _L, _I, _P, _P, _F, _P, _I, _P, _P, _P]),
     "ds4b200_rope_rows_f32": (_I, [_P, _P, _L, _I, _I, _I, _P, _RP, _I, _I, _F, _P]),
     "ds4b200_fp8_kv_round_trip_rows_f32": (_I, [_P, _P, _L, _I, _I, _P]),
     "ds4b200_rope_fp8_store_rows": (_I, [_P, _L, _I, _I, _P, _RP, _P, _F, _I, _P, _P, _P, _P, _P, _P]),
+    "ds4b200_kv_rows_to_raw_f32": (_I, [_P, _L, _I, _I, _P, _RP, _P, _F, _P, _P, _P]),
+    "ds4b200_swa_window_push_rows_f32": (_I, [_P, _I, _I, _P, _I, _I, C.POINTER(C.c_int), _P]),
     "ds4b200_swiglu_rows_f32": (_I, [_P, _P, _P, _P, _L, _I, _I, _I, _F, _I, _I, _P]),
     "ds4b200_hc_pre_rows_f32": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _F, _P]),
+    "ds4b200_output_hc_head_rows_f32": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _I, _F, _P]),
     "ds4b200_hc_post_rows_f32": (_I, [_P, _P, _P, _P, _P, _P, _L, _I, _P]),
     "ds4b200_hc_sinkhorn_rows_f32": (_I, [_P, _P, _L, _I, _F, _P]),
     "ds4b200_hc_sinkhorn_mix_rows_f32": (_I, [_P, _P, _P, _P, _L, _I, _I, _F, _P]),

@@ -76,6 +76,43 @@ int ds4b200_rms_norm_rows_f32(const float *x, const float *residual_in, const fl
     return launched("rms_norm_rows");
 }
 
+int ds4b200_rms_norm_q8_0_rows_f32(const float *x, const float *residual_in, const float *w,
+                                   int64_t weight_dim, float *y_f32, float *residual_out, int8_t *xq,
+                                   float *xscale, int64_t n_rows, int n, float eps, void *stream) {
+    REQUIRE(n_rows >= 0 && n >= 0, "rms_norm_q8_0_rows: negative size");
+    if (n_rows == 0 || n == 0) return 0;
+    REQUIRE(n_rows < ((int64_t)1 << 31), "rms_norm_q8_0_rows: n_rows >= 2^31");
+    REQUIRE(x && xq && xscale, "rms_norm_q8_0_rows: null pointer");
+    REQUIRE(n % 32 == 0 && n <= 8192, "rms_norm_q8_0_rows: n must be a multiple of 32, at most 8192");
+    REQUIRE(weight_dim == 0 || weight_dim == n || weight_dim == (int64_t)n * n_rows,
+            "rms_norm_q8_0_rows: weight_dim must be 0, n or n*n_rows");
+    REQUIRE(weight_dim == 0 || w, "rms_norm_q8_0_rows: w is null");
+    REQUIRE(!residual_out || residual_in, "rms_norm_q8_0_rows: residual_out without residual_in");
+    REQUIRE(a16(x) && a16(residual_in) && a16(w) && a16(y_f32) && a16(residual_out) && a4(xq),
+            "rms_norm_q8_0_rows: f32 buffers need 16-byte and xq 4-byte alignment");
+    ds4b200::rms_norm_rows(x, residual_in, w, weight_dim, y_f32, nullptr, residual_out, n_rows, n, eps,
+                           STREAM(stream), xq, xscale);
+    return launched("rms_norm_q8_0_rows");
+}
+
+int ds4b200_quantize_q8_0_rows_f32(const float *x, int8_t *xq, float *xscale, int64_t n_blocks, void *stream) {
+    REQUIRE(n_blocks >= 0, "quantize_q8_0_rows: n_blocks < 0");
+    if (n_blocks == 0) return 0;
+    REQUIRE(x && xq && xscale, "quantize_q8_0_rows: null pointer");
+    ds4b200::quantize_q8_0_rows(x, xq, xscale, n_blocks, STREAM(stream));
+    return launched("quantize_q8_0_rows");
+}
+
+int ds4b200_quantize_q8_K_rows_f32(const float *x, int8_t *xq, float *xscale, int16_t *xbsums,
+                                   int64_t n_blocks, void *stream) {
+    REQUIRE(n_blocks >= 0, "quantize_q8_K_rows: n_blocks < 0");
+    if (n_blocks == 0) return 0;
+    REQUIRE(x && xq && xscale && xbsums, "quantize_q8_K_rows: null pointer");
+    REQUIRE(a16(x) && a4(xq), "quantize_q8_K_rows: x needs 16-byte and xq 4-byte alignment");
+    ds4b200::quantize_q8_K_rows(x, xq, xscale, xbsums, n_blocks, STREAM(stream));
+    return launched("quantize_q8_K_rows");
+}
+
 int ds4b200_embed_gather_rows(const void *table, int table_dtype, const int32_t *ids,
                               int64_t n_tokens, int n_embd, const float *residual_in,
                               const float *norm_w, float eps, float *out_rows, int n_replicas,
@@ -148,6 +185,36 @@ int ds4b200_rope_fp8_store_rows(const float *kv_in, int64_t n_rows, int head_dim
     return launched("rope_fp8_store_rows");
 }
 
+int ds4b200_kv_rows_to_raw_f32(const float *kv_in, int64_t n_rows, int head_dim, int n_rot, const int32_t *pos,
+                               const ds4b200_rope_params *params, const float *norm_w, float eps,
+                               const int32_t *slots, float *raw_out, void *stream) {
+    REQUIRE(n_rows >= 0, "kv_rows_to_raw: n_rows < 0");
+    if (n_rows == 0) return 0;
+    REQUIRE(kv_in && raw_out, "kv_rows_to_raw: null pointer");
+    REQUIRE(head_dim > 0 && head_dim <= 1024 && head_dim % 64 == 0 && n_rot >= 0 && n_rot <= head_dim && n_rot % 64 == 0,
+            "kv_rows_to_raw: head_dim and n_rot must be multiples of 64, head_dim at most 1024");
+    REQUIRE(!params || pos, "kv_rows_to_raw: params without pos");
+    REQUIRE(!params || params->theta_scale > 0.0f || params->freq_base > 0.0f,
+            "kv_rows_to_raw: no theta_scale and no freq_base");
+    REQUIRE(a16(kv_in) && a16(norm_w) && a16(raw_out), "kv_rows_to_raw: buffers need 16-byte alignment");
+    ds4b200::rope_fp8_store_rows(kv_in, n_rows, head_dim, n_rot, pos, params, norm_w, eps, DS4B200_FP8_BLOCK64_POW2,
+                                 slots, nullptr, nullptr, nullptr, nullptr, STREAM(stream), raw_out);
+    return launched("kv_rows_to_raw");
+}
+
+int ds4b200_swa_window_push_rows_f32(float *raw_kv, int cap, int n_raw, const float *new_rows, int n_new,
+                                     int head_dim, int *n_raw_after, void *stream) {
+    REQUIRE(cap > 0 && n_raw >= 0 && n_raw <= cap && n_new >= 0, "swa_window_push_rows: bad window state");
+    REQUIRE(head_dim > 0 && head_dim % 4 == 0, "swa_window_push_rows: head_dim must be a multiple of 4");
+    const int total = n_raw + n_new;
+    if (n_raw_after) *n_raw_after = total < cap ? total : cap;
+    if (n_new == 0) return 0;
+    REQUIRE(raw_kv && new_rows, "swa_window_push_rows: null pointer");
+    REQUIRE(a16(raw_kv) && a16(new_rows), "swa_window_push_rows: buffers need 16-byte alignment");
+    ds4b200::swa_window_push_rows(raw_kv, cap, n_raw, new_rows, n_new, head_dim, STREAM(stream));
+    return launched("swa_window_push_rows");
+}
+
 int ds4b200_swiglu_rows_f32(const float *gate, const float *up, const float *weights, float *out,
                             int64_t n_tokens, int k, int n, int mode, float clamp, int combine,
                             int fast_exp, void *stream) {
@@ -175,6 +242,23 @@ int ds4b200_hc_pre_rows_f32(const float *residual_hc, const uint16_t *hc_fn,
     ds4b200::hc_pre_rows(residual_hc, hc_fn, hc_scale, hc_base, post, comb, out, n_tokens, n_embd,
                          sinkhorn_iters, eps, STREAM(stream));
     return launched("hc_pre_rows");
+}
+
+int ds4b200_output_hc_head_rows_f32(const float *residual_hc, const uint16_t *output_hc_fn,
+                                    const float *output_hc_scale, const float *output_hc_base,
+                                    const float *norm_w, float *out, float *normed, int64_t n_tokens,
+                                    int n_embd, float eps, void *stream) {
+    REQUIRE(n_tokens >= 0, "output_hc_head_rows: n_tokens < 0");
+    if (n_tokens == 0) return 0;
+    REQUIRE(n_tokens < ((int64_t)1 << 31), "output_hc_head_rows: n_tokens >= 2^31");
+    REQUIRE(residual_hc && output_hc_fn && output_hc_scale && output_hc_base, "output_hc_head_rows: null pointer");
+    REQUIRE(out || normed, "output_hc_head_rows: no output");
+    REQUIRE(!normed == !norm_w, "output_hc_head_rows: normed and norm_w go together");
+    REQUIRE(n_embd > 0 && n_embd % 4 == 0 && n_embd <= 8192,
+            "output_hc_head_rows: n_embd must be a multiple of 4, at most 8192");
+    ds4b200::hc_head_rows(residual_hc, output_hc_fn, output_hc_scale, output_hc_base, norm_w, out, normed,
+                          n_tokens, n_embd, eps, STREAM(stream));
+    return launched("output_hc_head_rows");
 }
 
 int ds4b200_hc_post_rows_f32(const float *block_out, const float *block_out2,

@@ -19,7 +19,12 @@ void add_f32(const float *a, const float *b, float *y, int64_t n, cudaStream_t s
 
 void rms_norm_rows(const float *x, const float *residual_in, const float *w, int64_t weight_dim,
                    float *y_f32, uint16_t *y_bf16, float *residual_out, int64_t n_rows, int n,
-                   float eps, cudaStream_t s);
+                   float eps, cudaStream_t s, int8_t *xq = nullptr, float *xscale = nullptr);
+
+// Activation quantisers (cuda/dense_q8.cu:122-152, cuda/moe_iq2_pair.cu:159-235).
+void quantize_q8_0_rows(const float *x, int8_t *xq, float *xscale, int64_t n_blocks, cudaStream_t s);
+void quantize_q8_K_rows(const float *x, int8_t *xq, float *xscale, int16_t *xbsums, int64_t n_blocks,
+                        cudaStream_t s);
 
 void embed_gather_rows(const void *table, int table_dtype, const int32_t *ids, int single_id,
                        int64_t n_tokens, int n_embd, const float *residual_in,
@@ -38,7 +43,12 @@ void fp8_kv_round_trip_rows(const float *kv_in, float *kv_out, int64_t n_rows, i
 void rope_fp8_store_rows(const float *kv_in, int64_t n_rows, int head_dim, int n_rot,
                          const int32_t *pos, const ds4b200_rope_params *p, const float *norm_w,
                          float eps, int scale_mode, const int32_t *slots, uint8_t *codes,
-                         float *scales, float *tail_out, float *rope_out, cudaStream_t s);
+                         float *scales, float *tail_out, float *rope_out, cudaStream_t s,
+                         float *raw_out = nullptr);
+
+// raw_kv window [cap][head_dim]: push n_new rows (f16-rounded), dropping the oldest.
+void swa_window_push_rows(float *raw_kv, int cap, int n_raw, const float *new_rows, int n_new, int head_dim,
+                          cudaStream_t s);
 
 void swiglu_rows(const float *gate, const float *up, const float *weights, float *out,
                  int64_t n_tokens, int k, int n, int mode, float clamp, int combine,
@@ -53,6 +63,11 @@ void hc_pre_rows(const float *residual_hc, const uint16_t *hc_fn, const float *h
 bool hc_pre_rows_cluster(const float *residual_hc, const uint16_t *hc_fn, const float *hc_scale,
                          const float *hc_base, float *post, float *comb, float *out, int64_t n_tokens,
                          int n_embd, float eps, cudaStream_t s);
+
+// Output HC head, optionally followed by the output RMSNorm (norm_w != nullptr -> normed).
+void hc_head_rows(const float *residual_hc, const uint16_t *fn, const float *scale1, const float *base4,
+                  const float *norm_w, float *out, float *normed, int64_t n_tokens, int n_embd, float eps,
+                  cudaStream_t s);
 
 // comb_out[t][16] = Sinkhorn(logits[t][16]), one thread per token.
 void hc_sinkhorn_rows(const float *logits, float *comb_out, int64_t n_tokens, int iters, float eps,

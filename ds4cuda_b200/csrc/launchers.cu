@@ -127,6 +127,14 @@ void launch_hc_post_f32(const float *block_out, const float *residual_hc, const 
                           n_embd, 0, 0.0f, stream);
 }
 
+void launch_output_hc_head_f32(const float *residual_hc, const uint16_t *output_hc_fn,
+                               const float *output_hc_scale, const float *output_hc_base, float *out,
+                               int n_embd, int n_hc, float eps, cudaStream_t stream) {
+    (void)n_hc;
+    ds4b200::hc_head_rows(residual_hc, output_hc_fn, output_hc_scale, output_hc_base, nullptr, out, nullptr, 1,
+                          n_embd, eps, stream);
+}
+
 }  // namespace ds4cuda
 
 // ---------------------------------------------------------------------------
@@ -187,6 +195,13 @@ void ds4b200_launch_hc_post_f32(const float *block_out, const float *residual_hc
                                 const float *post, const float *comb, float *out_hc, int n_hc,
                                 int n_embd, void *stream) {
     ds4cuda::launch_hc_post_f32(block_out, residual_hc, post, comb, out_hc, n_hc, n_embd, S(stream));
+}
+
+void ds4b200_launch_output_hc_head_f32(const float *residual_hc, const uint16_t *output_hc_fn,
+                                       const float *output_hc_scale, const float *output_hc_base,
+                                       float *out, int n_embd, int n_hc, float eps, void *stream) {
+    ds4cuda::launch_output_hc_head_f32(residual_hc, output_hc_fn, output_hc_scale, output_hc_base, out, n_embd,
+                                       n_hc, eps, S(stream));
 }
 
 }  // extern "C"

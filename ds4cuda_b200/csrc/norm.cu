@@ -28,6 +28,8 @@ struct NormArgs {
     int64_t n_rows;
     int n;
     float eps;
+    int8_t *xq;        // optional Q8_0 split form of the normalised row (n % 32 == 0)
+    float *xscale;     // [n_rows][n / 32]
 };
 
 __device__ __forceinline__ const float *row_gain(const NormArgs &a, int64_t row) {
@@ -70,6 +72,11 @@ __device__ __forceinline__ float load_row(const NormArgs &a, int64_t row, int fi
     return ss;
 }
 
+__device__ __forceinline__ int q8_round(float v) {
+    const int q = __float2int_rn(v);
+    return q > 127 ? 127 : (q < -128 ? -128 : q);
+}
+
 template <int VPT>
 __device__ __forceinline__ void store_row(const NormArgs &a, int64_t row, int first, int stride,
                                           const float4 (&v)[VPT], float scale) {
@@ -80,14 +87,30 @@ __device__ __forceinline__ void store_row(const NormArgs &a, int64_t row, int fi
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
         const int i = first + j * stride;
-        if (i >= n4) continue;
+        const bool live = i < n4;
         float4 y = make_float4(v[j].x * scale, v[j].y * scale, v[j].z * scale, v[j].w * scale);
-        if (g) {
+        if (g && live) {
             const float4 w4 = ld_ro4(g + 4 * i);
             y.x *= w4.x; y.y *= w4.y; y.z *= w4.z; y.w *= w4.w;
         }
-        if (yf) st_stream4(yf + 4 * i, y);
-        if (yb) st_bf16x4(yb + 4 * i, y);
+        if (live && yf) st_stream4(yf + 4 * i, y);
+        if (live && yb) st_bf16x4(yb + 4 * i, y);
+        if (a.xq) {
+            // Q8_0 activation quantiser of the matvec that consumes this row
+            // (cuda/dense_q8.cu:122-152): 32 elements = 8 consecutive lanes.  n % 32 == 0, so
+            // a group of 8 lanes is live or dead as a whole; dead lanes only feed the shuffles.
+            float amax = live ? amax4(y) : 0.0f;
+#pragma unroll
+            for (int off = 4; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+            const float d = amax / 127.0f;
+            const float id = (d != 0.0f) ? 1.0f / d : 0.0f;
+            if (live) {
+                const uint32_t packed = (uint32_t)(q8_round(y.x * id) & 0xff) | ((uint32_t)(q8_round(y.y * id) & 0xff) << 8) |
+                                        ((uint32_t)(q8_round(y.z * id) & 0xff) << 16) | ((uint32_t)(q8_round(y.w * id) & 0xff) << 24);
+                reinterpret_cast<uint32_t *>(a.xq + row * a.n)[i] = packed;
+                if ((i & 7) == 0) a.xscale[row * (a.n >> 5) + (i >> 3)] = d;
+            }
+        }
     }
 }
 
@@ -185,9 +208,9 @@ void add_f32(const float *a, const float *b, float *y, int64_t n, cudaStream_t s
 
 void rms_norm_rows(const float *x, const float *residual_in, const float *w, int64_t weight_dim,
                    float *y_f32, uint16_t *y_bf16, float *residual_out, int64_t n_rows, int n,
-                   float eps, cudaStream_t s) {
+                   float eps, cudaStream_t s, int8_t *xq, float *xscale) {
     if (n_rows <= 0 || n <= 0) return;
-    const NormArgs a{x, residual_in, w, weight_dim, y_f32, y_bf16, residual_out, n_rows, n, eps};
+    const NormArgs a{x, residual_in, w, weight_dim, y_f32, y_bf16, residual_out, n_rows, n, eps, xq, xscale};
     const bool vec = (n & 3) == 0 && n <= 8192 && aligned16(x) && aligned16(residual_in) &&
                      aligned16(w) && aligned16(y_f32) && aligned8(y_bf16) &&
                      aligned16(residual_out);

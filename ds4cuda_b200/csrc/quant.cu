@@ -1,0 +1,133 @@
+// quant.cu — the activation quantisers that sit between the row ops of this library
+// and the reference's quantised matvecs: Q8_0 in split form (int8 values + one f32 scale
+// per 32 elements, cuda/dense_q8.cu:122-152) and Q8_K (per 256 elements: int8 values, f32
+// scale, 16 partial sums, cuda/moe_iq2_pair.cu:159-235).  Integer outputs are bit-exact.
+//
+// Data movement: 128-bit loads, 32-bit (char4) stores; a Q8_0 block is 8 consecutive
+// lanes (3 shuffles), a Q8_K block is one warp holding two float4 per lane.
+#include "device_utils.cuh"
+#include "kernels.cuh"
+
+namespace ds4b200 {
+namespace {
+
+__device__ __forceinline__ int q8_round(float v) {
+    const int q = __float2int_rn(v);           // ties to even, like lrintf
+    return q > 127 ? 127 : (q < -128 ? -128 : q);
+}
+__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
+    return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) |
+           ((uint32_t)(d & 0xff) << 24);
+}
+
+// n4 float4s, 8 per block.  Every lane of a warp takes part in the shuffles; lanes past
+// the end carry zeros and store nothing.
+__global__ void quantize_q8_0_kernel(const float *__restrict__ x, int8_t *__restrict__ xq,
+                                     float *__restrict__ xscale, int64_t n4) {
+    const int64_t rounded = (n4 + 31) & ~(int64_t)31;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < rounded;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const float4 v = (i < n4) ? ld_stream4(x + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float amax = amax4(v);
+#pragma unroll
+        for (int off = 4; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        const float d = amax / 127.0f;
+        const float id = (d != 0.0f) ? 1.0f / d : 0.0f;
+        if (i < n4) {
+            reinterpret_cast<uint32_t *>(xq)[i] =
+                pack4(q8_round(v.x * id), q8_round(v.y * id), q8_round(v.z * id), q8_round(v.w * id));
+            if ((i & 7) == 0) xscale[i >> 3] = d;
+        }
+    }
+}
+
+// One warp per 256-element block: lane l holds elements 4l..4l+3 and 128+4l..128+4l+3.
+// `max` is the element of largest magnitude, the first one in index order on ties.
+__global__ void quantize_q8_K_kernel(const float *__restrict__ x, int8_t *__restrict__ xq,
+                                     float *__restrict__ xscale, int16_t *__restrict__ xbsums,
+                                     int64_t n_blocks) {
+    const int lane = threadIdx.x & 31;
+    const int64_t b = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (b >= n_blocks) return;
+    const float *xb = x + b * 256;
+    const float4 v0 = ld_stream4(xb + 4 * lane), v1 = ld_stream4(xb + 128 + 4 * lane);
+    const float e[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    // key = magnitude bits in the high word, inverted index in the low word: the maximum key
+    // is the largest magnitude and, among equals, the smallest index
+    unsigned long long key = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const uint32_t idx = (k < 4 ? 4 * lane + k : 128 + 4 * lane + (k - 4));
+        const unsigned long long cand = ((unsigned long long)__float_as_uint(fabsf(e[k])) << 32) | (0xffffffffu - idx);
+        key = cand > key ? cand : key;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, off);
+        key = other > key ? other : key;
+    }
+    const float amax = __uint_as_float((uint32_t)(key >> 32));
+    int8_t *qb = xq + b * 256;
+    if (amax == 0.0f) {
+        reinterpret_cast<uint32_t *>(qb)[lane] = 0u;
+        reinterpret_cast<uint32_t *>(qb)[32 + lane] = 0u;
+        if (lane < 16) xbsums[b * 16 + lane] = 0;
+        if (lane == 0) xscale[b] = 0.0f;
+        return;
+    }
+    const uint32_t idx = 0xffffffffu - (uint32_t)key;
+    const int k_own = (idx < 128 ? (int)(idx & 3u) : 4 + (int)(idx & 3u));
+    float mine = e[0];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) mine = (k == k_own) ? e[k] : mine;
+    const float smax = __shfl_sync(0xffffffffu, mine, (int)((idx & 127u) >> 2));
+    const float iscale = -127.0f / smax;
+    int q[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) q[k] = q8_round(iscale * e[k]);
+    reinterpret_cast<uint32_t *>(qb)[lane] = pack4(q[0], q[1], q[2], q[3]);
+    reinterpret_cast<uint32_t *>(qb)[32 + lane] = pack4(q[4], q[5], q[6], q[7]);
+    // 16 consecutive values = 4 consecutive lanes of one half
+    int s0 = q[0] + q[1] + q[2] + q[3], s1 = q[4] + q[5] + q[6] + q[7];
+    s0 += __shfl_xor_sync(0xffffffffu, s0, 1); s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
+    s0 += __shfl_xor_sync(0xffffffffu, s0, 2); s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+    if ((lane & 3) == 0) {
+        xbsums[b * 16 + (lane >> 2)] = (int16_t)s0;
+        xbsums[b * 16 + 8 + (lane >> 2)] = (int16_t)s1;
+    }
+    if (lane == 0) xscale[b] = 1.0f / iscale;
+}
+
+// Scalar forms for buffers without 16-byte (input) / 4-byte (output) alignment.
+__global__ void quantize_q8_0_scalar_kernel(const float *x, int8_t *xq, float *xscale, int64_t n_blocks) {
+    const int lane = threadIdx.x & 31;
+    const int64_t b = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (b >= n_blocks) return;
+    const float v = x[b * 32 + lane];
+    const float d = warp_max(fabsf(v)) / 127.0f;
+    const float id = (d != 0.0f) ? 1.0f / d : 0.0f;
+    xq[b * 32 + lane] = (int8_t)q8_round(v * id);
+    if (lane == 0) xscale[b] = d;
+}
+
+}  // namespace
+
+void quantize_q8_0_rows(const float *x, int8_t *xq, float *xscale, int64_t n_blocks, cudaStream_t s) {
+    if (n_blocks <= 0) return;
+    if (aligned16(x) && (reinterpret_cast<uintptr_t>(xq) & 3u) == 0) {
+        const int64_t n4 = n_blocks * 8;
+        int64_t blocks = (n4 + 255) / 256;
+        if (blocks > 148 * 16) blocks = 148 * 16;
+        quantize_q8_0_kernel<<<(unsigned)blocks, 256, 0, s>>>(x, xq, xscale, n4);
+    } else {
+        quantize_q8_0_scalar_kernel<<<(unsigned)((n_blocks + 7) / 8), 256, 0, s>>>(x, xq, xscale, n_blocks);
+    }
+}
+
+void quantize_q8_K_rows(const float *x, int8_t *xq, float *xscale, int16_t *xbsums, int64_t n_blocks,
+                        cudaStream_t s) {
+    if (n_blocks <= 0) return;
+    quantize_q8_K_kernel<<<(unsigned)((n_blocks + 7) / 8), 256, 0, s>>>(x, xq, xscale, xbsums, n_blocks);
+}
+
+}  // namespace ds4b200

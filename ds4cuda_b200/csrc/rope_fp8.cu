@@ -206,7 +206,15 @@ struct StoreArgs {
     float *scales;
     float *tail_out;
     float *rope_out;
+    float *raw_out;     // BLOCK64_POW2 only: f16-rounded round-trip row, the raw-KV cache form
 };
+
+// f32 -> f16 -> f32, the rounding the reference applies when a row enters its raw KV cache
+// (cuda/forward_layer.cu:182-190).
+__device__ __forceinline__ float f16_round(float v) { return __half2float(__float2half_rn(v)); }
+__device__ __forceinline__ float4 f16_round4(float4 v) {
+    return make_float4(f16_round(v.x), f16_round(v.y), f16_round(v.z), f16_round(v.w));
+}
 
 template <int VPT>
 __global__ void __launch_bounds__(kRowsPerCta * 32) rope_fp8_store_kernel(StoreArgs a) {
@@ -277,14 +285,57 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) rope_fp8_store_kernel(StoreA
             if (i >= n4) continue;
             if (4 * i < n_nope) {
                 const float scale = pow2_scale(amax);
-                if ((lane & 15) == 0) a.scales[slot * n_scales + (i >> 4)] = scale;
-                const float4 q = make_float4(clamp448(v[j].x / scale), clamp448(v[j].y / scale),
-                                             clamp448(v[j].z / scale), clamp448(v[j].w / scale));
-                __stcs(code_row + i, e4m3_encode4(q));
+                if (a.scales && (lane & 15) == 0) a.scales[slot * n_scales + (i >> 4)] = scale;
+                if (a.codes) {
+                    const float4 q = make_float4(clamp448(v[j].x / scale), clamp448(v[j].y / scale),
+                                                 clamp448(v[j].z / scale), clamp448(v[j].w / scale));
+                    __stcs(code_row + i, e4m3_encode4(q));
+                }
+                if (a.raw_out)
+                    st_stream4(a.raw_out + slot * head_dim + 4 * i,
+                               f16_round4(make_float4(e4m3_round_trip(v[j].x, scale), e4m3_round_trip(v[j].y, scale),
+                                                      e4m3_round_trip(v[j].z, scale), e4m3_round_trip(v[j].w, scale))));
             } else {
-                __stcs(code_row + i, 0u);
+                if (a.codes) __stcs(code_row + i, 0u);
                 if (a.tail_out) st_stream4(a.tail_out + slot * a.n_rot + (4 * i - n_nope), v[j]);
+                if (a.raw_out) st_stream4(a.raw_out + slot * head_dim + 4 * i, f16_round4(v[j]));
             }
+        }
+    }
+}
+
+// --------------------------- sliding raw-KV window ---------------------------
+// The reference keeps the last `cap` rows in a linear window: append while there is room,
+// otherwise move every row down by one and write the new row last, one token per call
+// (cuda/forward_layer.cu:159-190, :941-972).  Here n_new rows enter at once: the window
+// afterwards holds the last min(cap, n_raw + n_new) rows of old ++ new.  Columns are
+// independent, so one thread owns one float4 column and walks the rows upwards in batches
+// of 16: every batch is read completely before it is written, and it only reads rows at or
+// above the ones it writes, so the move is safe in place.  New rows get the f16 rounding;
+// old rows already have it.
+__global__ void swa_window_push_kernel(float *raw_kv, int cap, int n_raw, const float *new_rows, int n_new,
+                                       int head_dim) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= (head_dim >> 2)) return;
+    const int total = n_raw + n_new;
+    const int kept = total < cap ? total : cap;              // rows in the window afterwards
+    const int first = total - kept;                          // index in old ++ new of window row 0
+    constexpr int kBatch = 16;
+    for (int r0 = (first == 0 ? n_raw : 0); r0 < kept; r0 += kBatch) {      // pure append: old rows stay
+        float4 v[kBatch];
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+            const int r = r0 + b, src = first + r;
+            if (r >= kept) break;
+            v[b] = src < n_raw ? *reinterpret_cast<const float4 *>(raw_kv + (int64_t)src * head_dim + 4 * c)
+                               : f16_round4(__ldg(reinterpret_cast<const float4 *>(
+                                     new_rows + (int64_t)(src - n_raw) * head_dim + 4 * c)));
+        }
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+            const int r = r0 + b;
+            if (r >= kept) break;
+            *reinterpret_cast<float4 *>(raw_kv + (int64_t)r * head_dim + 4 * c) = v[b];
         }
     }
 }
@@ -394,9 +445,10 @@ void fp8_kv_round_trip_rows(const float *kv_in, float *kv_out, int64_t n_rows, i
 void rope_fp8_store_rows(const float *kv_in, int64_t n_rows, int head_dim, int n_rot,
                          const int32_t *pos, const ds4b200_rope_params *p, const float *norm_w,
                          float eps, int scale_mode, const int32_t *slots, uint8_t *codes,
-                         float *scales, float *tail_out, float *rope_out, cudaStream_t s) {
+                         float *scales, float *tail_out, float *rope_out, cudaStream_t s, float *raw_out) {
     if (n_rows <= 0) return;
     StoreArgs a{};
+    a.raw_out = raw_out;
     a.kv_in = kv_in; a.n_rows = n_rows; a.head_dim = head_dim; a.n_rot = n_rot; a.pos = pos;
     a.do_rope = p != nullptr;
     if (p) a.rope = to_dev(*p);
@@ -408,6 +460,13 @@ void rope_fp8_store_rows(const float *kv_in, int64_t n_rows, int head_dim, int n
     else if (vpt <= 2) rope_fp8_store_kernel<2><<<grid, kRowsPerCta * 32, 0, s>>>(a);
     else if (vpt <= 4) rope_fp8_store_kernel<4><<<grid, kRowsPerCta * 32, 0, s>>>(a);
     else rope_fp8_store_kernel<8><<<grid, kRowsPerCta * 32, 0, s>>>(a);
+}
+
+void swa_window_push_rows(float *raw_kv, int cap, int n_raw, const float *new_rows, int n_new, int head_dim,
+                          cudaStream_t s) {
+    if (n_new <= 0 || cap <= 0) return;
+    const int n4 = head_dim >> 2;
+    swa_window_push_kernel<<<(n4 + 31) / 32, 32, 0, s>>>(raw_kv, cap, n_raw, new_rows, n_new, head_dim);
 }
 
 void e4m3_encode(const float *x, uint8_t *codes, int64_t n, cudaStream_t s) {

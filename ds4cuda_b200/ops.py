@@ -17,8 +17,8 @@ from ._lib import (FP8_BLOCK64_POW2, FP8_ROW_AMAX, GLU_CLAMP_REF, GLU_CLAMP_SYM,
 __all__ = [
     "FP8_BLOCK64_POW2", "FP8_ROW_AMAX", "GLU_CLAMP_REF", "GLU_CLAMP_SYM", "GLU_PLAIN",
     "TABLE_F16", "TABLE_Q8_0", "RopeParams", "rope_params_for_layer", "rope_params_explicit",
-    "add", "rms_norm_rows", "embed_gather_rows", "rope_rows", "fp8_kv_round_trip_rows",
-    "rope_fp8_store_rows", "swiglu_rows", "hc_pre_rows", "hc_post_rows", "hc_sinkhorn_rows", "hc_sinkhorn_mix_rows",
+    "add", "rms_norm_rows", "rms_norm_q8_0_rows", "quantize_q8_0_rows", "quantize_q8_K_rows", "embed_gather_rows", "rope_rows", "fp8_kv_round_trip_rows",
+    "rope_fp8_store_rows", "kv_rows_to_raw", "swa_window_push_rows", "swiglu_rows", "hc_pre_rows", "output_hc_head_rows", "hc_post_rows", "hc_sinkhorn_rows", "hc_sinkhorn_mix_rows",
     "e4m3_encode", "e4m3_decode", "e4m3_selfcheck", "div_selfcheck", "device_status",
 ]
 
@@ -74,6 +74,36 @@ def rms_norm_rows(x, w=None, residual=None, eps=1e-6, want_f32=True, want_bf16=F
     return y, yb, ro
 
 
+def rms_norm_q8_0_rows(x, w=None, residual=None, eps=1e-6, want_f32=True, want_residual=False):
+    """RMSNorm + Q8_0 activation quantiser.  Returns (y_f32, residual_out, xq int8 [rows, n], xscale [rows, n/32])."""
+    rows, n = x.shape
+    y = torch.empty_like(x) if want_f32 else None
+    ro = torch.empty_like(x) if want_residual else None
+    xq = torch.empty((rows, n), dtype=torch.int8, device=x.device)
+    xs = torch.empty((rows, n // 32), dtype=torch.float32, device=x.device)
+    check(_lib.load().ds4b200_rms_norm_q8_0_rows_f32(_p(x), _p(residual), _p(w), 0 if w is None else w.numel(), _p(y),
+                                                     _p(ro), _p(xq), _p(xs), rows, n, eps, _s()))
+    return y, ro, xq, xs
+
+
+def quantize_q8_0_rows(x):
+    """x with numel % 32 == 0 -> (int8 like x, f32 scales [numel/32])."""
+    xq = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    xs = torch.empty(x.numel() // 32, dtype=torch.float32, device=x.device)
+    check(_lib.load().ds4b200_quantize_q8_0_rows_f32(_p(x), _p(xq), _p(xs), x.numel() // 32, _s()))
+    return xq, xs
+
+
+def quantize_q8_K_rows(x):
+    """x with numel % 256 == 0 -> (int8 like x, f32 scales [numel/256], int16 sums [numel/16])."""
+    nb = x.numel() // 256
+    xq = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    xs = torch.empty(nb, dtype=torch.float32, device=x.device)
+    bs = torch.empty(nb * 16, dtype=torch.int16, device=x.device)
+    check(_lib.load().ds4b200_quantize_q8_K_rows_f32(_p(x), _p(xq), _p(xs), _p(bs), nb, _s()))
+    return xq, xs, bs
+
+
 def embed_gather_rows(table, table_dtype, ids, n_embd, residual=None, norm_w=None, eps=1e-6,
                       n_replicas=1, want_rows=True, want_f32=False, want_bf16=False):
     """Returns (rows [T, n_replicas, n_embd] f32, normed_f32, normed_bf16)."""
@@ -113,6 +143,24 @@ def rope_fp8_store_rows(kv, pos, params, n_rot, scale_mode, codes, scales, slots
         eps, scale_mode, _p(slots), _p(codes), _p(scales), _p(tail_out), _p(rope_out), _s()))
 
 
+def kv_rows_to_raw(kv, pos, params, raw_out, n_rot=64, slots=None, norm_w=None, eps=1e-6):
+    """norm -> RoPE -> FP8 round trip -> f16 round, written to raw_out[slot] (f32 rows)."""
+    rows, D = kv.shape
+    check(_lib.load().ds4b200_kv_rows_to_raw_f32(_p(kv), rows, D, n_rot, _p(pos),
+                                                 None if params is None else C.byref(params), _p(norm_w), eps,
+                                                 _p(slots), _p(raw_out), _s()))
+    return raw_out
+
+
+def swa_window_push_rows(raw_kv, n_raw, new_rows):
+    """raw_kv [cap, D] window with n_raw rows; pushes new_rows [n, D]; returns the new row count."""
+    cap, D = raw_kv.shape
+    after = C.c_int()
+    check(_lib.load().ds4b200_swa_window_push_rows_f32(_p(raw_kv), cap, n_raw, _p(new_rows), new_rows.shape[0], D,
+                                                       C.byref(after), _s()))
+    return after.value
+
+
 def swiglu_rows(gate, up, weights=None, mode=GLU_PLAIN, clamp=0.0, combine=False, fast_exp=False):
     """gate/up [T, k, n]; returns [T, n] when combine else [T, k, n]."""
     T, k, n = gate.shape
@@ -132,6 +180,16 @@ def hc_pre_rows(resid, fn_f16, scale3, base24, iters=20, eps=1e-6):
     check(_lib.load().ds4b200_hc_pre_rows_f32(_p(resid), _p(fn_f16), _p(scale3), _p(base24), _p(post),
                                               _p(comb), _p(out), T, n, iters, eps, _s()))
     return post, comb, out
+
+
+def output_hc_head_rows(resid, fn_f16, scale1, base4, norm_w=None, eps=1e-6, want_out=True):
+    """resid [T, 4, n]; fn_f16 [4, 4n].  Returns (out [T, n], normed [T, n] or None)."""
+    T, _, n = resid.shape
+    out = torch.empty((T, n), dtype=torch.float32, device=resid.device) if want_out else None
+    normed = torch.empty((T, n), dtype=torch.float32, device=resid.device) if norm_w is not None else None
+    check(_lib.load().ds4b200_output_hc_head_rows_f32(_p(resid), _p(fn_f16), _p(scale1), _p(base4), _p(norm_w),
+                                                      _p(out), _p(normed), T, n, eps, _s()))
+    return out, normed
 
 
 def hc_post_rows(block_out, resid, post, comb, block_out2=None):

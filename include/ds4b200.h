@@ -117,6 +117,11 @@ void ds4b200_launch_hc_post_f32(const float *block_out, const float *residual_hc
                                 const float *post, const float *comb, float *out_hc,
                                 int n_hc, int n_embd, void *stream);
 
+/* cuda/output_head.cuh:68 */
+void ds4b200_launch_output_hc_head_f32(const float *residual_hc, const uint16_t *output_hc_fn,
+                                       const float *output_hc_scale, const float *output_hc_base,
+                                       float *out, int n_embd, int n_hc, float eps, void *stream);
+
 /* ---- 2. batched, checked siblings ---------------------------------------------- */
 
 /* y = a + b over n elements (cuda/elementwise.cu:36-43, any n). */
@@ -130,6 +135,24 @@ int ds4b200_rms_norm_rows_f32(const float *x, const float *residual_in, const fl
                               int64_t weight_dim, float *y_f32, uint16_t *y_bf16,
                               float *residual_out, int64_t n_rows, int n, float eps,
                               void *stream);
+
+/* The same RMSNorm with the activation quantiser of the Q8_0 matvec that consumes the row
+ * fused behind it (cuda/dense_q8.cu:122-152: per 32 elements d = amax/127 as f32,
+ * q = clamp(rint(y/d))): xq[n_rows][n] int8, xscale[n_rows][n/32].  y_f32 nullable.
+ * n a multiple of 32, at most 8192; 16-byte aligned f32 buffers. */
+int ds4b200_rms_norm_q8_0_rows_f32(const float *x, const float *residual_in, const float *w,
+                                   int64_t weight_dim, float *y_f32, float *residual_out,
+                                   int8_t *xq, float *xscale, int64_t n_rows, int n, float eps,
+                                   void *stream);
+
+/* The activation quantisers on their own.  Q8_0 split form: n_blocks blocks of 32 f32 ->
+ * int8 + one f32 scale each (cuda/dense_q8.cu:122-152).  Q8_K: n_blocks blocks of 256 ->
+ * int8, one f32 scale and 16 int16 partial sums each (cuda/moe_iq2_pair.cu:159-235; on equal
+ * magnitudes the first element decides the sign of the scale). */
+int ds4b200_quantize_q8_0_rows_f32(const float *x, int8_t *xq, float *xscale, int64_t n_blocks,
+                                   void *stream);
+int ds4b200_quantize_q8_K_rows_f32(const float *x, int8_t *xq, float *xscale, int16_t *xbsums,
+                                   int64_t n_blocks, void *stream);
 
 /* Embedding gather for n_tokens ids (cuda/embedding.cu:27-39 for F16 rows,
  * cuda/dense_q8.cu:60-67 for Q8_0 rows of 34-byte blocks), fused with what
@@ -168,6 +191,23 @@ int ds4b200_rope_fp8_store_rows(const float *kv_in, int64_t n_rows, int head_dim
                                 const int32_t *slots, uint8_t *codes, float *scales,
                                 float *tail_out, float *rope_out, void *stream);
 
+/* The whole KV row chain of the reference in one launch (cuda/forward_layer.cu:868, :910,
+ * :921, :950): optional weighted RMSNorm -> tail RoPE at pos[r] -> E4M3FN round trip of the
+ * non-rotated prefix with per-64 power-of-two scales -> f16 rounding -> raw_out[slot][head_dim]
+ * in f32, the form rows have in the reference's raw KV cache.  slots nullable (= r). */
+int ds4b200_kv_rows_to_raw_f32(const float *kv_in, int64_t n_rows, int head_dim, int n_rot,
+                               const int32_t *pos, const ds4b200_rope_params *params,
+                               const float *norm_w, float eps, const int32_t *slots,
+                               float *raw_out, void *stream);
+
+/* Sliding raw-KV window [cap][head_dim] holding n_raw rows: push n_new rows at once
+ * (f16-rounded on entry).  Equivalent to n_new single-row pushes of the reference
+ * (append while there is room, else shift every row down by one and write last,
+ * cuda/forward_layer.cu:159-190, :941-972).  *n_raw_after (host, nullable) receives
+ * min(cap, n_raw + n_new).  In place. */
+int ds4b200_swa_window_push_rows_f32(float *raw_kv, int cap, int n_raw, const float *new_rows,
+                                     int n_new, int head_dim, int *n_raw_after, void *stream);
+
 /* SwiGLU over gate/up[n_tokens][k][n].  weights[n_tokens][k] nullable.
  * combine != 0: out[n_tokens][n] = sum of the k slots in slot order; else
  * out[n_tokens][k][n].  fast_exp != 0 uses the hardware exp approximation the
@@ -190,6 +230,16 @@ int ds4b200_hc_pre_rows_f32(const float *residual_hc, const uint16_t *hc_fn,
 int ds4b200_hc_post_rows_f32(const float *block_out, const float *block_out2,
                              const float *residual_hc, const float *post, const float *comb,
                              float *out_hc, int64_t n_tokens, int n_embd, void *stream);
+
+/* Output HC head for n_tokens tokens (cuda/output_head.cu:62-149): RMS over the 4*n_embd
+ * block, 4-row f16 matvec, w[h] = sigmoid(pre[h]*scale[0]+base[h]) + eps, out[t] = sum_h
+ * w[h]*resid[t][h].  With norm_w given, the output RMSNorm that follows it in the forward
+ * pass (cuda/forward_token.cu:211) is fused: normed[t] = rmsnorm(out[t]) * norm_w.  `out`
+ * may be NULL when only `normed` is wanted. */
+int ds4b200_output_hc_head_rows_f32(const float *residual_hc, const uint16_t *output_hc_fn,
+                                    const float *output_hc_scale, const float *output_hc_base,
+                                    const float *norm_w, float *out, float *normed,
+                                    int64_t n_tokens, int n_embd, float eps, void *stream);
 
 /* The Sinkhorn step alone (cuda/hc_sinkhorn.cu:224-289): logits[t][16] (index
  * src+4*dst) -> row softmax + eps -> one column pass, then sinkhorn_iters-1

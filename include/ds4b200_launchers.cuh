@@ -63,4 +63,9 @@ void launch_hc_post_f32(const float *block_out, const float *residual_hc, const 
                         const float *comb, float *out_hc, int n_hc, int n_embd,
                         cudaStream_t stream = 0);
 
+// cuda/output_head.cuh:68 — final collapse of the four streams (cuda/forward_token.cu:198)
+void launch_output_hc_head_f32(const float *residual_hc, const uint16_t *output_hc_fn,
+                               const float *output_hc_scale, const float *output_hc_base, float *out,
+                               int n_embd, int n_hc, float eps, cudaStream_t stream = 0);
+
 }  // namespace ds4cuda

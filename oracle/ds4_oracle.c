@@ -65,6 +65,11 @@ uint16_t ds4o_f32_to_bf16(float f)
 
 float ds4o_bf16_to_f32(uint16_t h) { return bits_f32((uint32_t)h << 16); }
 
+void ds4o_f16_round(const float *x, float *y, int64_t n)
+{
+    for (int64_t i = 0; i < n; i++) y[i] = ds4o_f16_to_f32(ds4o_f32_to_f16(x[i]));
+}
+
 /* ====================================================================== */
 /* E4M3FN  (cuda/fp8_kv.cu:11-35,88-131)                                   */
 /* ====================================================================== */
@@ -330,6 +335,50 @@ void ds4o_rope_fp8_store_rows(const float *kv_in, int64_t n_rows, int head_dim, 
 }
 
 /* ====================================================================== */
+/* activation quantisers                                                   */
+/* ====================================================================== */
+
+static inline int clamp_i8(long v) { return v > 127 ? 127 : (v < -128 ? -128 : (int)v); }
+
+void ds4o_quantize_q8_0_rows(const float *x, int8_t *xq, float *xscale, int64_t n_blocks)
+{
+    for (int64_t b = 0; b < n_blocks; b++) {
+        const float *xb = x + b * 32;
+        float amax = 0.0f;
+        for (int i = 0; i < 32; i++) amax = fmaxf(amax, fabsf(xb[i]));
+        const float d = amax / 127.0f;
+        const float id = (d != 0.0f) ? 1.0f / d : 0.0f;
+        xscale[b] = d;
+        for (int i = 0; i < 32; i++) xq[b * 32 + i] = (int8_t)clamp_i8(lrintf(xb[i] * id));
+    }
+}
+
+void ds4o_quantize_q8_K_rows(const float *x, int8_t *xq, float *xscale, int16_t *xbsums, int64_t n_blocks)
+{
+    for (int64_t b = 0; b < n_blocks; b++) {
+        const float *xb = x + b * 256;
+        int8_t *qb = xq + b * 256;
+        float amax = 0.0f, smax = 0.0f;
+        for (int i = 0; i < 256; i++)
+            if (fabsf(xb[i]) > amax) { amax = fabsf(xb[i]); smax = xb[i]; }
+        if (amax == 0.0f) {
+            memset(qb, 0, 256);
+            for (int k = 0; k < 16; k++) xbsums[b * 16 + k] = 0;
+            xscale[b] = 0.0f;
+            continue;
+        }
+        const float iscale = -127.0f / smax;
+        for (int i = 0; i < 256; i++) qb[i] = (int8_t)clamp_i8(lrintf(iscale * xb[i]));
+        for (int k = 0; k < 16; k++) {
+            int sum = 0;
+            for (int j = 0; j < 16; j++) sum += qb[k * 16 + j];
+            xbsums[b * 16 + k] = (int16_t)sum;
+        }
+        xscale[b] = 1.0f / iscale;
+    }
+}
+
+/* ====================================================================== */
 /* SwiGLU                                                                  */
 /* ====================================================================== */
 
@@ -509,6 +558,40 @@ void ds4o_hc_post_rows(const float *block_out, const float *block_out2,
                 }
                 out_hc[(t * 4 + dst) * (int64_t)n_embd + d] = acc;
             }
+        }
+    }
+}
+
+void ds4o_output_hc_head_rows(const float *residual_hc, const uint16_t *fn_f16, const float *scale1,
+                              const float *base4, const float *norm_w, float *out, float *normed,
+                              int64_t n_tokens, int n_embd, float eps)
+{
+    const int64_t hc_dim = 4 * (int64_t)n_embd;
+    for (int64_t t = 0; t < n_tokens; t++) {
+        const float *x = residual_hc + t * hc_dim;
+        const float rms = rms_scale_of(x, hc_dim, eps);
+        float w[4];
+        for (int h = 0; h < 4; h++) {
+            double acc = 0.0;
+            for (int64_t i = 0; i < hc_dim; i++) {
+                const float xf = x[i] * rms;
+                const float pr = ds4o_f16_to_f32(fn_f16[h * hc_dim + i]) * xf;
+                acc += (double)pr;
+            }
+            const float z = (float)acc * scale1[0] + base4[h];
+            w[h] = 1.0f / (1.0f + expf(-z)) + eps;
+        }
+        float *o = out + t * n_embd;
+        for (int d = 0; d < n_embd; d++) {
+            float acc = x[d] * w[0];
+            acc = acc + x[n_embd + d] * w[1];
+            acc = acc + x[2 * n_embd + d] * w[2];
+            acc = acc + x[3 * n_embd + d] * w[3];
+            o[d] = acc;
+        }
+        if (norm_w) {
+            const float sc = rms_scale_of(o, n_embd, eps);
+            for (int d = 0; d < n_embd; d++) normed[t * n_embd + d] = o[d] * sc * norm_w[d];
         }
     }
 }

@@ -50,6 +50,10 @@ uint16_t ds4o_f32_to_f16(float f);               /* RNE, test-input helper */
 uint16_t ds4o_f32_to_bf16(float f);              /* RNE */
 float    ds4o_bf16_to_f32(uint16_t h);
 
+/* f32 -> f16 -> f32 per element: the rounding rows get when they enter the raw KV cache
+ * (cuda/forward_layer.cu:182-190). */
+void ds4o_f16_round(const float *x, float *y, int64_t n);
+
 /* ---- E4M3FN ------------------------------------------------------------ */
 float   ds4o_e4m3_value(int idx);                /* cuda/fp8_kv.cu:88-94   */
 int     ds4o_e4m3_nearest_index(float ax);       /* cuda/fp8_kv.cu:102-131 */
@@ -103,6 +107,15 @@ void ds4o_rope_fp8_store_rows(const float *kv_in, int64_t n_rows, int head_dim, 
                               uint8_t *codes, float *scales, float *tail_out,
                               float *rope_out);
 
+/* ---- activation quantisers that sit between these ops and the matvecs ------- */
+/* Q8_0 split form (cuda/dense_q8.cu:122-152): per 32 elements d = amax/127 kept as f32,
+ * q = clamp(rint(x * (d != 0 ? 1/d : 0)), -128, 127), ties to even. */
+void ds4o_quantize_q8_0_rows(const float *x, int8_t *xq, float *xscale, int64_t n_blocks);
+/* Q8_K (cuda/moe_iq2_pair.cu:159-235): per 256 elements, `max` = the element of largest
+ * magnitude (first one on ties), iscale = -127/max, q = clamp(rint(iscale*x)), 16 sums of
+ * 16 consecutive q, scale = 1/iscale; an all-zero block gives zeros and scale 0. */
+void ds4o_quantize_q8_K_rows(const float *x, int8_t *xq, float *xscale, int16_t *xbsums, int64_t n_blocks);
+
 /* ---- SwiGLU ---------------------------------------------------------------- */
 /* gate/up: [n_tokens][k][n]; weights (nullable): [n_tokens][k];
  * combine != 0: out[n_tokens][n] = sum over slots in order; else out[n_tokens][k][n]. */
@@ -136,6 +149,13 @@ void ds4o_hc_pre_rows(const float *residual_hc, const uint16_t *fn_f16,
 void ds4o_hc_post_rows(const float *block_out, const float *block_out2,
                        const float *residual_hc, const float *post, const float *comb,
                        float *out_hc, int64_t n_tokens, int n_embd);
+/* Output HC head (cuda/output_head.cu:62-149): RMS over the 4*n_embd block, 4-row f16
+ * matvec, w[h] = sigmoid(pre[h]*scale[0] + base[h]) + eps, out = sum_h x[h]*w[h] in order.
+ * When norm_w != NULL the output RMSNorm that follows it (cuda/forward_token.cu:211,
+ * cuda/norm.cu:52-105) is applied to `out` and written to normed. */
+void ds4o_output_hc_head_rows(const float *residual_hc, const uint16_t *fn_f16, const float *scale1,
+                              const float *base4, const float *norm_w, float *out, float *normed,
+                              int64_t n_tokens, int n_embd, float eps);
 /* Benchmark config "Sinkhorn mixing": logits[t][16] -> comb -> mix 4 streams. */
 void ds4o_hc_sinkhorn_mix_rows(const float *logits, const float *residual_hc,
                                float *out_hc, float *comb_out, int64_t n_tokens,

@@ -180,6 +180,51 @@ def rope_fp8_store_rows(kv, pos, params, n_rot, scale_mode, n_slots=None, slots=
     return codes, scales, tail, rope_out
 
 
+def f16_round(x):
+    x = _f32(x)
+    y = np.empty_like(x)
+    _call("ds4o_f16_round", x, y, x.size)
+    return y
+
+
+def kv_rows_to_raw(kv, pos, params, n_rot=64, norm_w=None, eps=1e-6):
+    """The reference's KV row chain: kv_norm -> RoPE -> FP8 round trip -> f16 round."""
+    kv = _f32(kv)
+    x = rms_norm_rows(kv, norm_w, eps=eps)[0] if norm_w is not None else kv
+    x = rope_rows(x[:, None, :], pos, params, n_rot=n_rot)[:, 0, :]
+    return f16_round(fp8_kv_round_trip_rows(x, n_rot=n_rot))
+
+
+def swa_window_push(window, n_raw, new_rows):
+    """One row at a time, as cuda/forward_layer.cu:941-972 does; returns (window, n_raw)."""
+    window = window.copy()
+    cap = window.shape[0]
+    for row in f16_round(new_rows):
+        if n_raw < cap:
+            window[n_raw] = row
+            n_raw += 1
+        else:
+            window[:-1] = f16_round(window[1:])
+            window[-1] = row
+    return window, n_raw
+
+
+def quantize_q8_0_rows(x):
+    x = _f32(x).ravel()
+    nb = x.size // 32
+    xq, xs = np.empty(nb * 32, dtype=np.int8), np.empty(nb, dtype=np.float32)
+    _call("ds4o_quantize_q8_0_rows", x, xq, xs, nb)
+    return xq, xs
+
+
+def quantize_q8_K_rows(x):
+    x = _f32(x).ravel()
+    nb = x.size // 256
+    xq, xs, bs = np.empty(nb * 256, dtype=np.int8), np.empty(nb, dtype=np.float32), np.empty(nb * 16, dtype=np.int16)
+    _call("ds4o_quantize_q8_K_rows", x, xq, xs, bs, nb)
+    return xq, xs, bs
+
+
 def swiglu_rows(gate, up, weights=None, mode=GLU_PLAIN, clamp=0.0, combine=False):
     gate, up = _f32(gate), _f32(up)
     T, k, n = gate.shape
@@ -219,6 +264,16 @@ def hc_pre_rows(resid, fn_f16, scale3, base24, iters=20, eps=1e-6):
     _call("ds4o_hc_pre_rows", resid, np.ascontiguousarray(fn_f16).view(np.uint16), _f32(scale3),
           _f32(base24), post, comb, out, mix, T, _i(n), _i(iters), float(eps))
     return post, comb, out, mix
+
+
+def output_hc_head_rows(resid, fn_f16, scale1, base4, norm_w=None, eps=1e-6):
+    resid = _f32(resid)
+    T, _, n = resid.shape
+    out = np.empty((T, n), dtype=np.float32)
+    normed = np.empty((T, n), dtype=np.float32) if norm_w is not None else None
+    _call("ds4o_output_hc_head_rows", resid, np.ascontiguousarray(fn_f16).view(np.uint16), _f32(scale1),
+          _f32(base4), None if norm_w is None else _f32(norm_w), out, normed, T, _i(n), float(eps))
+    return out, normed
 
 
 def hc_post_rows(block_out, resid, post, comb, block_out2=None):

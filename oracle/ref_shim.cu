@@ -14,6 +14,7 @@
 #include "glu.cuh"
 #include "hc_sinkhorn.cuh"
 #include "norm.cuh"
+#include "output_head.cuh"
 #include "rope.cuh"
 
 #define S(s) static_cast<cudaStream_t>(s)
@@ -68,6 +69,11 @@ void ds4ref_hc_attn_pre_v2_f32(const float *residual_hc, const uint16_t *fn, con
 void ds4ref_hc_post_f32(const float *block_out, const float *residual_hc, const float *post,
                         const float *comb, float *out_hc, int n_hc, int n_embd, void *s) {
     launch_hc_post_f32(block_out, residual_hc, post, comb, out_hc, n_hc, n_embd, S(s));
+}
+
+void ds4ref_output_hc_head_f32(const float *residual_hc, const uint16_t *fn, const float *scale, const float *base,
+                               float *out, int n_embd, int n_hc, float eps, void *s) {
+    launch_output_hc_head_f32(residual_hc, fn, scale, base, out, n_embd, n_hc, eps, S(s));
 }
 
 // ---- per-token loops, issued from C++ the way the reference's forward pass issues them

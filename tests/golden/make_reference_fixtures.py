@@ -36,6 +36,11 @@ def golden_inputs():
     w = inputs.hc_pre_weights(6, 4096)
     d["hc_fn"], d["hc_scale"], d["hc_base"] = w["fn"], w["scale"], w["base"]
     d["add_b"] = inputs.normal(g, (4096,))
+    # appended after the first fixture was made: draws above keep their values
+    d["head_fn"] = (g.standard_normal((4, 16384), dtype=np.float32) / 128).astype(np.float16)
+    d["head_scale"] = inputs.uniform(g, (1,), 0.5, 1.5)
+    d["head_base"] = inputs.normal(g, (4,), 0.5)
+    d["out_norm_w"] = inputs.uniform(g, (4096,), 0.5, 1.5)
     return d
 
 
@@ -92,6 +97,12 @@ def main(out_path):
     hp = torch.empty(4, 4096, device="cuda")
     ref_lib.call("hc_post_f32", dev(d["hc_block"][0]), resid, post, comb, hp, 4, 4096)
     out["hc_post"] = hp.cpu().numpy()
+    ho = torch.empty(4096, device="cuda")
+    ref_lib.call("output_hc_head_f32", resid, dev(d["head_fn"]), dev(d["head_scale"]), dev(d["head_base"]), ho,
+                 4096, 4, 1e-6)
+    hn = torch.empty(4096, device="cuda")
+    ref_lib.call("rms_norm_f32", ho, dev(d["out_norm_w"]), hn, 4096, 1e-6)
+    out["output_hc_head"], out["output_norm"] = ho.cpu().numpy(), hn.cpu().numpy()
     torch.cuda.synchronize()
     meta = {"gpu": torch.cuda.get_device_name(0), "cuda": torch.version.cuda}
     np.savez_compressed(out_path, __digests__=np.array(repr(digest(d))), __meta__=np.array(repr(meta)), **out)

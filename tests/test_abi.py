@@ -21,7 +21,7 @@ def lib():
 def _declared(header: str):
     text = (ROOT / "include" / header).read_text()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(ds4b200_[a-z0-9_]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(ds4b200_[A-Za-z0-9_]+)\s*\(", text)))
 
 
 def test_every_declared_c_symbol_is_exported_and_bound(lib):
@@ -52,6 +52,7 @@ def test_reference_cxx_launchers_are_exported_with_reference_signatures():
         "ds4cuda::launch_hc_attn_pre_v2_f32(float const*, unsigned short const*, float const*, float const*, float*, float*, float*, int, int, int, float, float*, float*, CUstream_st*)",
         "ds4cuda::launch_hc_ffn_pre_v2_f32(float const*, unsigned short const*, float const*, float const*, float*, float*, float*, int, int, int, float, float*, float*, CUstream_st*)",
         "ds4cuda::launch_hc_post_f32(float const*, float const*, float const*, float const*, float*, int, int, CUstream_st*)",
+        "ds4cuda::launch_output_hc_head_f32(float const*, unsigned short const*, float const*, float const*, float*, int, int, float, CUstream_st*)",
     ]
     for sig in want:
         assert sig in out, f"missing drop-in symbol: {sig}"
@@ -131,7 +132,7 @@ CALLERS = ["forward_layer.cu", "forward_token.cu", "forward_batch.cu", "compress
 STAR = ("launch_rms_norm_f32", "launch_rms_norm_batch_f32", "launch_add_f32", "launch_tail_rope_yarn_f32",
         "launch_tail_rope_yarn_inverse_f32", "launch_fp8_kv_quantize_round_trip_f32", "launch_silu_mul_f32",
         "launch_embed_token_f16_to_f32", "launch_hc_attn_pre_f32", "launch_hc_attn_pre_v2_f32",
-        "launch_hc_ffn_pre_v2_f32", "launch_hc_post_f32")
+        "launch_hc_ffn_pre_v2_f32", "launch_hc_post_f32", "launch_output_hc_head_f32")
 
 
 @pytest.mark.skipif(not (REFERENCE / "cuda" / "forward_layer.cu").exists(), reason="reference tree not mounted")
@@ -150,6 +151,6 @@ def test_reference_callers_resolve_their_launchers_in_our_library(tmp_path):
         for line in subprocess.run(["nm", "-u", str(obj)], capture_output=True, text=True, check=True).stdout.split():
             if line.startswith("_ZN7ds4cuda") and any(f"{len(n)}{n}E" in line for n in STAR):
                 wanted.add(line)
-    assert len(wanted) >= 11, wanted          # every launcher of the path is imported by some caller
+    assert len(wanted) >= 12, wanted          # every launcher of the path is imported by some caller
     missing = sorted(w for w in wanted if w not in defined)
     assert not missing, f"reference callers import launchers we do not define: {missing}"

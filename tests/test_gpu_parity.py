@@ -509,6 +509,135 @@ def test_hc_post_and_sinkhorn_mix_rows(ops, oracle, ref, n_embd, T):
         assert_bits(host(mine), host(r), "hc_post vs reference kernel, bit for bit")
 
 
+@pytest.mark.parametrize("n_embd,T", [(4096, 7), (1024, 3), (8192, 2), (100, 3)])
+def test_output_hc_head_rows(ops, oracle, ref, n_embd, T):
+    g = inputs.rng(720 + n_embd)
+    resid = inputs.normal(g, (T, 4, n_embd))
+    fn = (g.standard_normal((4, 4 * n_embd), dtype=np.float32) / np.sqrt(4 * n_embd)).astype(np.float16)
+    scale, base, nw = inputs.uniform(g, (1,), 0.5, 1.5), inputs.normal(g, (4,), 0.5), inputs.uniform(g, (n_embd,), 0.5, 1.5)
+    want, want_n = oracle.output_hc_head_rows(resid, fn, scale, base, norm_w=nw)
+    out, normed = ops.output_hc_head_rows(dev(resid), dev(fn), dev(scale), dev(base), norm_w=dev(nw))
+    assert_close(host(out), want, what="output head")
+    assert_close(host(normed), want_n, what="output head + output norm")
+    only_n = ops.output_hc_head_rows(dev(resid), dev(fn), dev(scale), dev(base), norm_w=dev(nw), want_out=False)[1]
+    assert_bits(host(only_n), host(normed), "normed only")
+    if n_embd == 4096:
+        from ds4cuda_b200 import _lib
+        L = _lib.load()
+        d = [dev(resid[0]), dev(fn), dev(scale), dev(base)]
+        mine = torch.empty(n_embd, device="cuda")
+        L.ds4b200_launch_output_hc_head_f32(*[t.data_ptr() for t in d], mine.data_ptr(), n_embd, 4, 1e-6, None)
+        assert_close(host(mine), want[0], what="launch_output_hc_head_f32")
+        if ref:
+            r = torch.empty(n_embd, device="cuda")
+            ref.call("output_hc_head_f32", *d, r, n_embd, 4, 1e-6)
+            assert_close(host(mine), host(r), what="output head vs reference kernel")
+
+
+# ------------------------------------------------------------------ raw KV rows and window
+
+@pytest.mark.parametrize("il", [0, 2])
+def test_kv_rows_to_raw_chain(ops, oracle, ref, il):
+    g = inputs.rng(830 + il)
+    T = 200
+    kv, w = inputs.normal(g, (T, 512), 1.5), inputs.uniform(g, (512,), 0.5, 1.5)
+    pos = g.permutation(4096)[:T].astype(np.int32)
+    slots = g.permutation(256)[:T].astype(np.int32)
+    p = oracle.rope_params_for_layer(il)
+    raw = torch.full((256, 512), -7.0, device="cuda")
+    ops.kv_rows_to_raw(dev(kv), dev(pos), to_ops_params(ops, p), raw, slots=dev(slots), norm_w=dev(w))
+    want = oracle.kv_rows_to_raw(kv, pos, p, norm_w=w)
+    got = host(raw)[slots]
+    untouched = np.setdiff1d(np.arange(256), slots)
+    assert (host(raw)[untouched] == -7.0).all()
+    # f16 rounding and the FP8 grid quantise the chain: values agree except where a last-bit
+    # difference upstream crossed a rounding boundary; then they differ by one grid step
+    assert (got != want).mean() < 2e-3
+    assert np.abs(got - want).max() <= 0.07 * np.abs(want).max()
+    assert_bits(oracle.f16_round(got), got, "rows are f16-representable")
+    if ref:
+        # the reference's own four launches on the same row
+        x = dev(kv[:1].copy())
+        normed, roped, rt = torch.empty_like(x), torch.empty_like(x), torch.empty_like(x)
+        ref.call("rms_norm_f32", x, dev(w), normed, 512, 1e-6)
+        ref.call("tail_rope_yarn_f32", normed, roped, 1, 512, 64, int(pos[0]), il)
+        ref.call("fp8_kv_quantize_round_trip_f32", roped, rt, 1, 512, 64)
+        want0 = rt.half().float()
+        diff = (raw[int(slots[0])] != want0[0]).float().mean().item()
+        assert diff < 0.01
+
+
+@pytest.mark.parametrize("n_raw,n_new", [(0, 5), (5, 3), (100, 28), (100, 29), (128, 1), (128, 40), (60, 300), (0, 128)])
+def test_swa_window_push_rows(ops, oracle, n_raw, n_new):
+    g = inputs.rng(840 + n_raw + n_new)
+    cap, D = 128, 512
+    win = np.zeros((cap, D), dtype=np.float32)
+    win[:n_raw] = oracle.f16_round(inputs.normal(g, (n_raw, D)))
+    rows = inputs.normal(g, (n_new, D))
+    dwin = dev(win)
+    after = ops.swa_window_push_rows(dwin, n_raw, dev(rows))
+    want, want_n = oracle.swa_window_push(win, n_raw, rows)
+    assert after == want_n
+    assert_bits(host(dwin)[:after], want[:want_n], "window rows")
+    assert_bits(host(dwin)[after:], win[after:], "rows beyond the window untouched")
+
+
+# ------------------------------------------------------------------ activation quantisers
+
+@pytest.mark.parametrize("n", [64, 4096, 32 * 1001, 1 << 20])
+def test_quantize_q8_0_bit_exact(ops, oracle, n):
+    g = inputs.rng(800 + n % 89)
+    x = inputs.normal(g, n, 2.0)
+    x[:32] = 0.0                                            # all-zero block: d = 0, id = 0
+    x[32:40] = [1.5, -1.5, 0.5, -0.5, 2.5, -2.5, 127.0, -127.0]     # exact ties at d = 1
+    xq, xs = ops.quantize_q8_0_rows(dev(x))
+    wq, ws = oracle.quantize_q8_0_rows(x)
+    assert_bits(host(xs), ws, "Q8_0 scales")
+    assert_bits(host(xq), wq, "Q8_0 values")
+    buf = torch.empty(n + 1, device="cuda")
+    buf[1:].copy_(dev(x))
+    xq2, xs2 = ops.quantize_q8_0_rows(buf[1:])               # 4-byte aligned input: scalar path
+    assert_bits(host(xq2), wq, "Q8_0 values, unaligned input")
+    assert_bits(host(xs2), ws, "Q8_0 scales, unaligned input")
+
+
+@pytest.mark.parametrize("n_blocks", [1, 7, 4096])
+def test_quantize_q8_K_bit_exact(ops, oracle, n_blocks):
+    g = inputs.rng(810 + n_blocks)
+    x = inputs.normal(g, n_blocks * 256, 2.0)
+    x[:256] = 0.0                                           # all-zero block
+    if n_blocks > 1:
+        x[256:512] = np.clip(x[256:512], -3, 3)
+        x[256 + 200] = -3.5                                 # equal magnitudes, opposite signs: the first wins
+        x[256 + 17] = 3.5
+    xq, xs, bs = ops.quantize_q8_K_rows(dev(x))
+    wq, ws, wb = oracle.quantize_q8_K_rows(x)
+    assert_bits(host(xs), ws, "Q8_K scales")
+    assert_bits(host(xq), wq, "Q8_K values")
+    assert_bits(host(bs), wb, "Q8_K partial sums")
+    if n_blocks > 1:
+        assert ws[1] < 0                                    # scale = -max/127 with max = +3.5 (index 17)
+
+
+@pytest.mark.parametrize("rows,n", [(1, 4096), (5, 1024), (300, 4096), (64, 512), (3, 8192)])
+def test_rms_norm_with_fused_q8_0(ops, oracle, rows, n):
+    g = inputs.rng(820 + rows + n)
+    x, r, w = inputs.normal(g, (rows, n)), inputs.normal(g, (rows, n)), inputs.uniform(g, (n,), 0.5, 1.5)
+    y, ro, xq, xs = ops.rms_norm_q8_0_rows(dev(x), dev(w), residual=dev(r), want_residual=True)
+    want, _, want_ro = oracle.rms_norm_rows(x, w, residual=r, want_residual=True)
+    assert_bits(host(ro), want_ro, "residual sum")
+    assert_close(host(y), want, what="normed row")
+    # the quantiser is exact on the GPU's own normalised row ...
+    wq, ws = oracle.quantize_q8_0_rows(host(y))
+    assert_bits(host(xq).ravel(), wq, "fused Q8_0 values")
+    assert_bits(host(xs).ravel(), ws, "fused Q8_0 scales")
+    # ... and equals the stand-alone quantiser run on that row
+    xq2, xs2 = ops.quantize_q8_0_rows(y)
+    assert torch.equal(xq2, xq) and torch.equal(xs2.view_as(xs), xs)
+    _, _, xq3, xs3 = ops.rms_norm_q8_0_rows(dev(x), dev(w), residual=dev(r), want_f32=False)
+    assert torch.equal(xq3, xq) and torch.equal(xs3, xs)
+
+
 def test_reference_kernel_library_present(ref):
     """The bit-for-bit comparisons above run only with the reference's kernels rebuilt for sm_100a."""
     if ref is None:

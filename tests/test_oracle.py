@@ -302,3 +302,32 @@ def test_fused_kv_chain_equals_its_parts(oracle):
     assert np.array_equal(rope_out, roped)
     c2, s2, _ = oracle.fp8_encode_rows(roped, 64, oracle.FP8_ROW_AMAX)
     assert np.array_equal(codes, c2) and np.array_equal(scales, s2)
+
+
+def test_f16_round_and_window_push(oracle):
+    g = inputs.rng(24)
+    x = inputs.normal(g, 1000, 3.0)
+    assert np.array_equal(oracle.f16_round(x), x.astype(np.float16).astype(np.float32))
+    assert np.array_equal(oracle.f16_round(oracle.f16_round(x)), oracle.f16_round(x))      # idempotent
+    win = np.zeros((8, 16), dtype=np.float32)
+    rows = inputs.normal(g, (13, 16))
+    w1, n1 = oracle.swa_window_push(win, 0, rows[:5])
+    assert n1 == 5 and np.array_equal(w1[:5], oracle.f16_round(rows[:5])) and not w1[5:].any()
+    w2, n2 = oracle.swa_window_push(w1, n1, rows[5:])
+    assert n2 == 8 and np.array_equal(w2, oracle.f16_round(rows[5:]))                      # the last 8 of 13
+
+
+def test_activation_quantisers(oracle):
+    g = inputs.rng(25)
+    x = inputs.normal(g, 2048, 2.0)
+    q, s = oracle.quantize_q8_0_rows(x)
+    blocks = x.reshape(-1, 32)
+    assert np.array_equal(s, (np.abs(blocks).max(axis=1) / np.float32(127.0)).astype(np.float32))
+    assert np.abs(q.reshape(-1, 32) * s[:, None] - blocks).max() <= s.max() * 0.5 + 1e-7
+    assert (np.abs(q.reshape(-1, 32)).max(axis=1) == 127).all()
+    qk, sk, bk = oracle.quantize_q8_K_rows(x)
+    assert np.array_equal(bk, qk.reshape(-1, 16).astype(np.int32).sum(axis=1).astype(np.int16))
+    assert np.abs(qk.reshape(-1, 256) * sk[:, None] - x.reshape(-1, 256)).max() <= np.abs(sk).max() * 0.5 + 1e-7
+    # the element of largest magnitude maps to -127 * sign(scale) ... i.e. q = -127 and scale = -max/127
+    k = np.abs(x[:256]).argmax()
+    assert qk[k] == -127 and np.isclose(sk[0], -x[k] / 127.0)
