@@ -163,9 +163,9 @@ fp8_round_trip_kernel(const float *kv_in, float *kv_out, int64_t n_rows, int hea
         const float amax = fmaxf(halfwarp_max(amax4(v[j])), kFp8AmaxFloor);
         if (i >= n4) continue;
         if (4 * i < n_nope) {
-            const float scale = pow2_scale(amax);
-            v[j] = make_float4(e4m3_round_trip(v[j].x, scale), e4m3_round_trip(v[j].y, scale),
-                               e4m3_round_trip(v[j].z, scale), e4m3_round_trip(v[j].w, scale));
+            const float scale = pow2_scale(amax), inv = 1.0f / scale;
+            v[j] = make_float4(e4m3_round_trip(v[j].x, scale, inv), e4m3_round_trip(v[j].y, scale, inv),
+                               e4m3_round_trip(v[j].z, scale, inv), e4m3_round_trip(v[j].w, scale, inv));
         }
         st_stream4(yr + 4 * i, v[j]);
     }
@@ -183,9 +183,9 @@ __global__ void fp8_round_trip_scalar_kernel(const float *kv_in, float *kv_out, 
     for (int off = 0; off < n_nope; off += 64) {
         const float a = xr[off + lane], b = xr[off + 32 + lane];
         const float amax = fmaxf(warp_max(fmaxf(fabsf(a), fabsf(b))), kFp8AmaxFloor);
-        const float scale = pow2_scale(amax);
-        yr[off + lane] = e4m3_round_trip(a, scale);
-        yr[off + 32 + lane] = e4m3_round_trip(b, scale);
+        const float scale = pow2_scale(amax), inv = 1.0f / scale;
+        yr[off + lane] = e4m3_round_trip(a, scale, inv);
+        yr[off + 32 + lane] = e4m3_round_trip(b, scale, inv);
     }
     for (int i = n_nope + lane; i < head_dim; i += 32) yr[i] = xr[i];
 }
@@ -284,17 +284,17 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) rope_fp8_store_kernel(StoreA
             const float amax = fmaxf(halfwarp_max(amax4(v[j])), kFp8AmaxFloor);
             if (i >= n4) continue;
             if (4 * i < n_nope) {
-                const float scale = pow2_scale(amax);
+                const float scale = pow2_scale(amax), inv = 1.0f / scale;     // power of two: x*inv == x/scale
                 if (a.scales && (lane & 15) == 0) a.scales[slot * n_scales + (i >> 4)] = scale;
                 if (a.codes) {
-                    const float4 q = make_float4(clamp448(v[j].x / scale), clamp448(v[j].y / scale),
-                                                 clamp448(v[j].z / scale), clamp448(v[j].w / scale));
+                    const float4 q = make_float4(clamp448(v[j].x * inv), clamp448(v[j].y * inv),
+                                                 clamp448(v[j].z * inv), clamp448(v[j].w * inv));
                     __stcs(code_row + i, e4m3_encode4(q));
                 }
                 if (a.raw_out)
                     st_stream4(a.raw_out + slot * head_dim + 4 * i,
-                               f16_round4(make_float4(e4m3_round_trip(v[j].x, scale), e4m3_round_trip(v[j].y, scale),
-                                                      e4m3_round_trip(v[j].z, scale), e4m3_round_trip(v[j].w, scale))));
+                               f16_round4(make_float4(e4m3_round_trip(v[j].x, scale, inv), e4m3_round_trip(v[j].y, scale, inv),
+                                                      e4m3_round_trip(v[j].z, scale, inv), e4m3_round_trip(v[j].w, scale, inv))));
             } else {
                 if (a.codes) __stcs(code_row + i, 0u);
                 if (a.tail_out) st_stream4(a.tail_out + slot * a.n_rot + (4 * i - n_nope), v[j]);
@@ -308,35 +308,39 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) rope_fp8_store_kernel(StoreA
 // The reference keeps the last `cap` rows in a linear window: append while there is room,
 // otherwise move every row down by one and write the new row last, one token per call
 // (cuda/forward_layer.cu:159-190, :941-972).  Here n_new rows enter at once: the window
-// afterwards holds the last min(cap, n_raw + n_new) rows of old ++ new.  Columns are
-// independent, so one thread owns one float4 column and walks the rows upwards in batches
-// of 16: every batch is read completely before it is written, and it only reads rows at or
-// above the ones it writes, so the move is safe in place.  New rows get the f16 rounding;
-// old rows already have it.
-__global__ void swa_window_push_kernel(float *raw_kv, int cap, int n_raw, const float *new_rows, int n_new,
-                                       int head_dim) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= (head_dim >> 2)) return;
+// afterwards holds the last min(cap, n_raw + n_new) rows of old ++ new.  New rows get the
+// f16 rounding; old rows already have it.
+__global__ void __launch_bounds__(1024)
+swa_window_push_kernel(float *raw_kv, int cap, int n_raw, const float *new_rows, int n_new, int head_dim) {
+    const int n4 = head_dim >> 2;
     const int total = n_raw + n_new;
     const int kept = total < cap ? total : cap;              // rows in the window afterwards
     const int first = total - kept;                          // index in old ++ new of window row 0
-    constexpr int kBatch = 16;
-    for (int r0 = (first == 0 ? n_raw : 0); r0 < kept; r0 += kBatch) {      // pure append: old rows stay
+    // One CTA.  A pass moves up to blockDim.x * kBatch float4s: every thread loads its share,
+    // the CTA synchronises, every thread stores.  Passes go upwards through the window and a
+    // pass only reads rows at or above the ones it writes, so the move is safe in place.
+    constexpr int kBatch = 8;
+    const int64_t begin = (int64_t)(first == 0 ? n_raw : 0) * n4;          // pure append: old rows stay
+    const int64_t end = (int64_t)kept * n4;
+    for (int64_t base = begin; base < end; base += (int64_t)blockDim.x * kBatch) {
         float4 v[kBatch];
 #pragma unroll
         for (int b = 0; b < kBatch; ++b) {
-            const int r = r0 + b, src = first + r;
-            if (r >= kept) break;
-            v[b] = src < n_raw ? *reinterpret_cast<const float4 *>(raw_kv + (int64_t)src * head_dim + 4 * c)
-                               : f16_round4(__ldg(reinterpret_cast<const float4 *>(
-                                     new_rows + (int64_t)(src - n_raw) * head_dim + 4 * c)));
+            const int64_t e = base + (int64_t)b * blockDim.x + threadIdx.x;
+            if (e < end) {
+                const int r = (int)(e / n4), c = (int)(e - (int64_t)r * n4), src = first + r;
+                v[b] = src < n_raw ? *reinterpret_cast<const float4 *>(raw_kv + (int64_t)src * head_dim + 4 * c)
+                                   : f16_round4(__ldg(reinterpret_cast<const float4 *>(
+                                         new_rows + (int64_t)(src - n_raw) * head_dim + 4 * c)));
+            }
         }
+        __syncthreads();
 #pragma unroll
         for (int b = 0; b < kBatch; ++b) {
-            const int r = r0 + b;
-            if (r >= kept) break;
-            *reinterpret_cast<float4 *>(raw_kv + (int64_t)r * head_dim + 4 * c) = v[b];
+            const int64_t e = base + (int64_t)b * blockDim.x + threadIdx.x;
+            if (e < end) *reinterpret_cast<float4 *>(raw_kv + 4 * e) = v[b];
         }
+        __syncthreads();
     }
 }
 
@@ -465,8 +469,7 @@ void rope_fp8_store_rows(const float *kv_in, int64_t n_rows, int head_dim, int n
 void swa_window_push_rows(float *raw_kv, int cap, int n_raw, const float *new_rows, int n_new, int head_dim,
                           cudaStream_t s) {
     if (n_new <= 0 || cap <= 0) return;
-    const int n4 = head_dim >> 2;
-    swa_window_push_kernel<<<(n4 + 31) / 32, 32, 0, s>>>(raw_kv, cap, n_raw, new_rows, n_new, head_dim);
+    swa_window_push_kernel<<<1, 1024, 0, s>>>(raw_kv, cap, n_raw, new_rows, n_new, head_dim);
 }
 
 void e4m3_encode(const float *x, uint8_t *codes, int64_t n, cudaStream_t s) {
