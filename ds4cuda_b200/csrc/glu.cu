@@ -57,7 +57,7 @@ __device__ __forceinline__ float4 glu4(float4 g, float4 u, float clamp) {
 
 // K > 0: compile-time slot count (loads fully unrolled); K == 0: runtime k.
 template <int K, int MODE, bool FAST>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 swiglu_vec_kernel(const float *__restrict__ gate, const float *__restrict__ up,
                   const float *__restrict__ weights, float *__restrict__ out, int64_t n_tokens,
                   int k_rt, int n4, float clamp, int combine) {
