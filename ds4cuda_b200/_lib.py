@@ -48,6 +48,7 @@ SIGNATURES = {
     "ds4b200_version": (C.c_char_p, []),
     "ds4b200_last_error": (C.c_char_p, []),
     "ds4b200_device_status": (_I, []),
+    "ds4b200_selftest_bounded_wait": (_I, [_I, _P, _P]),
     "ds4b200_rope_params_for_layer": (None, [_I, _I, _RP]),
     "ds4b200_rope_params_explicit": (None, [_F, _F, _I, _I, _RP]),
     # drop-in launchers

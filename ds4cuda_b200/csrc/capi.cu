@@ -50,6 +50,13 @@ int ds4b200_device_status(void) {
     return v;
 }
 
+int ds4b200_selftest_bounded_wait(int max_polls, int *gave_up, void *stream) {
+    REQUIRE(gave_up, "selftest_bounded_wait: null pointer");
+    REQUIRE(max_polls >= 1 && max_polls <= (1 << 16), "selftest_bounded_wait: max_polls must be in [1, 65536]");
+    ds4b200::selftest_bounded_wait(max_polls, gave_up, STREAM(stream));
+    return launched("selftest_bounded_wait");
+}
+
 int ds4b200_add_f32(const float *a, const float *b, float *y, int64_t n, void *stream) {
     REQUIRE(n >= 0, "add: n < 0");
     if (n == 0) return 0;

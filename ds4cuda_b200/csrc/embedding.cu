@@ -227,6 +227,20 @@ void embed_gather_rows(const void *table, int table_dtype, const int32_t *ids, i
     }
 }
 
+// A wait that nothing will ever satisfy, with a short poll limit: it must give up, raise
+// the status bit and let the kernel end normally.  Used by the self-test of the bounded wait.
+__global__ void wait_gives_up_kernel(int max_polls, int *gave_up) {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) mbar_init(&bar, 1);
+    __syncthreads();
+    const bool done = mbar_wait_bounded(&bar, 0, &g_status_word, max_polls);
+    if (threadIdx.x == 0) *gave_up = done ? 0 : 1;
+}
+
+void selftest_bounded_wait(int max_polls, int *gave_up_dev, cudaStream_t s) {
+    wait_gives_up_kernel<<<1, 32, 0, s>>>(max_polls, gave_up_dev);
+}
+
 int read_and_clear_device_status() {
     int v = 0, zero = 0;
     if (cudaDeviceSynchronize() != cudaSuccess) return -5;

@@ -31,6 +31,7 @@ void embed_gather_rows(const void *table, int table_dtype, const int32_t *ids, i
                        const float *norm_w, float eps, float *out_rows, int n_replicas,
                        float *normed_f32, uint16_t *normed_bf16, cudaStream_t s);
 int read_and_clear_device_status();   // embedding.cu owns the status word
+void selftest_bounded_wait(int max_polls, int *gave_up_dev, cudaStream_t s);
 
 // pos == nullptr: every token uses single_pos.
 void rope_rows(const float *x_in, float *x_out, int64_t n_tokens, int n_heads, int head_dim,

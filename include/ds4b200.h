@@ -67,6 +67,11 @@ const char *ds4b200_last_error(void);
  * reading clears it.  Synchronises the device.  Negative errno on failure. */
 int ds4b200_device_status(void);
 
+/* Self-test of the bounded device-side wait: a one-warp kernel waits on a barrier that
+ * nothing signals, gives up after max_polls (<= 65536) polls, writes 1 to *gave_up (device
+ * int) and ends normally; ds4b200_device_status() then reports bit 0.  Never hangs. */
+int ds4b200_selftest_bounded_wait(int max_polls, int *gave_up, void *stream);
+
 /* Host-side routing helpers (no device work).
  * for_layer: the reference's rule, cuda/rope.cu:214-250 (theta_scale left 0). */
 void ds4b200_rope_params_for_layer(int il, int n_rot, ds4b200_rope_params *out);

@@ -112,6 +112,19 @@ def test_checked_entry_points_reject_bad_arguments_without_a_gpu(lib):
     assert b"geometry" in lib.ds4b200_last_error()
 
 
+def test_path_create_reports_allocation_or_device_failure_instead_of_crashing(lib):
+    """Host-side failure path: without a usable device (this CPU box) or with a request no
+    device can hold, path_create returns NULL and says which step failed."""
+    from ds4cuda_b200._lib import PathConfig, RopeParams
+    cfg = PathConfig(n_tokens=1 << 30, n_embd=8192, vocab=1 << 30, table_dtype=0, kv_dim=1024, n_rot=64,
+                     n_slots=1 << 30, ff_dim=4096, top_k=8, max_layers=64, sinkhorn_iters=20, fp8_scale_mode=1,
+                     glu_mode=1, glu_fast_exp=0, use_graph=0, eps=1e-6, clamp=10.0,
+                     rope=RopeParams(10000.0, 0.75, 1.0, 0.0, 1.0, 0.0, 0.0))
+    assert lib.ds4b200_path_create(C.byref(cfg)) is None
+    msg = lib.ds4b200_last_error()
+    assert b"path_create" in msg and (b"cudaMalloc" in msg or b"cudaStreamCreate" in msg)
+
+
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     from ds4cuda_b200 import _lib
     monkeypatch.setattr(_lib, "_lib", None)

@@ -645,6 +645,22 @@ def test_reference_kernel_library_present(ref):
     assert ref.lib() is not None
 
 
+def test_bounded_wait_gives_up_and_reports_status(ops):
+    """Failure detection without a fault: a wait nothing satisfies runs out of polls, the kernel
+    returns, the status word says so, and the context stays usable."""
+    from ds4cuda_b200 import _lib
+    L = _lib.load()
+    assert ops.device_status() == 0
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert L.ds4b200_selftest_bounded_wait(2000, flag.data_ptr(), None) == 0
+    torch.cuda.synchronize()
+    assert int(flag.item()) == 1
+    assert ops.device_status() == 1          # bit 0: a wait on a bulk copy gave up
+    assert ops.device_status() == 0          # reading cleared it
+    a = torch.ones(8, device="cuda")
+    assert torch.equal(ops.add(a, a), a * 2)  # the context is alive
+
+
 def test_empty_inputs_are_no_ops(ops):
     e = torch.empty(0, device="cuda")
     assert ops.add(e, e).numel() == 0
