@@ -110,4 +110,4 @@ def main(out_path):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else str(ROOT / "gpurun_out" / "reference_kernels_config1.npz"))
+    main(sys.argv[1] if len(sys.argv) > 1 else str(ROOT / "tests" / "golden" / "reference_kernels_config1.npz"))
