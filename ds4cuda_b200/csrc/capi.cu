@@ -192,6 +192,24 @@ int ds4b200_rope_fp8_store_rows(const float *kv_in, int64_t n_rows, int head_dim
     return launched("rope_fp8_store_rows");
 }
 
+int ds4b200_fp8_cache_load_rows(const uint8_t *codes, const float *scales, const float *tail,
+                                const int32_t *slots, int64_t n_rows, int head_dim, int n_rot,
+                                int scale_mode, int f16_round, float *out, void *stream) {
+    REQUIRE(n_rows >= 0, "fp8_cache_load_rows: n_rows < 0");
+    if (n_rows == 0) return 0;
+    REQUIRE(codes && scales && out, "fp8_cache_load_rows: null pointer");
+    REQUIRE(head_dim > 0 && head_dim <= 1024 && head_dim % 4 == 0 && n_rot >= 0 && n_rot <= head_dim && n_rot % 4 == 0,
+            "fp8_cache_load_rows: head_dim and n_rot must be multiples of 4, head_dim at most 1024");
+    REQUIRE(scale_mode == DS4B200_FP8_BLOCK64_POW2 || scale_mode == DS4B200_FP8_ROW_AMAX,
+            "fp8_cache_load_rows: unknown scale mode");
+    REQUIRE(scale_mode != DS4B200_FP8_BLOCK64_POW2 || ((head_dim - n_rot) % 64 == 0 && (tail || n_rot == 0)),
+            "fp8_cache_load_rows: BLOCK64_POW2 needs a prefix that is a multiple of 64 and the f32 tail");
+    REQUIRE(a4(codes) && a16(tail) && a16(out), "fp8_cache_load_rows: codes need 4-byte, tail and out 16-byte alignment");
+    ds4b200::fp8_cache_load_rows(codes, scales, tail, slots, n_rows, head_dim, n_rot, scale_mode, f16_round, out,
+                                 STREAM(stream));
+    return launched("fp8_cache_load_rows");
+}
+
 int ds4b200_kv_rows_to_raw_f32(const float *kv_in, int64_t n_rows, int head_dim, int n_rot, const int32_t *pos,
                                const ds4b200_rope_params *params, const float *norm_w, float eps,
                                const int32_t *slots, float *raw_out, void *stream) {

@@ -47,6 +47,11 @@ void rope_fp8_store_rows(const float *kv_in, int64_t n_rows, int head_dim, int n
                          float *scales, float *tail_out, float *rope_out, cudaStream_t s,
                          float *raw_out = nullptr);
 
+// Read side of the FP8 byte cache: rows at slots[] -> f32 (optionally f16-rounded).
+void fp8_cache_load_rows(const uint8_t *codes, const float *scales, const float *tail, const int32_t *slots,
+                         int64_t n_rows, int head_dim, int n_rot, int scale_mode, int f16_out, float *out,
+                         cudaStream_t s);
+
 // raw_kv window [cap][head_dim]: push n_new rows (f16-rounded), dropping the oldest.
 void swa_window_push_rows(float *raw_kv, int cap, int n_raw, const float *new_rows, int n_new, int head_dim,
                           cudaStream_t s);

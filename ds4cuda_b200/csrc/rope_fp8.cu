@@ -304,6 +304,47 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) rope_fp8_store_kernel(StoreA
     }
 }
 
+// ------------------------------ FP8 cache read -------------------------------
+// The read side of the byte cache: row r = slot slots[r] -> f32.  BLOCK64_POW2: prefix =
+// code value x block scale (exactly what the reference's round trip leaves in its f32 cache,
+// cuda/fp8_kv.cu:176-180), tail = the stored f32 tail.  ROW_AMAX: every element = code value
+// x row scale.  One warp per row, 32-bit code loads, 128-bit stores.
+template <int VPT>
+__global__ void __launch_bounds__(kRowsPerCta * 32)
+fp8_cache_load_kernel(const uint8_t *__restrict__ codes, const float *__restrict__ scales,
+                      const float *__restrict__ tail, const int32_t *__restrict__ slots, int64_t n_rows,
+                      int head_dim, int n_rot, int scale_mode, int f16_out, float *__restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * kRowsPerCta + (threadIdx.x >> 5);
+    if (row >= n_rows) return;
+    const int n4 = head_dim >> 2, n_nope = head_dim - n_rot;
+    const int64_t slot = slots ? slots[row] : row;
+    const uint32_t *code_row = reinterpret_cast<const uint32_t *>(codes + slot * head_dim);
+    const int n_scales = scale_mode == DS4B200_FP8_BLOCK64_POW2 ? n_nope >> 6 : 1;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = lane + 32 * j;
+        if (i >= n4) continue;
+        float4 v;
+        if (scale_mode == DS4B200_FP8_BLOCK64_POW2 && 4 * i >= n_nope) {
+            v = ld_stream4(tail + slot * n_rot + (4 * i - n_nope));
+        } else {
+            const uint32_t c = __ldcs(code_row + i);
+            const float sc = __ldg(scales + slot * n_scales + (scale_mode == DS4B200_FP8_BLOCK64_POW2 ? (i >> 4) : 0));
+            float e[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint32_t b = (c >> (8 * k)) & 0xffu;
+                const float m = e4m3_magnitude(b & 0x7fu);
+                e[k] = ((b & 0x80u) ? -m : m) * sc;
+            }
+            v = make_float4(e[0], e[1], e[2], e[3]);
+        }
+        if (f16_out) v = f16_round4(v);
+        st_stream4(out + row * head_dim + 4 * i, v);
+    }
+}
+
 // --------------------------- sliding raw-KV window ---------------------------
 // The reference keeps the last `cap` rows in a linear window: append while there is room,
 // otherwise move every row down by one and write the new row last, one token per call
@@ -464,6 +505,21 @@ void rope_fp8_store_rows(const float *kv_in, int64_t n_rows, int head_dim, int n
     else if (vpt <= 2) rope_fp8_store_kernel<2><<<grid, kRowsPerCta * 32, 0, s>>>(a);
     else if (vpt <= 4) rope_fp8_store_kernel<4><<<grid, kRowsPerCta * 32, 0, s>>>(a);
     else rope_fp8_store_kernel<8><<<grid, kRowsPerCta * 32, 0, s>>>(a);
+}
+
+void fp8_cache_load_rows(const uint8_t *codes, const float *scales, const float *tail, const int32_t *slots,
+                         int64_t n_rows, int head_dim, int n_rot, int scale_mode, int f16_out, float *out,
+                         cudaStream_t s) {
+    if (n_rows <= 0) return;
+    const int vpt = ((head_dim >> 2) + 31) / 32;
+    const unsigned grid = warp_row_grid(n_rows);
+#define DS4B200_LOAD(V) fp8_cache_load_kernel<V><<<grid, kRowsPerCta * 32, 0, s>>>( \
+        codes, scales, tail, slots, n_rows, head_dim, n_rot, scale_mode, f16_out, out)
+    if (vpt <= 1) DS4B200_LOAD(1);
+    else if (vpt <= 2) DS4B200_LOAD(2);
+    else if (vpt <= 4) DS4B200_LOAD(4);
+    else DS4B200_LOAD(8);
+#undef DS4B200_LOAD
 }
 
 void swa_window_push_rows(float *raw_kv, int cap, int n_raw, const float *new_rows, int n_new, int head_dim,

@@ -18,7 +18,7 @@ __all__ = [
     "FP8_BLOCK64_POW2", "FP8_ROW_AMAX", "GLU_CLAMP_REF", "GLU_CLAMP_SYM", "GLU_PLAIN",
     "TABLE_F16", "TABLE_Q8_0", "RopeParams", "rope_params_for_layer", "rope_params_explicit",
     "add", "rms_norm_rows", "rms_norm_q8_0_rows", "quantize_q8_0_rows", "quantize_q8_K_rows", "embed_gather_rows", "rope_rows", "fp8_kv_round_trip_rows",
-    "rope_fp8_store_rows", "kv_rows_to_raw", "swa_window_push_rows", "swiglu_rows", "hc_pre_rows", "output_hc_head_rows", "hc_post_rows", "hc_sinkhorn_rows", "hc_sinkhorn_mix_rows",
+    "rope_fp8_store_rows", "fp8_cache_load_rows", "kv_rows_to_raw", "swa_window_push_rows", "swiglu_rows", "hc_pre_rows", "output_hc_head_rows", "hc_post_rows", "hc_sinkhorn_rows", "hc_sinkhorn_mix_rows",
     "e4m3_encode", "e4m3_decode", "e4m3_selfcheck", "div_selfcheck", "device_status",
 ]
 
@@ -141,6 +141,15 @@ def rope_fp8_store_rows(kv, pos, params, n_rot, scale_mode, codes, scales, slots
     check(_lib.load().ds4b200_rope_fp8_store_rows(
         _p(kv), rows, D, n_rot, _p(pos), None if params is None else C.byref(params), _p(norm_w),
         eps, scale_mode, _p(slots), _p(codes), _p(scales), _p(tail_out), _p(rope_out), _s()))
+
+
+def fp8_cache_load_rows(codes, scales, slots, n_rot, scale_mode, tail=None, f16_round=False):
+    """Rows at `slots` of the byte cache -> f32 [len(slots), head_dim]."""
+    D = codes.shape[1]
+    out = torch.empty((slots.numel(), D), dtype=torch.float32, device=codes.device)
+    check(_lib.load().ds4b200_fp8_cache_load_rows(_p(codes), _p(scales), _p(tail), _p(slots), slots.numel(), D, n_rot,
+                                                  scale_mode, int(f16_round), _p(out), _s()))
+    return out
 
 
 def kv_rows_to_raw(kv, pos, params, raw_out, n_rot=64, slots=None, norm_w=None, eps=1e-6):

@@ -196,6 +196,16 @@ int ds4b200_rope_fp8_store_rows(const float *kv_in, int64_t n_rows, int head_dim
                                 const int32_t *slots, uint8_t *codes, float *scales,
                                 float *tail_out, float *rope_out, void *stream);
 
+/* Read side of the byte cache written by ds4b200_rope_fp8_store_rows: out[r][head_dim] =
+ * the row at slot slots[r] (slots nullable = r) as f32.  With BLOCK64_POW2 the result is
+ * bit for bit what the reference's f32 round trip leaves in its cache (code value x
+ * power-of-two scale, f32 tail; cuda/fp8_kv.cu:161-195) — except that an input of exactly
+ * -0.0 reads back as -0.0 where the reference gives +0.0.  f16_round != 0 adds the f16
+ * rounding of the raw KV cache (cuda/forward_layer.cu:182-190). */
+int ds4b200_fp8_cache_load_rows(const uint8_t *codes, const float *scales, const float *tail,
+                                const int32_t *slots, int64_t n_rows, int head_dim, int n_rot,
+                                int scale_mode, int f16_round, float *out, void *stream);
+
 /* The whole KV row chain of the reference in one launch (cuda/forward_layer.cu:868, :910,
  * :921, :950): optional weighted RMSNorm -> tail RoPE at pos[r] -> E4M3FN round trip of the
  * non-rotated prefix with per-64 power-of-two scales -> f16 rounding -> raw_out[slot][head_dim]

@@ -536,6 +536,32 @@ def test_output_hc_head_rows(ops, oracle, ref, n_embd, T):
 
 # ------------------------------------------------------------------ raw KV rows and window
 
+@pytest.mark.parametrize("mode", ["block64", "row_amax"])
+def test_fp8_cache_store_then_load_equals_the_round_trip(ops, oracle, mode):
+    """Write side + read side of the byte cache == the reference's f32 round-trip cache."""
+    g = inputs.rng(850)
+    T, n_slots = 333, 1024
+    kv = inputs.normal(g, (T, 512), 1.5)
+    kv[1, :64] = 0.0
+    slots = g.permutation(n_slots)[:T].astype(np.int32)
+    sm = ops.FP8_BLOCK64_POW2 if mode == "block64" else ops.FP8_ROW_AMAX
+    ns = 7 if mode == "block64" else 1
+    codes = torch.zeros((n_slots, 512), dtype=torch.uint8, device="cuda")
+    scales = torch.zeros((n_slots, ns), device="cuda")
+    tail = torch.zeros((n_slots, 64), device="cuda")
+    ops.rope_fp8_store_rows(dev(kv), None, None, 64, sm, codes, scales, slots=dev(slots), tail_out=tail)
+    got = ops.fp8_cache_load_rows(codes, scales, dev(slots), 64, sm, tail=tail)
+    if mode == "block64":
+        assert_bits(host(got), oracle.fp8_kv_round_trip_rows(kv), "store + load vs f32 round trip")
+        raw = ops.fp8_cache_load_rows(codes, scales, dev(slots), 64, sm, tail=tail, f16_round=True)
+        assert_bits(host(raw), oracle.f16_round(oracle.fp8_kv_round_trip_rows(kv)), "f16-rounded read")
+    else:
+        c, s_, _ = oracle.fp8_encode_rows(kv, 64, oracle.FP8_ROW_AMAX)
+        want = oracle.e4m3_decode(c).reshape(T, 512) * s_
+        assert_bits(host(got), want.astype(np.float32), "row-scale decode")
+        assert np.abs(host(got) - kv).max() <= 0.0625 * np.abs(kv).max() + 1e-6
+
+
 @pytest.mark.parametrize("il", [0, 2])
 def test_kv_rows_to_raw_chain(ops, oracle, ref, il):
     g = inputs.rng(830 + il)
