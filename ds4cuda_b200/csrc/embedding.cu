@@ -241,6 +241,17 @@ void selftest_bounded_wait(int max_polls, int *gave_up_dev, cudaStream_t s) {
     wait_gives_up_kernel<<<1, 32, 0, s>>>(max_polls, gave_up_dev);
 }
 
+// Device address of the status word on the current device (null on error), for kernels in
+// other translation units that make bounded waits.
+int *device_status_word() {
+    void *p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return static_cast<int *>(p);
+}
+
 int read_and_clear_device_status() {
     int v = 0, zero = 0;
     if (cudaDeviceSynchronize() != cudaSuccess) return -5;

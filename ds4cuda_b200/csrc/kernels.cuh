@@ -31,6 +31,7 @@ void embed_gather_rows(const void *table, int table_dtype, const int32_t *ids, i
                        const float *norm_w, float eps, float *out_rows, int n_replicas,
                        float *normed_f32, uint16_t *normed_bf16, cudaStream_t s);
 int read_and_clear_device_status();   // embedding.cu owns the status word
+int *device_status_word();            // its device address on the current device, or null
 void selftest_bounded_wait(int max_polls, int *gave_up_dev, cudaStream_t s);
 
 // pos == nullptr: every token uses single_pos.
@@ -67,6 +68,9 @@ void hc_pre_rows(const float *residual_hc, const uint16_t *hc_fn, const float *h
 // Cluster variant of the pre step without the Sinkhorn sweeps (comb receives the 16
 // pre-softmax values); false = shape not covered, nothing launched.
 bool hc_pre_rows_cluster(const float *residual_hc, const uint16_t *hc_fn, const float *hc_scale,
+                         const float *hc_base, float *post, float *comb, float *out, int64_t n_tokens,
+                         int n_embd, float eps, cudaStream_t s);
+bool hc_pre_rows_mma(const float *residual_hc, const uint16_t *hc_fn, const float *hc_scale,
                          const float *hc_base, float *post, float *comb, float *out, int64_t n_tokens,
                          int n_embd, float eps, cudaStream_t s);
 

@@ -444,7 +444,8 @@ def test_silu_mul_drop_in_and_reference_kernel(ops, oracle, ref):
 
 # ------------------------------------------------------------------ hyper-connections
 
-@pytest.mark.parametrize("n_embd,T", [(4096, 9), (1024, 5), (512, 3), (8192, 2), (100, 4)])
+@pytest.mark.parametrize("n_embd,T", [(4096, 9), (1024, 5), (512, 3), (8192, 2), (100, 4),
+                                      (4096, 150), (2048, 77), (2048, 7)])
 def test_hc_pre_rows(ops, oracle, n_embd, T):
     g = inputs.rng(700 + n_embd)
     resid = inputs.normal(g, (T, 4, n_embd))
