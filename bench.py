@@ -248,6 +248,59 @@ def reference_kernels_leg(tokens, n_layers):
     return out
 
 
+def standalone_ops_leg(tokens, peak):
+    """The batched forms the layer chain does not contain, one launch each between L2 flushes.
+
+    Full HC pre (24 x 16384 f16 matvec + gates + weighted stream sum), HC post with the block
+    term, and the FP8 cache store at a row count that fills the GPU.  CUDA events on torch's
+    current stream, which is the stream these wrappers launch on; median of 15.
+    """
+    import torch
+    from ds4cuda_b200 import ops
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(7)
+    flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device=dev)
+
+    def timed(fn):
+        ts = []
+        for i in range(18):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record(); torch.cuda.synchronize()
+            if i >= 3:
+                ts.append(a.elapsed_time(b) * 1e3)
+        return sorted(ts)[len(ts) // 2]
+
+    def entry(us, nbytes, what):
+        gbs = nbytes / us / 1e3
+        return {"us_per_launch": round(us, 1), "algorithmic_bytes": int(nbytes), "gbs": round(gbs, 1),
+                "frac_of_peak": round(gbs / peak, 4), "what": what}
+
+    out = {}
+    resid = torch.randn(tokens, 4, N_EMBD, device=dev, generator=g)
+    fn = (torch.randn(24, 4 * N_EMBD, device=dev, generator=g) / 128).half()
+    scale, base = torch.ones(3, device=dev), torch.zeros(24, device=dev)
+    us = timed(lambda: ops.hc_pre_rows(resid, fn, scale, base))
+    out["hc_pre_rows"] = entry(us, tokens * (4 * N_EMBD * 4 + N_EMBD * 4 + 80) + fn.numel() * 2,
+                               "24 dots per token on the tensor cores + gates + stream sum + Sinkhorn rows")
+    block = torch.randn(tokens, N_EMBD, device=dev, generator=g)
+    post = torch.rand(tokens, 4, device=dev, generator=g)
+    comb = torch.rand(tokens, 16, device=dev, generator=g)
+    us = timed(lambda: ops.hc_post_rows(block, resid, post, comb))
+    out["hc_post_rows_with_block"] = entry(us, tokens * (2 * 4 * N_EMBD * 4 + N_EMBD * 4 + 80), "config 5 with the block term")
+    del resid, block
+    rows = 65536
+    kv = torch.randn(rows, KV_DIM, device=dev, generator=g) * 1.5
+    pos = (torch.arange(rows, device=dev, dtype=torch.int32) % 4096).contiguous()
+    slots = torch.arange(rows, device=dev, dtype=torch.int32)
+    codes = torch.zeros(rows, KV_DIM, dtype=torch.uint8, device=dev)
+    scales = torch.zeros(rows, 1, device=dev)
+    rp = ops.rope_params_explicit(10000.0, 16.0, 4096, N_ROT)
+    us = timed(lambda: ops.rope_fp8_store_rows(kv, pos, rp, N_ROT, ops.FP8_ROW_AMAX, codes, scales, slots=slots))
+    out["rope_fp8_store_65536_rows"] = entry(us, rows * (KV_DIM * 4 + KV_DIM + 4 + 4), "config 3 kernel at a row count that fills the GPU")
+    return out
+
+
 def run_reference_arm(args):
     """The reference's CPU path: the scalar C restatement, all host threads, bounded sample per step."""
     rank = int(os.environ.get("RANK", "0"))
@@ -382,6 +435,7 @@ def run_ours(args):
 
     launches = path.launches_per_run(args.layers) * args.steps
     path.close()
+    standalone = standalone_ops_leg(tokens, peak) if (rank == 0 and world == 1) else None
     if world > 1:
         dist.destroy_process_group()
     if rank != 0:
@@ -394,7 +448,7 @@ def run_ours(args):
         "hbm_gbs_per_gpu": round(hbm_gbs_step, 1),
         "hbm_frac_of_peak": round(hbm_gbs_step / peak, 4), "hbm_frac_of_8000": round(hbm_gbs_step / 8000.0, 4),
         "ops": ops_table, "roofline": roofline, "cpu_baseline": cpu,
-        "reference_kernels_sm100a": ref_kernels,
+        "reference_kernels_sm100a": ref_kernels, "standalone_ops": standalone,
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms_step,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "pipeline": f"{args.e2e_chunks} row slices over copy-in / compute / copy-out streams"},
