@@ -126,7 +126,8 @@ __global__ void swiglu_scalar_kernel(const float *gate, const float *up, const f
 }
 
 // Counts (n, d) pairs, d in [1, 2], n spread over +-2^-40..2^40 and signs, for which
-// div_by_1to2 differs from the IEEE division.  Pairs come from a counter-based hash.
+// div_by_1to2 differs from the IEEE division, plus (a, b) pairs for which div_with_rcp does.
+// Pairs come from a counter-based hash.
 __global__ void div_selfcheck_kernel(uint64_t first, uint64_t count, unsigned long long *mismatches) {
     unsigned bad = 0;
     for (uint64_t k = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; k < count;
@@ -140,6 +141,13 @@ __global__ void div_selfcheck_kernel(uint64_t first, uint64_t count, unsigned lo
         const float n = __uint_as_float(((uint32_t)(z >> 63) << 31) | (ne << 23) | (uint32_t)((z >> 32) & 0x7fffffu));
         const float dd = (k & 1023u) == 0 ? 2.0f : d;                                         // include the end point
         bad += (__float_as_uint(div_by_1to2(n, dd)) != __float_as_uint(n / dd));
+        // the shared-reciprocal division of the FP8 row quantiser: divisor 2^-23..2^23, quotient
+        // 2^-20..2^9, both signs
+        const float b = __uint_as_float(((104u + (uint32_t)((z >> 40) % 47u)) << 23) | (uint32_t)(z & 0x7fffffu));
+        const float qt = __uint_as_float(((uint32_t)(z >> 63) << 31) | ((107u + (uint32_t)((z >> 48) % 30u)) << 23) |
+                                         (uint32_t)((z >> 9) & 0x7fffffu));
+        const float a = qt * b;
+        bad += (__float_as_uint(div_with_rcp(a, b, 1.0f / b)) != __float_as_uint(a / b));
     }
     bad = __reduce_add_sync(0xffffffffu, bad);
     if ((threadIdx.x & 31) == 0 && bad) atomicAdd(mismatches, (unsigned long long)bad);

@@ -246,10 +246,35 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) rope_fp8_store_kernel(StoreA
     if (a.do_rope) {                                  // cuda/forward_layer.cu:910 KV RoPE
         const float posf = (float)a.pos[row];
         const float ts = rope_theta_scale(a.rope, a.n_rot);
+        if (a.n_rot <= 64) {
+            // At most 32 pairs: lane k evaluates the angle of pair k (the same k multiplies and
+            // the same cosf / sinf as in rope_float4), and the lanes that hold the tail fetch the
+            // two (cos, sin) they need by shuffle, instead of 16 lanes doing two pairs each.
+            float c = 1.0f, sn = 0.0f;
+            if (2 * lane < a.n_rot) {
+                float te = posf;
+                for (int k = 0; k < lane; ++k) te *= ts;
+                rope_cs(a.rope, lane, te, false, c, sn);
+            }
 #pragma unroll
-        for (int j = 0; j < VPT; ++j) {
-            const int i = lane + 32 * j;
-            if (i < n4 && 4 * i >= n_nope) rope_float4(v[j], 4 * i - n_nope, posf, ts, a.rope, false);
+            for (int j = 0; j < VPT; ++j) {
+                if ((32 * j + 31) * 4 < n_nope) continue;          // no lane of this j is in the tail
+                const int i = lane + 32 * j;
+                const bool tail = i < n4 && 4 * i >= n_nope;
+                const int k0 = tail ? (4 * i - n_nope) >> 1 : 0;
+                const float c0 = __shfl_sync(0xffffffffu, c, k0), s0 = __shfl_sync(0xffffffffu, sn, k0);
+                const float c1 = __shfl_sync(0xffffffffu, c, k0 + 1), s1 = __shfl_sync(0xffffffffu, sn, k0 + 1);
+                if (tail) {
+                    rotate(v[j].x, v[j].y, c0, s0);
+                    rotate(v[j].z, v[j].w, c1, s1);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const int i = lane + 32 * j;
+                if (i < n4 && 4 * i >= n_nope) rope_float4(v[j], 4 * i - n_nope, posf, ts, a.rope, false);
+            }
         }
     }
     if (a.rope_out) {
@@ -267,13 +292,14 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) rope_fp8_store_kernel(StoreA
         for (int j = 0; j < VPT; ++j) amax = fmaxf(amax, amax4(v[j]));
         amax = fmaxf(warp_max(amax), kFp8AmaxFloor);
         const float scale = amax / kFp8Max;
+        const float inv = 1.0f / scale;               // one IEEE reciprocal per row, see div_with_rcp
         if (lane == 0) a.scales[slot] = scale;
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
             const int i = lane + 32 * j;
             if (i >= n4) continue;
-            const float4 q = make_float4(clamp448(v[j].x / scale), clamp448(v[j].y / scale),
-                                         clamp448(v[j].z / scale), clamp448(v[j].w / scale));
+            const float4 q = make_float4(clamp448(div_with_rcp(v[j].x, scale, inv)), clamp448(div_with_rcp(v[j].y, scale, inv)),
+                                         clamp448(div_with_rcp(v[j].z, scale, inv)), clamp448(div_with_rcp(v[j].w, scale, inv)));
             __stcs(code_row + i, e4m3_encode4(q));
         }
     } else {                                          // cuda/fp8_kv.cu:161-180 scale rule
