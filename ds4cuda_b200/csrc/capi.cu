@@ -350,6 +350,26 @@ int ds4b200_e4m3_decode_f32(const uint8_t *codes, float *x, int64_t n, void *str
     return launched("e4m3_decode");
 }
 
+int ds4b200_compressor_step_f32(int is_attn, const float *kv_cur, float *sc_cur, const uint16_t *ape_f16,
+                                const float *norm_w, int head_dim, int compress_ratio, int pos, int il,
+                                float *state_kv, float *state_score, float *emit_out,
+                                int *emitted_host, void *stream) {
+    REQUIRE(kv_cur && sc_cur && ape_f16 && norm_w && state_kv && state_score && emit_out,
+            "compressor_step: null pointer");
+    REQUIRE(head_dim >= 128 && head_dim <= 1024 && head_dim % 64 == 0,
+            "compressor_step: head_dim must be a multiple of 64 in [128, 1024], got %d", head_dim);
+    REQUIRE(compress_ratio == 4 || (compress_ratio >= 1 && compress_ratio <= 4096),
+            "compressor_step: compress_ratio out of range");
+    REQUIRE(pos >= 0, "compressor_step: negative position");
+    ds4b200_rope_params rope;
+    ds4b200_rope_params_for_layer(il, 64, &rope);
+    const bool emitted = ds4b200::compressor_step(is_attn, kv_cur, sc_cur, ape_f16, norm_w, head_dim, compress_ratio,
+                                                  pos, rope, 64, 1.0e-6f, state_kv, state_score, emit_out,
+                                                  STREAM(stream));
+    if (emitted_host) *emitted_host = emitted ? 1 : 0;
+    return launched("compressor_step");
+}
+
 int ds4b200_div_selfcheck(uint64_t first, uint64_t count, unsigned long long *mismatches, void *stream) {
     REQUIRE(mismatches, "div_selfcheck: null pointer");
     ds4b200::div_selfcheck(first, count, mismatches, STREAM(stream));

@@ -90,6 +90,11 @@ void hc_post_rows(const float *block_out, const float *block_out2, const float *
                   float *out_hc, int64_t n_tokens, int n_embd, int iters, float eps,
                   cudaStream_t s);
 
+// compressor.cu: returns whether the step emitted
+bool compressor_step(int is_attn, const float *kv_cur, float *sc_cur, const uint16_t *ape_f16,
+                     const float *norm_w, int head_dim, int ratio, int pos, const ds4b200_rope_params &rope,
+                     int n_rot, float eps, float *state_kv, float *state_score, float *emit_out,
+                     cudaStream_t s);
 void div_selfcheck(uint64_t first, uint64_t count, unsigned long long *mismatches, cudaStream_t s);
 void e4m3_encode(const float *x, uint8_t *codes, int64_t n, cudaStream_t s);
 void e4m3_decode(const uint8_t *codes, float *x, int64_t n, cudaStream_t s);

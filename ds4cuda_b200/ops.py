@@ -19,7 +19,7 @@ __all__ = [
     "TABLE_F16", "TABLE_Q8_0", "RopeParams", "rope_params_for_layer", "rope_params_explicit",
     "add", "rms_norm_rows", "rms_norm_q8_0_rows", "quantize_q8_0_rows", "quantize_q8_K_rows", "embed_gather_rows", "rope_rows", "fp8_kv_round_trip_rows",
     "rope_fp8_store_rows", "fp8_cache_load_rows", "kv_rows_to_raw", "swa_window_push_rows", "swiglu_rows", "hc_pre_rows", "output_hc_head_rows", "hc_post_rows", "hc_sinkhorn_rows", "hc_sinkhorn_mix_rows",
-    "e4m3_encode", "e4m3_decode", "e4m3_selfcheck", "div_selfcheck", "device_status",
+    "e4m3_encode", "e4m3_decode", "e4m3_selfcheck", "div_selfcheck", "device_status", "compressor_step",
 ]
 
 
@@ -168,6 +168,16 @@ def swa_window_push_rows(raw_kv, n_raw, new_rows):
     check(_lib.load().ds4b200_swa_window_push_rows_f32(_p(raw_kv), cap, n_raw, _p(new_rows), new_rows.shape[0], D,
                                                        C.byref(after), _s()))
     return after.value
+
+
+def compressor_step(is_attn, kv_cur, sc_cur, ape_f16, norm_w, head_dim, ratio, pos, il, state_kv, state_score,
+                    emit_out):
+    """One streaming-compressor step after its projections, in place; True when emit_out was written."""
+    emitted = C.c_int()
+    check(_lib.load().ds4b200_compressor_step_f32(int(is_attn), _p(kv_cur), _p(sc_cur), _p(ape_f16), _p(norm_w),
+                                                  head_dim, ratio, pos, il, _p(state_kv), _p(state_score),
+                                                  _p(emit_out), C.byref(emitted), _s()))
+    return bool(emitted.value)
 
 
 def swiglu_rows(gate, up, weights=None, mode=GLU_PLAIN, clamp=0.0, combine=False, fast_exp=False):

@@ -223,6 +223,22 @@ int ds4b200_kv_rows_to_raw_f32(const float *kv_in, int64_t n_rows, int head_dim,
 int ds4b200_swa_window_push_rows_f32(float *raw_kv, int cap, int n_raw, const float *new_rows,
                                      int n_new, int head_dim, int *n_raw_after, void *stream);
 
+/* One streaming-compressor step after its two projections: everything
+ * launch_compressor_decode_step_f32{,_prealloc} (cuda/compressor.cuh:78,102; cuda/compressor.cu:328-420)
+ * does once kv_cur / sc_cur = W_kv x, W_gate x are known, in one launch.
+ *   sc_cur[j] += f16(ape[pos % ratio][j]);  state row (ratio == 4 ? 4 + pos % 4 : pos % ratio) <- kv_cur, sc_cur
+ * and, when (pos + 1) % ratio == 0: pool the state rows per column with softmax weights ->
+ * RMSNorm (norm_w, eps 1e-6) -> tail RoPE at position pos + 1 - ratio with the parameters of
+ * layer il -> E4M3FN round trip of the non-rotated prefix (is_attn != 0 only) -> emit_out[head_dim];
+ * ratio 4 then copies state rows 4-7 over rows 0-3.
+ * width = head_dim * (ratio == 4 ? 2 : 1).  kv_cur, sc_cur [width]; ape_f16 [ratio][width];
+ * state_kv, state_score [(ratio == 4 ? 8 : ratio)][width]; n_rot 64.  *emitted_host (host,
+ * nullable) receives 1 when emit_out was written.  head_dim a multiple of 64, 128..1024. */
+int ds4b200_compressor_step_f32(int is_attn, const float *kv_cur, float *sc_cur, const uint16_t *ape_f16,
+                                const float *norm_w, int head_dim, int compress_ratio, int pos, int il,
+                                float *state_kv, float *state_score, float *emit_out,
+                                int *emitted_host, void *stream);
+
 /* SwiGLU over gate/up[n_tokens][k][n].  weights[n_tokens][k] nullable.
  * combine != 0: out[n_tokens][n] = sum of the k slots in slot order; else
  * out[n_tokens][k][n].  fast_exp != 0 uses the hardware exp approximation the

@@ -608,3 +608,73 @@ void ds4o_hc_sinkhorn_mix_rows(const float *logits, const float *residual_hc,
                           out_hc + t * 4 * (int64_t)n_embd, 1, n_embd);
     }
 }
+
+/* ====================================================================== */
+/* Streaming compressor step (after the projections)                      */
+/* ====================================================================== */
+
+int ds4o_compressor_step(int is_attn, const float *kv_cur, float *sc_cur, const uint16_t *ape_f16,
+                         const float *norm_w, int head_dim, int ratio, int pos,
+                         const ds4o_rope_params *rope, int n_rot, float eps,
+                         float *state_kv, float *state_score, float *emit_out)
+{
+    const int coff = ratio == 4 ? 2 : 1, width = coff * head_dim;
+    const int pos_mod = pos % ratio;
+    const int row = ratio == 4 ? ratio + pos_mod : pos_mod;          /* cuda/compressor.cu:84-86 */
+    for (int j = 0; j < width; j++) {
+        const float sc = sc_cur[j] + ds4o_f16_to_f32(ape_f16[(size_t)pos_mod * width + j]);
+        state_kv[(size_t)row * width + j] = kv_cur[j];
+        state_score[(size_t)row * width + j] = sc;
+        sc_cur[j] = sc;
+    }
+    if ((pos + 1) % ratio != 0) return 0;
+
+    const float neg_inf = -1.0e30f;                                  /* cuda/compressor.cu:52 */
+    for (int j = 0; j < head_dim; j++) {                             /* cuda/compressor.cu:107-164 */
+        float mx = neg_inf;
+        if (ratio == 4) {
+            for (int r = 0; r < 4; r++) {
+                const float sp = state_score[(size_t)r * width + j];
+                const float sc = state_score[(size_t)(4 + r) * width + head_dim + j];
+                if (sp > mx) mx = sp;
+                if (sc > mx) mx = sc;
+            }
+        } else {
+            for (int r = 0; r < ratio; r++) {
+                const float s = state_score[(size_t)r * width + j];
+                if (s > mx) mx = s;
+            }
+        }
+        if (mx <= neg_inf * 0.5f) { emit_out[j] = 0.0f; continue; }
+        float denom = 0.0f, sum = 0.0f;
+        if (ratio == 4) {
+            for (int r = 0; r < 4; r++) {
+                const float wp = expf(state_score[(size_t)r * width + j] - mx);
+                const float wc = expf(state_score[(size_t)(4 + r) * width + head_dim + j] - mx);
+                denom += wp + wc;
+                sum += wp * state_kv[(size_t)r * width + j];
+                sum += wc * state_kv[(size_t)(4 + r) * width + head_dim + j];
+            }
+        } else {
+            for (int r = 0; r < ratio; r++) {
+                const float w = expf(state_score[(size_t)r * width + j] - mx);
+                denom += w;
+                sum += w * state_kv[(size_t)r * width + j];
+            }
+        }
+        emit_out[j] = denom > 0.0f ? sum / denom : 0.0f;
+    }
+    {                                                                /* cuda/compressor.cu:173-220 */
+        const float scale = rms_scale_of(emit_out, head_dim, eps);
+        for (int i = 0; i < head_dim; i++) emit_out[i] = emit_out[i] * scale * norm_w[i];
+    }
+    rope_tail_inplace(emit_out, head_dim, n_rot, pos + 1 - ratio, rope, 0);
+    if (is_attn) ds4o_fp8_kv_round_trip_rows(emit_out, emit_out, 1, head_dim, n_rot);
+    if (ratio == 4) {                                                /* cuda/compressor.cu:232-252 */
+        for (int i = 0; i < 4 * width; i++) {
+            state_kv[i] = state_kv[4 * width + i];
+            state_score[i] = state_score[4 * width + i];
+        }
+    }
+    return 1;
+}

@@ -161,6 +161,16 @@ void ds4o_hc_sinkhorn_mix_rows(const float *logits, const float *residual_hc,
                                float *out_hc, float *comb_out, int64_t n_tokens,
                                int n_embd, int iters, float eps);
 
+/* One streaming-compressor step after its two projections (cuda/compressor.cu:65-90 bias and
+ * state row, :107-164 pool, :173-220 RMSNorm, cuda/rope.cu tail RoPE at pos + 1 - ratio,
+ * cuda/fp8_kv.cu round trip when is_attn, :232-252 state roll for ratio 4).
+ * width = head_dim * (ratio == 4 ? 2 : 1); state arrays hold (ratio == 4 ? 8 : ratio) rows.
+ * Returns 1 when emit_out was written. */
+int ds4o_compressor_step(int is_attn, const float *kv_cur, float *sc_cur, const uint16_t *ape_f16,
+                         const float *norm_w, int head_dim, int ratio, int pos,
+                         const ds4o_rope_params *rope, int n_rot, float eps,
+                         float *state_kv, float *state_score, float *emit_out);
+
 #ifdef __cplusplus
 }
 #endif

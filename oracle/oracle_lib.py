@@ -295,6 +295,19 @@ def hc_sinkhorn_mix_rows(logits, resid, iters=20, eps=1e-6):
     return out, comb
 
 
+def compressor_step(is_attn, kv_cur, sc_cur, ape_f16, norm_w, head_dim, ratio, pos, params,
+                    state_kv, state_score, n_rot=64, eps=1e-6):
+    """One step; sc_cur, state_kv, state_score are updated in place.  Returns emit [head_dim] or None."""
+    assert kv_cur.dtype == np.float32 and sc_cur.dtype == np.float32 and ape_f16.dtype == np.uint16
+    assert state_kv.dtype == np.float32 and state_score.dtype == np.float32
+    emit = np.zeros(head_dim, dtype=np.float32)
+    fn = lib().ds4o_compressor_step
+    fn.restype = C.c_int
+    rc = fn(_i(is_attn), _p(kv_cur), _p(sc_cur), _p(ape_f16), _p(_f32(norm_w)), _i(head_dim), _i(ratio), _i(pos),
+            C.byref(params), _i(n_rot), C.c_float(eps), _p(state_kv), _p(state_score), _p(emit))
+    return emit if rc else None
+
+
 def e4m3_encode(x):
     x = _f32(x).ravel()
     f = lib().ds4o_e4m3_encode

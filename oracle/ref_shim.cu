@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include "attn_out.cuh"
+#include "compressor.cuh"
 #include "dense_q8.cuh"
 #include "elementwise.cuh"
 #include "embedding.cuh"
@@ -16,6 +17,7 @@
 #include "norm.cuh"
 #include "output_head.cuh"
 #include "rope.cuh"
+#include "router.cuh"
 
 #define S(s) static_cast<cudaStream_t>(s)
 using namespace ds4cuda;
@@ -100,4 +102,22 @@ void ds4ref_loop_hc_post(const float *block_out, const float *residual_hc, const
                            out_hc + (size_t)t * 4 * n_embd, 4, n_embd, S(s));
 }
 
+
+void ds4ref_mul_mv_f16_f32(const uint16_t *w, const float *x, float *y, int out_dim, int in_dim, void *s) {
+    launch_mul_mv_f16_f32(w, x, y, out_dim, in_dim, S(s));
+}
+
+// The whole compressor step (projections included) with caller-owned scratch, so that the
+// harness can read back the projections the step used.
+int ds4ref_compressor_decode_step_prealloc(int is_attn, const float *x, const uint16_t *w_kv,
+                                           const uint16_t *w_gate, const uint16_t *w_ape, const float *w_norm,
+                                           int in_dim, int head_dim_out, int ratio, int pos, int il,
+                                           float *state_kv, float *state_score, float *emit_out,
+                                           float *scratch_kv, float *scratch_sc, void *s) {
+    int emitted = 0;
+    launch_compressor_decode_step_f32_prealloc(is_attn != 0, x, w_kv, w_gate, w_ape, w_norm, in_dim, head_dim_out,
+                                               ratio, pos, il, state_kv, state_score, emit_out, &emitted,
+                                               scratch_kv, scratch_sc, S(s));
+    return emitted;
+}
 }  // extern "C"

@@ -696,3 +696,80 @@ def test_empty_inputs_are_no_ops(ops):
     assert ops.swiglu_rows(torch.empty(0, 6, 64, device="cuda"), torch.empty(0, 6, 64, device="cuda")).numel() == 0
     assert ops.fp8_kv_round_trip_rows(torch.empty(0, 512, device="cuda")).numel() == 0
     torch.cuda.synchronize()
+
+
+# ------------------------------------------------------------------ streaming compressor step
+
+def _i16(a):
+    return torch.from_numpy(np.ascontiguousarray(a).view(np.int16)).cuda()
+
+
+@pytest.mark.parametrize("head_dim,ratio,is_attn,il", [(512, 4, 1, 2), (128, 4, 0, 3), (512, 128, 1, 3), (128, 16, 0, 5)])
+def test_compressor_step_against_oracle(ops, oracle, head_dim, ratio, is_attn, il):
+    g = inputs.rng(910 + head_dim + ratio)
+    n_steps = 3 * ratio if ratio <= 16 else ratio
+    coff = 2 if ratio == 4 else 1
+    width, rows = coff * head_dim, (8 if ratio == 4 else ratio)
+    kv, sc = inputs.normal(g, (n_steps, width)), inputs.normal(g, (n_steps, width), 2.0)
+    ape = inputs.normal(g, (ratio, width), 0.5).astype(np.float16).view(np.uint16)
+    norm_w = inputs.uniform(g, (head_dim,), 0.5, 1.5)
+    p = oracle.rope_params_for_layer(il)
+    o_kv = np.zeros((rows, width), dtype=np.float32)
+    o_sc = np.full((rows, width), -1.0e30, dtype=np.float32)
+    d_kv, d_sc = dev(o_kv), dev(o_sc)
+    d_ape, d_w = _i16(ape), dev(norm_w)
+    emit = torch.full((head_dim,), -7.0, device="cuda")
+    n_emits = 0
+    for pos in range(n_steps):
+        o_cur_sc = sc[pos].copy()
+        want = oracle.compressor_step(is_attn, kv[pos].copy(), o_cur_sc, ape, norm_w, head_dim, ratio, pos, p, o_kv, o_sc)
+        d_cur_sc = dev(sc[pos])
+        emitted = ops.compressor_step(is_attn, dev(kv[pos]), d_cur_sc, d_ape, d_w, head_dim, ratio, pos, il, d_kv, d_sc, emit)
+        assert emitted == (want is not None)
+        assert_bits(host(d_cur_sc), o_cur_sc, "score + bias, written back")
+        assert_bits(host(d_kv), o_kv, f"state_kv after step {pos}")
+        assert_bits(host(d_sc), o_sc, f"state_score after step {pos}")
+        if want is None:
+            continue
+        n_emits += 1
+        got = host(emit)
+        n_nope = head_dim - 64
+        if is_attn:
+            assert (got[:n_nope] != want[:n_nope]).mean() < 0.02       # a value on a rounding boundary may flip
+            assert np.abs(got - want).max() <= 0.07 * np.abs(want).max()
+        else:
+            assert_close(got[:n_nope], want[:n_nope], rel=2e-5, what="emit prefix")
+        assert_close(got[n_nope:], want[n_nope:], rel=2e-5, what="emit tail")
+    assert n_emits == n_steps // ratio
+
+
+@pytest.mark.parametrize("head_dim,is_attn,il", [(512, 1, 2), (128, 0, 3)])
+def test_compressor_step_equals_the_reference_launcher(ops, ref, head_dim, is_attn, il):
+    """Same projections in, same state and emit out, bit for bit, over three windows of ratio 4."""
+    if not ref:
+        pytest.skip("reference kernels not built")
+    g = inputs.rng(930 + head_dim)
+    ratio, in_dim = 4, 256
+    width = 2 * head_dim
+    w_kv = _i16((inputs.normal(g, (width, in_dim)) / 16).astype(np.float16).view(np.uint16))
+    w_gate = _i16((inputs.normal(g, (width, in_dim)) / 8).astype(np.float16).view(np.uint16))
+    ape = _i16(inputs.normal(g, (ratio, width), 0.5).astype(np.float16).view(np.uint16))
+    norm_w = dev(inputs.uniform(g, (head_dim,), 0.5, 1.5))
+    r_kv, r_sc = torch.zeros(8, width, device="cuda"), torch.full((8, width), -1.0e30, device="cuda")
+    m_kv, m_sc = r_kv.clone(), r_sc.clone()
+    r_emit, m_emit = torch.zeros(head_dim, device="cuda"), torch.zeros(head_dim, device="cuda")
+    scratch_kv, scratch_sc = torch.empty(width, device="cuda"), torch.empty(width, device="cuda")
+    for pos in range(12):
+        x = dev(inputs.normal(g, (in_dim,)))
+        kv_cur, sc_cur = torch.empty(width, device="cuda"), torch.empty(width, device="cuda")
+        ref.call("mul_mv_f16_f32", w_kv, x, kv_cur, width, in_dim)
+        ref.call("mul_mv_f16_f32", w_gate, x, sc_cur, width, in_dim)
+        ref.call("compressor_decode_step_prealloc", is_attn, x, w_kv, w_gate, ape, norm_w, in_dim, head_dim, ratio,
+                 pos, il, r_kv, r_sc, r_emit, scratch_kv, scratch_sc)
+        emitted = ops.compressor_step(is_attn, kv_cur, sc_cur, ape, norm_w, head_dim, ratio, pos, il, m_kv, m_sc, m_emit)
+        torch.cuda.synchronize()
+        assert emitted == ((pos + 1) % ratio == 0)
+        assert_bits(host(m_kv), host(r_kv), f"state_kv, step {pos}")
+        assert_bits(host(m_sc), host(r_sc), f"state_score, step {pos}")
+        if emitted:
+            assert_bits(host(m_emit), host(r_emit), f"emit, step {pos}")

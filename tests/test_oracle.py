@@ -331,3 +331,62 @@ def test_activation_quantisers(oracle):
     # the element of largest magnitude maps to -127 * sign(scale) ... i.e. q = -127 and scale = -max/127
     k = np.abs(x[:256]).argmax()
     assert qk[k] == -127 and np.isclose(sk[0], -x[k] / 127.0)
+
+
+# ------------------------------------------------------------------ streaming compressor step
+
+def _compressor_inputs(g, head_dim, ratio, n_steps):
+    coff = 2 if ratio == 4 else 1
+    width = coff * head_dim
+    return dict(
+        width=width, rows=8 if ratio == 4 else ratio,
+        kv=inputs.normal(g, (n_steps, width)), sc=inputs.normal(g, (n_steps, width), 2.0),
+        ape=inputs.normal(g, (ratio, width), 0.5).astype(np.float16).view(np.uint16),
+        norm_w=inputs.uniform(g, (head_dim,), 0.5, 1.5))
+
+
+@pytest.mark.parametrize("head_dim,ratio,is_attn", [(512, 4, 1), (128, 4, 0), (128, 16, 0)])
+def test_compressor_step_against_float64(oracle, head_dim, ratio, is_attn):
+    g = inputs.rng(900 + head_dim + ratio)
+    n_steps = 2 * ratio
+    d = _compressor_inputs(g, head_dim, ratio, n_steps)
+    width = d["width"]
+    p = oracle.rope_params_for_layer(2)
+    state_kv = np.zeros((d["rows"], width), dtype=np.float32)
+    state_sc = np.full((d["rows"], width), -1.0e30, dtype=np.float32)
+    for pos in range(n_steps):
+        kv, sc = d["kv"][pos].copy(), d["sc"][pos].copy()
+        before_kv, before_sc = state_kv.copy(), state_sc.copy()
+        emit = oracle.compressor_step(is_attn, kv, sc, d["ape"], d["norm_w"], head_dim, ratio, pos, p,
+                                      state_kv, state_sc)
+        ape = d["ape"][pos % ratio].view(np.float16).astype(np.float32)
+        np.testing.assert_array_equal(sc, d["sc"][pos] + ape)          # one f32 add, written back
+        row = ratio + pos % ratio if ratio == 4 else pos % ratio
+        if (pos + 1) % ratio:
+            assert emit is None
+            np.testing.assert_array_equal(state_kv[row], kv)
+            np.testing.assert_array_equal(state_sc[row], sc)
+            continue
+        # the window closed: rebuild the emit in float64 from the state as it was before the roll
+        skv, ssc = before_kv.astype(np.float64), before_sc.astype(np.float64)
+        skv[row], ssc[row] = kv, sc
+        if ratio == 4:
+            scores = np.concatenate([ssc[0:4, :head_dim], ssc[4:8, head_dim:]], axis=0)
+            values = np.concatenate([skv[0:4, :head_dim], skv[4:8, head_dim:]], axis=0)
+        else:
+            scores, values = ssc[:, :head_dim], skv[:, :head_dim]
+        w = np.exp(scores - scores.max(axis=0))
+        pooled = (w * values).sum(axis=0) / w.sum(axis=0)
+        normed = pooled / np.sqrt((pooled ** 2).mean() + 1e-6) * d["norm_w"]
+        want = oracle.rope_rows(normed.astype(np.float32)[None, None, :], np.array([pos + 1 - ratio], np.int32), p)[0, 0]
+        if is_attn:
+            want = oracle.fp8_kv_round_trip_rows(want[None, :])[0]
+            n_nope = head_dim - 64
+            assert (emit[:n_nope] != want[:n_nope]).mean() < 0.02        # a value on a rounding boundary may flip
+            assert np.abs(emit - want).max() <= 0.07 * np.abs(want).max()
+            assert np.abs(emit[n_nope:] - want[n_nope:]).max() <= 2e-5 * np.abs(want).max()
+        else:
+            assert np.abs(emit - want).max() <= 2e-5 * np.abs(want).max()
+        if ratio == 4:
+            np.testing.assert_array_equal(state_kv[0:4], state_kv[4:8])
+            np.testing.assert_array_equal(state_sc[0:4], state_sc[4:8])
