@@ -222,6 +222,20 @@ hc_pre_mma_kernel(const __grid_constant__ CUtensorMap x_map, const float *__rest
             const float4 xd = *reinterpret_cast<const float4 *>(ra + 8 * kRowStride + 64);
             ss_a += dot4(xa) + dot4(xb);
             ss_b += dot4(xc) + dot4(xd);
+            // This warp is done with the slot: its rows are in registers (the sums above consumed
+            // all four loads, so they have returned before the arrive can issue).  The slot is
+            // refilled by one lane of a warp that changes from stage to stage (issuing a TMA load
+            // costs its warp a few hundred cycles), as soon as all 16 warps have said so; the
+            // load then has the whole MMA work of this stage and of the next two to land.  The
+            // slot of a step's last stage is refilled later: it first serves as scratch below.
+            asm volatile("" ::"f"(ss_a), "f"(ss_b) : "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[slot]);
+            if (h != 3 && lane == 0 && warp == (int)((n + kStages) & 15)) {
+                mbar_wait_bounded(&empty[slot], (uint32_t)(n / kStages) & 1u, status);
+                issue_stage(n + kStages);
+            }
+            __syncwarp();
             float acc_hi[3][4];
 #pragma unroll
             for (int nt = 0; nt < 3; ++nt)
@@ -249,48 +263,27 @@ hc_pre_mma_kernel(const __grid_constant__ CUtensorMap x_map, const float *__rest
 #pragma unroll
                 for (int i = 0; i < 4; ++i) sum[nt][i] += acc_hi[nt][i];
             if (prev_step >= 0) out_store(prev_step, h, xo, pre_prev);
-            // This warp is done with the stage (its rows went through registers into the MMAs
-            // above).  The slot is refilled by one lane of a warp that changes from stage to
-            // stage (issuing a TMA load costs its warp a few hundred cycles), once all 16 warps
-            // have said so; nobody else waits.
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[slot]);
-            if (lane == 0 && warp == (int)((n + kStages) & 15)) {
-                mbar_wait_bounded(&empty[slot], (uint32_t)(n / kStages) & 1u, status);
-                issue_stage(n + kStages);
-            }
-            __syncwarp();
         }
 
-        // ---- the warps' partial sums for the 16 tokens meet in `part`: warps 8-15 store theirs,
-        // warps 0-7 add their own on top
+        // ---- the warps' partial sums for the 16 tokens: warps 0-7 store theirs in `part`, warps
+        // 8-15 in the ring slot of the step's last stage, which every warp has released by then
+        // (they check) and whose refill waits until the sums below have been read.
         ss_a += __shfl_xor_sync(0xffffffffu, ss_a, 1); ss_a += __shfl_xor_sync(0xffffffffu, ss_a, 2);
         ss_b += __shfl_xor_sync(0xffffffffu, ss_b, 1); ss_b += __shfl_xor_sync(0xffffffffu, ss_b, 2);
-        float *pa = part + ((warp & 7) * kStepTokens + g) * kPartStride;
+        const int last_slot = (int)((n - 1) % kStages);
+        float *part_hi = reinterpret_cast<float *>(ring + last_slot * kStageBytes);
+        if (warp >= 8) mbar_wait_bounded(&empty[last_slot], (uint32_t)((n - 1) / kStages) & 1u, status);
+        float *pa = (warp < 8 ? part : part_hi) + ((warp & 7) * kStepTokens + g) * kPartStride;
         float *pb = pa + 8 * kPartStride;
 #pragma unroll
-        for (int phase = 0; phase < 2; ++phase) {
-            if ((warp >> 3) == 1 - phase) {
-#pragma unroll
-                for (int nt = 0; nt < 3; ++nt) {
-                    float2 va = make_float2(sum[nt][0] + acc_lo[nt][0], sum[nt][1] + acc_lo[nt][1]);
-                    float2 vb = make_float2(sum[nt][2] + acc_lo[nt][2], sum[nt][3] + acc_lo[nt][3]);
-                    float2 *qa = reinterpret_cast<float2 *>(pa + nt * 8 + 2 * t4);
-                    float2 *qb = reinterpret_cast<float2 *>(pb + nt * 8 + 2 * t4);
-                    if (phase == 1) {
-                        const float2 oa = *qa, ob = *qb;
-                        va.x += oa.x; va.y += oa.y; vb.x += ob.x; vb.y += ob.y;
-                    }
-                    *qa = va;
-                    *qb = vb;
-                }
-                if (t4 == 0) {
-                    pa[kMixN] = (phase == 1 ? pa[kMixN] : 0.0f) + ss_a;
-                    pb[kMixN] = (phase == 1 ? pb[kMixN] : 0.0f) + ss_b;
-                }
-            }
-            __syncthreads();
+        for (int nt = 0; nt < 3; ++nt) {
+            *reinterpret_cast<float2 *>(pa + nt * 8 + 2 * t4) =
+                make_float2(sum[nt][0] + acc_lo[nt][0], sum[nt][1] + acc_lo[nt][1]);
+            *reinterpret_cast<float2 *>(pb + nt * 8 + 2 * t4) =
+                make_float2(sum[nt][2] + acc_lo[nt][2], sum[nt][3] + acc_lo[nt][3]);
         }
+        if (t4 == 0) { pa[kMixN] = ss_a; pb[kMixN] = ss_b; }
+        __syncthreads();
 
         // ---- CTA totals, pushed into every CTA of the cluster over DSMEM.  The peers must have
         // finished reading the previous step's values: they said so with the arrive below, a
@@ -301,11 +294,19 @@ hc_pre_mma_kernel(const __grid_constant__ CUtensorMap x_map, const float *__rest
             float s = 0.0f;
 #pragma unroll
             for (int w = 0; w < 8; ++w) s += part[(w * kStepTokens + m) * kPartStride + k];
+#pragma unroll
+            for (int w = 0; w < 8; ++w) s += part_hi[(w * kStepTokens + m) * kPartStride + k];
             float *mine = cl_part + rank * kStepTokens * kVals + tid;
 #pragma unroll
             for (int r = 0; r < C; ++r) *cluster.map_shared_rank(mine, r) = s;
         }
         cluster.sync();
+        // every thread has read the scratch slot: order those generic-proxy accesses before the
+        // asynchronous copy, then refill the slot with the third stage of the next step
+        if (tid == 0) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            issue_stage(n - 1 + kStages);
+        }
 
         // ---- gates.  Every CTA computes `pre` for the 16 tokens (identical results: the ranks
         // are summed in the same order everywhere); post and comb of a token are written by one
@@ -320,7 +321,7 @@ hc_pre_mma_kernel(const __grid_constant__ CUtensorMap x_map, const float *__rest
             const int m = tid >> 2, h = tid & 3;
             const float rms = rms_scale(total(m, kMixN), (float)hc_dim, eps);
             const float zp = (total(m, h) * rms) * hc_scale[0] + hc_base[h];
-            pre_cur[m * 4 + h] = 1.0f / (1.0f + expf(-zp)) + eps;
+            pre_cur[m * 4 + h] = __fdividef(1.0f, 1.0f + expf(-zp)) + eps;
         } else if (tid >= 128 && tid < 128 + 4 * kTokensPerRank) {
             const int m = rank * kTokensPerRank + ((tid - 128) >> 2), h = tid & 3;
             const int64_t t = step * kStepTokens + m;
