@@ -383,7 +383,9 @@ def run_ours(args):
     value = job_tokens / (ms_step * 1e-3)
 
     # ---- per-kernel durations inside the chain (events around every launch)
-    per_op_ms = path.profile_ops(20)
+    per_op_ms = path.profile_ops(50)
+    # one launch of each kernel on its own (events around a single launch; includes the launch gap)
+    single_ms = path.profile_ops(1)
     ops_table = {}
     peaks_file = ROOT / "MEASURED_PEAKS.json"
     if peaks_file.exists():
@@ -393,7 +395,8 @@ def run_ours(args):
     for i, name in enumerate(OP_NAMES):
         us = per_op_ms[name] * 1e3
         gbs = path.op_bytes(i) / (us * 1e-6) / 1e9
-        ops_table[name] = {"us_per_launch": round(us, 2), "algorithmic_bytes": path.op_bytes(i),
+        ops_table[name] = {"us_per_launch": round(us, 2), "us_single_launch": round(single_ms[name] * 1e3, 2),
+                           "algorithmic_bytes": path.op_bytes(i),
                            "gbs": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4),
                            "frac_of_8000": round(gbs / 8000.0, 4)}
     dominant = max(OP_NAMES, key=lambda n: ops_table[n]["us_per_launch"])
