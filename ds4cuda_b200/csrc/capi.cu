@@ -350,6 +350,18 @@ int ds4b200_e4m3_decode_f32(const uint8_t *codes, float *x, int64_t n, void *str
     return launched("e4m3_decode");
 }
 
+int ds4b200_swiglu_q8_K_rows_f32(const float *gate, const float *up, const float *weights, int8_t *xq,
+                                 float *xscale, int16_t *xbsums, float *mid_f32, int64_t n_tokens, int k,
+                                 int n, int mode, float clamp, int fast_exp, void *stream) {
+    REQUIRE(gate && up && xq && xscale && xbsums, "swiglu_q8_K_rows: null pointer");
+    REQUIRE(n_tokens >= 0 && k >= 1 && n >= 256 && n % 256 == 0, "swiglu_q8_K_rows: n must be a multiple of 256, got %d", n);
+    REQUIRE(mode >= DS4B200_GLU_PLAIN && mode <= DS4B200_GLU_CLAMP_SYM, "swiglu_q8_K_rows: unknown mode %d", mode);
+    REQUIRE(a16(gate) && a16(up) && a16(mid_f32) && a4(xq), "swiglu_q8_K_rows: pointers must be 16-byte aligned (xq: 4)");
+    ds4b200::swiglu_q8_K_rows(gate, up, weights, xq, xscale, xbsums, mid_f32, n_tokens * k, n, mode, clamp, fast_exp,
+                              STREAM(stream));
+    return launched("swiglu_q8_K_rows");
+}
+
 int ds4b200_compressor_step_f32(int is_attn, const float *kv_cur, float *sc_cur, const uint16_t *ape_f16,
                                 const float *norm_w, int head_dim, int compress_ratio, int pos, int il,
                                 float *state_kv, float *state_score, float *emit_out,

@@ -9,6 +9,7 @@
 // thread before the first use, stores are 128-bit, all coalesced.
 #include "device_utils.cuh"
 #include "kernels.cuh"
+#include "q8k_device.cuh"
 
 namespace ds4b200 {
 namespace {
@@ -104,6 +105,36 @@ swiglu_vec_kernel(const float *__restrict__ gate, const float *__restrict__ up,
     }
 }
 
+// SwiGLU whose output leaves as Q8_K blocks, the form the routed experts' down projection
+// takes its activations in (cuda/moe_iq2_pair.cu:159-235 quantises the f32 `mid` rows in a
+// second kernel).  One warp per 256-element block of one (token, slot) row: the eight values
+// of a lane go from the epilogue straight into the block quantiser, so the f32 rows are
+// neither written nor read back (mid_f32 is optional, for callers that want them too).
+template <int MODE, bool FAST>
+__global__ void __launch_bounds__(256)
+swiglu_q8k_kernel(const float *__restrict__ gate, const float *__restrict__ up,
+                  const float *__restrict__ weights, int8_t *__restrict__ xq, float *__restrict__ xscale,
+                  int16_t *__restrict__ xbsums, float *__restrict__ mid_f32, int64_t n_blocks,
+                  int blocks_per_row, float clamp) {
+    const int lane = threadIdx.x & 31;
+    const int64_t b = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (b >= n_blocks) return;
+    const int64_t base = b * 256;
+    float4 v0 = glu4<MODE, FAST>(ld_stream4(gate + base + 4 * lane), ld_stream4(up + base + 4 * lane), clamp);
+    float4 v1 = glu4<MODE, FAST>(ld_stream4(gate + base + 128 + 4 * lane), ld_stream4(up + base + 128 + 4 * lane), clamp);
+    if (weights) {
+        const float w = __ldg(weights + b / blocks_per_row);        // one weight per (token, slot) row
+        v0 = mul4_rn(v0, w);
+        v1 = mul4_rn(v1, w);
+    }
+    if (mid_f32) {
+        st_stream4(mid_f32 + base + 4 * lane, v0);
+        st_stream4(mid_f32 + base + 128 + 4 * lane, v1);
+    }
+    const float e[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    q8k_block_store(e, lane, xq + base, xscale + b, xbsums + b * 16);
+}
+
 template <int MODE, bool FAST>
 __global__ void swiglu_scalar_kernel(const float *gate, const float *up, const float *weights,
                                      float *out, int64_t n_tokens, int k, int n, float clamp,
@@ -185,6 +216,21 @@ void launch_mode(const float *gate, const float *up, const float *weights, float
 
 void div_selfcheck(uint64_t first, uint64_t count, unsigned long long *mismatches, cudaStream_t s) {
     if (count > 0) div_selfcheck_kernel<<<148 * 16, 256, 0, s>>>(first, count, mismatches);
+}
+
+void swiglu_q8_K_rows(const float *gate, const float *up, const float *weights, int8_t *xq, float *xscale,
+                      int16_t *xbsums, float *mid_f32, int64_t n_rows, int n, int mode, float clamp,
+                      int fast_exp, cudaStream_t s) {
+    const int blocks_per_row = n / 256;
+    const int64_t n_blocks = n_rows * blocks_per_row;
+    if (n_blocks <= 0) return;
+    const unsigned grid = (unsigned)((n_blocks + 7) / 8);
+#define DS4B200_Q8K(M, F) swiglu_q8k_kernel<M, F><<<grid, 256, 0, s>>>(gate, up, weights, xq, xscale, xbsums, mid_f32, \
+                                                                        n_blocks, blocks_per_row, clamp)
+    if (mode == DS4B200_GLU_PLAIN) { if (fast_exp) DS4B200_Q8K(DS4B200_GLU_PLAIN, true); else DS4B200_Q8K(DS4B200_GLU_PLAIN, false); }
+    else if (mode == DS4B200_GLU_CLAMP_REF) { if (fast_exp) DS4B200_Q8K(DS4B200_GLU_CLAMP_REF, true); else DS4B200_Q8K(DS4B200_GLU_CLAMP_REF, false); }
+    else { if (fast_exp) DS4B200_Q8K(DS4B200_GLU_CLAMP_SYM, true); else DS4B200_Q8K(DS4B200_GLU_CLAMP_SYM, false); }
+#undef DS4B200_Q8K
 }
 
 void swiglu_rows(const float *gate, const float *up, const float *weights, float *out,

@@ -95,6 +95,9 @@ bool compressor_step(int is_attn, const float *kv_cur, float *sc_cur, const uint
                      const float *norm_w, int head_dim, int ratio, int pos, const ds4b200_rope_params &rope,
                      int n_rot, float eps, float *state_kv, float *state_score, float *emit_out,
                      cudaStream_t s);
+void swiglu_q8_K_rows(const float *gate, const float *up, const float *weights, int8_t *xq, float *xscale,
+                      int16_t *xbsums, float *mid_f32, int64_t n_rows, int n, int mode, float clamp,
+                      int fast_exp, cudaStream_t s);
 void div_selfcheck(uint64_t first, uint64_t count, unsigned long long *mismatches, cudaStream_t s);
 void e4m3_encode(const float *x, uint8_t *codes, int64_t n, cudaStream_t s);
 void e4m3_decode(const uint8_t *codes, float *x, int64_t n, cudaStream_t s);

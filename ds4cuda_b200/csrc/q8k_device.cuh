@@ -1,0 +1,69 @@
+// q8k_device.cuh — the Q8_K block quantiser as a warp-collective device function, shared by
+// the stand-alone quantiser and by the SwiGLU kernel that quantises its own output
+// (cuda/moe_iq2_pair.cu:159-235 of the reference: per 256 elements int8 values, one f32 scale,
+// 16 partial sums; `max` is the element of largest magnitude, the first one on ties).
+#pragma once
+
+#include "device_utils.cuh"
+
+namespace ds4b200 {
+
+__device__ __forceinline__ int q8k_round(float v) {
+    const int q = __float2int_rn(v);           // ties to even, like lrintf
+    return q > 127 ? 127 : (q < -128 ? -128 : q);
+}
+__device__ __forceinline__ uint32_t q8k_pack4(int a, int b, int c, int d) {
+    return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) |
+           ((uint32_t)(d & 0xff) << 24);
+}
+
+// One warp, one block: lane l holds elements 4l..4l+3 in e[0..3] and 128+4l..128+4l+3 in
+// e[4..7].  Writes qb[256], *scale_b and sums_b[16].
+__device__ __forceinline__ void q8k_block_store(const float (&e)[8], int lane, int8_t *qb, float *scale_b,
+                                                int16_t *sums_b) {
+    // key = magnitude bits in the high word, inverted index in the low word: the maximum key
+    // is the largest magnitude and, among equals, the smallest index
+    unsigned long long key = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const uint32_t idx = (k < 4 ? 4 * lane + k : 128 + 4 * lane + (k - 4));
+        const unsigned long long cand = ((unsigned long long)__float_as_uint(fabsf(e[k])) << 32) | (0xffffffffu - idx);
+        key = cand > key ? cand : key;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, off);
+        key = other > key ? other : key;
+    }
+    const float amax = __uint_as_float((uint32_t)(key >> 32));
+    if (amax == 0.0f) {
+        reinterpret_cast<uint32_t *>(qb)[lane] = 0u;
+        reinterpret_cast<uint32_t *>(qb)[32 + lane] = 0u;
+        if (lane < 16) sums_b[lane] = 0;
+        if (lane == 0) *scale_b = 0.0f;
+        return;
+    }
+    const uint32_t idx = 0xffffffffu - (uint32_t)key;
+    const int k_own = (idx < 128 ? (int)(idx & 3u) : 4 + (int)(idx & 3u));
+    float mine = e[0];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) mine = (k == k_own) ? e[k] : mine;
+    const float smax = __shfl_sync(0xffffffffu, mine, (int)((idx & 127u) >> 2));
+    const float iscale = -127.0f / smax;
+    int q[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) q[k] = q8k_round(iscale * e[k]);
+    reinterpret_cast<uint32_t *>(qb)[lane] = q8k_pack4(q[0], q[1], q[2], q[3]);
+    reinterpret_cast<uint32_t *>(qb)[32 + lane] = q8k_pack4(q[4], q[5], q[6], q[7]);
+    // 16 consecutive values = 4 consecutive lanes of one half
+    int s0 = q[0] + q[1] + q[2] + q[3], s1 = q[4] + q[5] + q[6] + q[7];
+    s0 += __shfl_xor_sync(0xffffffffu, s0, 1); s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
+    s0 += __shfl_xor_sync(0xffffffffu, s0, 2); s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+    if ((lane & 3) == 0) {
+        sums_b[lane >> 2] = (int16_t)s0;
+        sums_b[8 + (lane >> 2)] = (int16_t)s1;
+    }
+    if (lane == 0) *scale_b = 1.0f / iscale;
+}
+
+}  // namespace ds4b200

@@ -7,6 +7,7 @@
 // lanes (3 shuffles), a Q8_K block is one warp holding two float4 per lane.
 #include "device_utils.cuh"
 #include "kernels.cuh"
+#include "q8k_device.cuh"
 
 namespace ds4b200 {
 namespace {
@@ -52,50 +53,7 @@ __global__ void quantize_q8_K_kernel(const float *__restrict__ x, int8_t *__rest
     const float *xb = x + b * 256;
     const float4 v0 = ld_stream4(xb + 4 * lane), v1 = ld_stream4(xb + 128 + 4 * lane);
     const float e[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-    // key = magnitude bits in the high word, inverted index in the low word: the maximum key
-    // is the largest magnitude and, among equals, the smallest index
-    unsigned long long key = 0;
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        const uint32_t idx = (k < 4 ? 4 * lane + k : 128 + 4 * lane + (k - 4));
-        const unsigned long long cand = ((unsigned long long)__float_as_uint(fabsf(e[k])) << 32) | (0xffffffffu - idx);
-        key = cand > key ? cand : key;
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-        const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, off);
-        key = other > key ? other : key;
-    }
-    const float amax = __uint_as_float((uint32_t)(key >> 32));
-    int8_t *qb = xq + b * 256;
-    if (amax == 0.0f) {
-        reinterpret_cast<uint32_t *>(qb)[lane] = 0u;
-        reinterpret_cast<uint32_t *>(qb)[32 + lane] = 0u;
-        if (lane < 16) xbsums[b * 16 + lane] = 0;
-        if (lane == 0) xscale[b] = 0.0f;
-        return;
-    }
-    const uint32_t idx = 0xffffffffu - (uint32_t)key;
-    const int k_own = (idx < 128 ? (int)(idx & 3u) : 4 + (int)(idx & 3u));
-    float mine = e[0];
-#pragma unroll
-    for (int k = 1; k < 8; ++k) mine = (k == k_own) ? e[k] : mine;
-    const float smax = __shfl_sync(0xffffffffu, mine, (int)((idx & 127u) >> 2));
-    const float iscale = -127.0f / smax;
-    int q[8];
-#pragma unroll
-    for (int k = 0; k < 8; ++k) q[k] = q8_round(iscale * e[k]);
-    reinterpret_cast<uint32_t *>(qb)[lane] = pack4(q[0], q[1], q[2], q[3]);
-    reinterpret_cast<uint32_t *>(qb)[32 + lane] = pack4(q[4], q[5], q[6], q[7]);
-    // 16 consecutive values = 4 consecutive lanes of one half
-    int s0 = q[0] + q[1] + q[2] + q[3], s1 = q[4] + q[5] + q[6] + q[7];
-    s0 += __shfl_xor_sync(0xffffffffu, s0, 1); s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
-    s0 += __shfl_xor_sync(0xffffffffu, s0, 2); s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
-    if ((lane & 3) == 0) {
-        xbsums[b * 16 + (lane >> 2)] = (int16_t)s0;
-        xbsums[b * 16 + 8 + (lane >> 2)] = (int16_t)s1;
-    }
-    if (lane == 0) xscale[b] = 1.0f / iscale;
+    q8k_block_store(e, lane, xq + b * 256, xscale + b, xbsums + b * 16);
 }
 
 // Scalar forms for buffers without 16-byte (input) / 4-byte (output) alignment.

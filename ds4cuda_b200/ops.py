@@ -19,7 +19,7 @@ __all__ = [
     "TABLE_F16", "TABLE_Q8_0", "RopeParams", "rope_params_for_layer", "rope_params_explicit",
     "add", "rms_norm_rows", "rms_norm_q8_0_rows", "quantize_q8_0_rows", "quantize_q8_K_rows", "embed_gather_rows", "rope_rows", "fp8_kv_round_trip_rows",
     "rope_fp8_store_rows", "fp8_cache_load_rows", "kv_rows_to_raw", "swa_window_push_rows", "swiglu_rows", "hc_pre_rows", "output_hc_head_rows", "hc_post_rows", "hc_sinkhorn_rows", "hc_sinkhorn_mix_rows",
-    "e4m3_encode", "e4m3_decode", "e4m3_selfcheck", "div_selfcheck", "device_status", "compressor_step",
+    "e4m3_encode", "e4m3_decode", "e4m3_selfcheck", "div_selfcheck", "device_status", "compressor_step", "swiglu_q8_K_rows",
 ]
 
 
@@ -168,6 +168,20 @@ def swa_window_push_rows(raw_kv, n_raw, new_rows):
     check(_lib.load().ds4b200_swa_window_push_rows_f32(_p(raw_kv), cap, n_raw, _p(new_rows), new_rows.shape[0], D,
                                                        C.byref(after), _s()))
     return after.value
+
+
+def swiglu_q8_K_rows(gate, up, weights=None, mode=GLU_PLAIN, clamp=0.0, fast_exp=False, want_f32=False):
+    """gate/up [T, k, n] -> Q8_K blocks of the [T, k, n] SwiGLU rows: (xq int8 [T,k,n], scales [T,k,n/256],
+    bsums int16 [T,k,n/256,16], mid f32 or None)."""
+    T, k, n = gate.shape
+    dev = gate.device
+    xq = torch.empty((T, k, n), dtype=torch.int8, device=dev)
+    xs = torch.empty((T, k, n // 256), dtype=torch.float32, device=dev)
+    bs = torch.empty((T, k, n // 256, 16), dtype=torch.int16, device=dev)
+    mid = torch.empty((T, k, n), dtype=torch.float32, device=dev) if want_f32 else None
+    check(_lib.load().ds4b200_swiglu_q8_K_rows_f32(_p(gate), _p(up), _p(weights), _p(xq), _p(xs), _p(bs), _p(mid),
+                                                   T, k, n, mode, clamp, int(fast_exp), _s()))
+    return xq, xs, bs, mid
 
 
 def compressor_step(is_attn, kv_cur, sc_cur, ape_f16, norm_w, head_dim, ratio, pos, il, state_kv, state_score,

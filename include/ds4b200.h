@@ -223,6 +223,16 @@ int ds4b200_kv_rows_to_raw_f32(const float *kv_in, int64_t n_rows, int head_dim,
 int ds4b200_swa_window_push_rows_f32(float *raw_kv, int cap, int n_raw, const float *new_rows,
                                      int n_new, int head_dim, int *n_raw_after, void *stream);
 
+/* SwiGLU whose output leaves as Q8_K blocks: mid[t][s][:] = glu(gate, up) * weights[t][s] (no
+ * sum over slots: the down projection is per expert), quantised per 256 elements exactly as
+ * ds4b200_quantize_q8_K_rows_f32 would quantise the f32 rows (cuda/moe_iq2_pair.cu:159-235,
+ * :352-373).  gate, up [n_tokens][k][n]; weights [n_tokens][k] nullable; xq int8 [n_tokens*k*n];
+ * xscale f32 and xbsums int16[16] per block; mid_f32 nullable (also writes the f32 rows).
+ * n a multiple of 256; pointers 16-byte aligned. */
+int ds4b200_swiglu_q8_K_rows_f32(const float *gate, const float *up, const float *weights, int8_t *xq,
+                                 float *xscale, int16_t *xbsums, float *mid_f32, int64_t n_tokens, int k,
+                                 int n, int mode, float clamp, int fast_exp, void *stream);
+
 /* One streaming-compressor step after its two projections: everything
  * launch_compressor_decode_step_f32{,_prealloc} (cuda/compressor.cuh:78,102; cuda/compressor.cu:328-420)
  * does once kv_cur / sc_cur = W_kv x, W_gate x are known, in one launch.

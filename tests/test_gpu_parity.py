@@ -773,3 +773,29 @@ def test_compressor_step_equals_the_reference_launcher(ops, ref, head_dim, is_at
         assert_bits(host(m_sc), host(r_sc), f"state_score, step {pos}")
         if emitted:
             assert_bits(host(m_emit), host(r_emit), f"emit, step {pos}")
+
+
+@pytest.mark.parametrize("T,k,n,fast", [(3, 6, 2048, True), (40, 6, 2048, False), (7, 1, 256, False), (5, 2, 1024, True)])
+def test_swiglu_with_fused_q8_K(ops, oracle, T, k, n, fast):
+    g = inputs.rng(950 + T + n)
+    gate, up = inputs.normal(g, (T, k, n), 2.0), inputs.normal(g, (T, k, n), 2.0)
+    w = inputs.router_weights(g, T, k)
+    gate[0, 0, :256] = 0.0                                  # an all-zero block
+    xq, xs, bs, mid = ops.swiglu_q8_K_rows(dev(gate), dev(up), dev(w), ops.GLU_CLAMP_REF, 10.0, fast_exp=fast,
+                                           want_f32=True)
+    # the f32 rows are the un-fused kernel's rows, bit for bit
+    plain = ops.swiglu_rows(dev(gate), dev(up), dev(w), ops.GLU_CLAMP_REF, 10.0, False, fast)
+    assert_bits(host(mid), host(plain), "f32 rows of the fused kernel vs swiglu_rows")
+    if not fast:
+        assert_close(host(mid), oracle.swiglu_rows(gate, up, w, oracle.GLU_CLAMP_REF, 10.0, False), what="mid rows")
+    # the quantiser is exact on the GPU's own rows
+    wq, ws, wb = oracle.quantize_q8_K_rows(host(mid).ravel())
+    assert_bits(host(xs).ravel(), ws, "Q8_K scales")
+    assert_bits(host(xq).ravel(), wq, "Q8_K values")
+    assert_bits(host(bs).ravel(), wb.ravel(), "Q8_K partial sums")
+    # and the same bits without the f32 output
+    xq2, xs2, bs2, none = ops.swiglu_q8_K_rows(dev(gate), dev(up), dev(w), ops.GLU_CLAMP_REF, 10.0, fast_exp=fast)
+    assert none is None
+    assert_bits(host(xq2), host(xq), "values, no f32 rows")
+    assert_bits(host(xs2), host(xs), "scales, no f32 rows")
+    assert_bits(host(bs2), host(bs), "sums, no f32 rows")
