@@ -38,8 +38,8 @@ FALLBACK_HBM_GBS = 6650.0      # earlier measurement on this pool, used only wit
 # at the benchmark shape, from the ncu capture summarised under profiles/.
 # Captured at 2048 tokens (profiles/ncu_full_set_small_case_2048tok.md) and scaled x2 to the
 # 4096-token launch; reads scale exactly, writes are undercounted by what the L2 still holds.
-NCU_TRAFFIC_BYTES = {"hcmix": 2 * (134360064 + 79665152), "swiglu": 2 * (201390848 + 10033152),
-                     "gather": 2 * (42454528 + 3393024), "kvstore": 2 * 4268032, "sinkhorn": 2 * 140032}
+NCU_TRAFFIC_BYTES = {"hcmix": 2 * (134360320 + 79656192), "swiglu": 2 * (201404160 + 10429952),
+                     "gather": 2 * (42454528 + 3300864), "kvstore": 2 * 4270848, "sinkhorn": 2 * 140032}
 
 
 def parse_args():
