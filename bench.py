@@ -301,6 +301,61 @@ def standalone_ops_leg(tokens, peak):
     return out
 
 
+def layer_row_stages_leg(tokens, peak):
+    """Every row stage of one layer in the order ds4_forward_layer runs them (cuda/forward_layer.cu:808-1461),
+    batched over `tokens` rows, with resident synthetic buffers standing in for the outputs of the matvec and
+    attention stages between them (those stages are outside this library).  One launch per stage between L2
+    flushes, CUDA events on torch's current stream; reports µs per stage and their sum."""
+    import torch
+    from ds4cuda_b200 import ops
+    dev, T, n = "cuda", tokens, N_EMBD
+    g = torch.Generator(device=dev).manual_seed(11)
+    rnd = lambda *shape, s=1.0: torch.randn(*shape, device=dev, generator=g) * s
+    flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    resid_hc = rnd(T, 4, n)
+    fn_a, fn_f = (rnd(24, 4 * n) / 128).half(), (rnd(24, 4 * n) / 128).half()
+    scale3, base24 = torch.ones(3, device=dev), torch.zeros(24, device=dev)
+    w_n = torch.rand(n, device=dev, generator=g) + 0.5
+    w_q = torch.rand(1024, device=dev, generator=g) + 0.5
+    w_kv = torch.rand(KV_DIM, device=dev, generator=g) + 0.5
+    pos = torch.arange(T, device=dev, dtype=torch.int32)
+    rope = ops.rope_params_for_layer(2)
+    q_lora, kv_raw = rnd(T, 1024), rnd(T, KV_DIM, s=1.5)
+    q_raw, kqv = rnd(T, 64, KV_DIM), rnd(T, 64, KV_DIM)
+    attn_out, moe_out, shexp = rnd(T, n), rnd(T, n), rnd(T, n)
+    sh_gate, sh_up = rnd(T, 1, FF_DIM, s=2.0), rnd(T, 1, FF_DIM, s=2.0)
+    gate, up = rnd(T, TOP_K, FF_DIM, s=2.0), rnd(T, TOP_K, FF_DIM, s=2.0)
+    w_r = torch.softmax(rnd(T, TOP_K), -1)
+    raw_rows = torch.empty(T, KV_DIM, device=dev)
+    st = {}
+
+    def stage(name, fn):
+        ts = []
+        for i in range(8):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); r = fn(); b.record(); torch.cuda.synchronize()
+            if i >= 2:
+                ts.append(a.elapsed_time(b) * 1e3)
+        st[name] = round(sorted(ts)[len(ts) // 2], 1)
+        return r
+
+    post_a, comb_a, x = stage("hc_attn_pre", lambda: ops.hc_pre_rows(resid_hc, fn_a, scale3, base24))
+    stage("attn_norm+q8_0", lambda: ops.rms_norm_q8_0_rows(x, w_n))
+    stage("q_a_norm", lambda: ops.rms_norm_rows(q_lora, w_q))
+    stage("kv_norm+rope+fp8+f16", lambda: ops.kv_rows_to_raw(kv_raw, pos, rope, raw_rows, norm_w=w_kv))
+    stage("q_norm+rope", lambda: ops.rope_rows(q_raw, pos, rope, unit_rms=True, out=q_raw))
+    stage("attn_out_inverse_rope", lambda: ops.rope_rows(kqv, pos, rope, inverse=True, out=kqv))
+    resid_attn = stage("hc_attn_post", lambda: ops.hc_post_rows(attn_out, resid_hc, post_a, comb_a))
+    post_f, comb_f, xf = stage("hc_ffn_pre", lambda: ops.hc_pre_rows(resid_attn, fn_f, scale3, base24))
+    stage("ffn_norm+q8_0", lambda: ops.rms_norm_q8_0_rows(xf, w_n))
+    stage("shared_silu_mul", lambda: ops.swiglu_rows(sh_gate, sh_up))
+    stage("expert_swiglu+q8_K", lambda: ops.swiglu_q8_K_rows(gate, up, w_r, ops.GLU_CLAMP_REF, 10.0, fast_exp=True))
+    stage("add+hc_ffn_post", lambda: ops.hc_post_rows(moe_out, resid_attn, post_f, comb_f, block_out2=shexp))
+    return {"tokens": T, "us_per_stage": st, "us_per_layer": round(sum(st.values()), 1),
+            "what": "batched row stages of one layer in forward_layer order; matvec / attention outputs are resident stand-ins"}
+
+
 def run_reference_arm(args):
     """The reference's CPU path: the scalar C restatement, all host threads, bounded sample per step."""
     rank = int(os.environ.get("RANK", "0"))
@@ -438,7 +493,17 @@ def run_ours(args):
 
     launches = path.launches_per_run(args.layers) * args.steps
     path.close()
-    standalone = standalone_ops_leg(tokens, peak) if (rank == 0 and world == 1) else None
+    # extra single-GPU legs; a failure there must not cost the main line
+    standalone = layer_stages = None
+    if rank == 0 and world == 1:
+        try:
+            standalone = standalone_ops_leg(tokens, peak)
+        except Exception as e:                      # noqa: BLE001
+            standalone = {"error": f"{type(e).__name__}: {e}"}
+        try:
+            layer_stages = layer_row_stages_leg(tokens, peak)
+        except Exception as e:                      # noqa: BLE001
+            layer_stages = {"error": f"{type(e).__name__}: {e}"}
     if world > 1:
         dist.destroy_process_group()
     if rank != 0:
@@ -451,7 +516,7 @@ def run_ours(args):
         "hbm_gbs_per_gpu": round(hbm_gbs_step, 1),
         "hbm_frac_of_peak": round(hbm_gbs_step / peak, 4), "hbm_frac_of_8000": round(hbm_gbs_step / 8000.0, 4),
         "ops": ops_table, "roofline": roofline, "cpu_baseline": cpu,
-        "reference_kernels_sm100a": ref_kernels, "standalone_ops": standalone,
+        "reference_kernels_sm100a": ref_kernels, "standalone_ops": standalone, "layer_row_stages": layer_stages,
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms_step,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "pipeline": f"{args.e2e_chunks} row slices over copy-in / compute / copy-out streams"},

@@ -1,0 +1,97 @@
+"""The row stages of one layer in the order ds4_forward_layer runs them (cuda/forward_layer.cu:808-1461),
+batched over T tokens through the C ABI, against the same chain on the CPU oracle.  The outputs of the
+matvec and attention stages in between are seeded stand-ins, the same on both sides."""
+import numpy as np
+import pytest
+import torch
+
+import inputs
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def host(t):
+    return t.cpu().numpy()
+
+
+def close(got, want, rel, what):
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    err = np.abs(got - want).max()
+    assert err <= rel * np.abs(want).max(), f"{what}: {err:.3e} > {rel * np.abs(want).max():.3e}"
+
+
+@pytest.mark.parametrize("T", [5, 80])          # 80 tokens: the HC pre steps run on the tensor cores
+def test_layer_row_stages_in_forward_order(ops, oracle, T):
+    g = inputs.rng(990 + T)
+    n, il = 4096, 2
+    resid_hc = inputs.normal(g, (T, 4, n))
+    wa, wf = inputs.hc_pre_weights(6, n), inputs.hc_pre_weights(7, n)
+    w_attn, w_ffn = inputs.uniform(g, (n,), 0.5, 1.5), inputs.uniform(g, (n,), 0.5, 1.5)
+    w_qa, w_kva = inputs.uniform(g, (1024,), 0.5, 1.5), inputs.uniform(g, (512,), 0.5, 1.5)
+    pos = (100 + np.arange(T)).astype(np.int32)
+    # stand-ins for what the matvecs and the attention hand to the next row stage
+    q_lora, kv_raw = inputs.normal(g, (T, 1024)), inputs.normal(g, (T, 512), 1.5)
+    q_raw, kqv = inputs.normal(g, (T, 64, 512)), inputs.normal(g, (T, 64, 512))
+    attn_out, moe_out, shexp = inputs.normal(g, (T, n)), inputs.normal(g, (T, n)), inputs.normal(g, (T, n))
+    sh_gate, sh_up = inputs.normal(g, (T, 1, 2048), 2.0), inputs.normal(g, (T, 1, 2048), 2.0)
+    gate, up = inputs.normal(g, (T, 6, 2048), 2.0), inputs.normal(g, (T, 6, 2048), 2.0)
+    w_r = inputs.router_weights(g, T, 6)
+    p_o = oracle.rope_params_for_layer(il)
+    p_d = ops.rope_params_for_layer(il)
+
+    # ---- device chain
+    post_a, comb_a, x = ops.hc_pre_rows(dev(resid_hc), dev(wa["fn"]), dev(wa["scale"]), dev(wa["base"]))
+    xn, _, xq, xs = ops.rms_norm_q8_0_rows(x, dev(w_attn))
+    qn, _, _ = ops.rms_norm_rows(dev(q_lora), dev(w_qa))
+    raw = torch.zeros(T, 512, device="cuda")
+    ops.kv_rows_to_raw(dev(kv_raw), dev(pos), p_d, raw, norm_w=dev(w_kva))
+    q_cur = ops.rope_rows(dev(q_raw), dev(pos), p_d, unit_rms=True)
+    kqv_back = ops.rope_rows(dev(kqv), dev(pos), p_d, inverse=True)
+    resid_attn = ops.hc_post_rows(dev(attn_out), dev(resid_hc), post_a, comb_a)
+    post_f, comb_f, xf = ops.hc_pre_rows(resid_attn, dev(wf["fn"]), dev(wf["scale"]), dev(wf["base"]))
+    xfn, _, _, _ = ops.rms_norm_q8_0_rows(xf, dev(w_ffn))
+    sh = ops.swiglu_rows(dev(sh_gate), dev(sh_up))
+    mq, ms, mb, mid = ops.swiglu_q8_K_rows(dev(gate), dev(up), dev(w_r), ops.GLU_CLAMP_REF, 10.0, want_f32=True)
+    out_hc = ops.hc_post_rows(dev(moe_out), resid_attn, post_f, comb_f, block_out2=dev(shexp))
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+
+    # ---- the same chain on the oracle, from the same first inputs
+    o_post_a, o_comb_a, o_x, _ = oracle.hc_pre_rows(resid_hc, wa["fn"], wa["scale"], wa["base"])
+    o_xn = oracle.rms_norm_rows(o_x, w_attn)[0]
+    o_qn = oracle.rms_norm_rows(q_lora, w_qa)[0]
+    o_q = oracle.rope_rows(q_raw, pos, p_o, unit_rms=True)
+    o_back = oracle.rope_rows(kqv, pos, p_o, inverse=True)
+    o_resid_attn = oracle.hc_post_rows(attn_out, resid_hc, o_post_a, o_comb_a)
+    o_post_f, o_comb_f, o_xf, _ = oracle.hc_pre_rows(o_resid_attn, wf["fn"], wf["scale"], wf["base"])
+    o_xfn = oracle.rms_norm_rows(o_xf, w_ffn)[0]
+    o_sh = oracle.swiglu_rows(sh_gate, sh_up)
+    o_mid = oracle.swiglu_rows(gate, up, w_r, oracle.GLU_CLAMP_REF, 10.0, False)
+    o_out = oracle.hc_post_rows(moe_out, o_resid_attn, o_post_f, o_comb_f, block_out2=shexp)
+
+    close(host(x), o_x, 1e-5, "hc_attn_pre out")
+    close(host(xn), o_xn, 1e-5, "attn_norm")
+    close(host(qn), o_qn, 1e-5, "q_a_norm")
+    close(host(q_cur), o_q, 2e-5, "q_norm + RoPE")
+    close(host(kqv_back), o_back, 2e-5, "inverse RoPE")
+    close(host(resid_attn), o_resid_attn, 1e-5, "hc_attn_post")
+    close(host(xf), o_xf, 2e-5, "hc_ffn_pre out (second hop of the chain)")
+    close(host(xfn), o_xfn, 2e-5, "ffn_norm")
+    close(host(sh), o_sh, 1e-5, "shared silu*up")
+    close(host(mid), o_mid, 1e-5, "routed epilogue rows")
+    close(host(out_hc), o_out, 2e-5, "residual streams after the layer")
+    # integer outputs are exact on the device's own f32 rows
+    wq, ws = oracle.quantize_q8_0_rows(host(xn))
+    assert np.array_equal(host(xq).ravel(), wq) and np.array_equal(host(xs).ravel(), ws.ravel())
+    kq, ks, kb = oracle.quantize_q8_K_rows(host(mid).ravel())
+    assert np.array_equal(host(mq).ravel(), kq) and np.array_equal(host(ms).ravel(), ks)
+    assert np.array_equal(host(mb).ravel(), kb.ravel())
+    # raw KV rows are f16-representable and agree with the oracle chain up to single grid steps
+    o_raw = oracle.kv_rows_to_raw(kv_raw, pos, p_o, norm_w=w_kva)
+    got_raw = host(raw)
+    assert np.array_equal(oracle.f16_round(got_raw), got_raw)
+    assert (got_raw != o_raw).mean() < 5e-3 and np.abs(got_raw - o_raw).max() <= 0.07 * np.abs(o_raw).max()
