@@ -34,10 +34,15 @@ __device__ __forceinline__ void rope_cs(const RopeDev &p, int k, float theta_ext
     if (inverse) s = -s;
 }
 
+// x0*c - x1*s and x0*s + x1*c with the roundings spelled out: x0 rounds x1*s and fuses x0*c
+// into the subtraction, x1 rounds x0*s and fuses x1*c into the addition.  That is what the
+// reference's expressions (cuda/rope.cu:199-200) compile to (checked bit for bit against its
+// kernel on the GPU); written with intrinsics the result does not depend on what the
+// surrounding code lets the compiler fuse.
 __device__ __forceinline__ void rotate(float &x0, float &x1, float c, float s) {
     const float a = x0, b = x1;
-    x0 = a * c - b * s;
-    x1 = a * s + b * c;
+    x0 = __fmaf_rn(a, c, -__fmul_rn(b, s));
+    x1 = __fmaf_rn(b, c, __fmul_rn(a, s));
 }
 
 inline RopeDev to_dev(const ds4b200_rope_params &p) {

@@ -37,6 +37,44 @@ __device__ __forceinline__ void rope_float4(float4 &v, int e_tail, float posf, f
     rotate(v.z, v.w, c, s);
 }
 
+// Rotate the tail of a row held by one warp (lane l holds float4 number l + 32 j).  With at
+// most 32 pairs, lane k evaluates the angle of pair k (the same k multiplies and the same
+// cosf / sinf as rope_float4) and the lanes that hold the tail fetch the two (cos, sin) they
+// need by shuffle, instead of 16 lanes doing two pairs each; more pairs fall back to
+// rope_float4 per lane.  Every lane of the warp must call this.
+template <int VPT>
+__device__ __forceinline__ void rope_tail_warp(float4 (&v)[VPT], int lane, int n4, int n_nope, int n_rot,
+                                               float posf, const RopeDev &p, bool inverse) {
+    const float ts = rope_theta_scale(p, n_rot);
+    if (n_rot <= 64) {
+        float c = 1.0f, sn = 0.0f;
+        if (2 * lane < n_rot) {
+            float te = posf;
+            for (int k = 0; k < lane; ++k) te *= ts;
+            rope_cs(p, lane, te, inverse, c, sn);
+        }
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            if ((32 * j + 31) * 4 < n_nope) continue;          // no lane of this j is in the tail
+            const int i = lane + 32 * j;
+            const bool tail = i < n4 && 4 * i >= n_nope;
+            const int k0 = tail ? (4 * i - n_nope) >> 1 : 0;
+            const float c0 = __shfl_sync(0xffffffffu, c, k0), s0 = __shfl_sync(0xffffffffu, sn, k0);
+            const float c1 = __shfl_sync(0xffffffffu, c, k0 + 1), s1 = __shfl_sync(0xffffffffu, sn, k0 + 1);
+            if (tail) {
+                rotate(v[j].x, v[j].y, c0, s0);
+                rotate(v[j].z, v[j].w, c1, s1);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int i = lane + 32 * j;
+            if (i < n4 && 4 * i >= n_nope) rope_float4(v[j], 4 * i - n_nope, posf, ts, p, inverse);
+        }
+    }
+}
+
 // ------------------------------- RoPE rows ---------------------------------
 template <int VPT>
 __global__ void __launch_bounds__(kRowsPerCta * 32)
@@ -64,13 +102,11 @@ rope_rows_kernel(const float *x_in, float *x_out, int64_t n_rows, int n_heads, i
         for (int j = 0; j < VPT; ++j) { v[j].x *= scale; v[j].y *= scale; v[j].z *= scale; v[j].w *= scale; }
     }
     const float posf = (float)(pos ? pos[row / n_heads] : single_pos);
-    const float ts = rope_theta_scale(p, n_rot);
+    rope_tail_warp<VPT>(v, lane, n4, n_nope, n_rot, posf, p, inverse != 0);
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
         const int i = lane + 32 * j;
-        if (i >= n4) continue;
-        if (4 * i >= n_nope) rope_float4(v[j], 4 * i - n_nope, posf, ts, p, inverse != 0);
-        st_stream4(yr + 4 * i, v[j]);
+        if (i < n4) st_stream4(yr + 4 * i, v[j]);
     }
 }
 
@@ -213,40 +249,8 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) rope_fp8_store_kernel(StoreA
                                v[j].z * scale * w4.z, v[j].w * scale * w4.w);
         }
     }
-    if (a.do_rope) {                                  // cuda/forward_layer.cu:910 KV RoPE
-        const float posf = (float)a.pos[row];
-        const float ts = rope_theta_scale(a.rope, a.n_rot);
-        if (a.n_rot <= 64) {
-            // At most 32 pairs: lane k evaluates the angle of pair k (the same k multiplies and
-            // the same cosf / sinf as in rope_float4), and the lanes that hold the tail fetch the
-            // two (cos, sin) they need by shuffle, instead of 16 lanes doing two pairs each.
-            float c = 1.0f, sn = 0.0f;
-            if (2 * lane < a.n_rot) {
-                float te = posf;
-                for (int k = 0; k < lane; ++k) te *= ts;
-                rope_cs(a.rope, lane, te, false, c, sn);
-            }
-#pragma unroll
-            for (int j = 0; j < VPT; ++j) {
-                if ((32 * j + 31) * 4 < n_nope) continue;          // no lane of this j is in the tail
-                const int i = lane + 32 * j;
-                const bool tail = i < n4 && 4 * i >= n_nope;
-                const int k0 = tail ? (4 * i - n_nope) >> 1 : 0;
-                const float c0 = __shfl_sync(0xffffffffu, c, k0), s0 = __shfl_sync(0xffffffffu, sn, k0);
-                const float c1 = __shfl_sync(0xffffffffu, c, k0 + 1), s1 = __shfl_sync(0xffffffffu, sn, k0 + 1);
-                if (tail) {
-                    rotate(v[j].x, v[j].y, c0, s0);
-                    rotate(v[j].z, v[j].w, c1, s1);
-                }
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < VPT; ++j) {
-                const int i = lane + 32 * j;
-                if (i < n4 && 4 * i >= n_nope) rope_float4(v[j], 4 * i - n_nope, posf, ts, a.rope, false);
-            }
-        }
-    }
+    if (a.do_rope)                                    // cuda/forward_layer.cu:910 KV RoPE
+        rope_tail_warp<VPT>(v, lane, n4, n_nope, a.n_rot, (float)a.pos[row], a.rope, false);
     if (a.rope_out) {
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
