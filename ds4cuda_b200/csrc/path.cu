@@ -4,6 +4,7 @@
 #include <cerrno>
 #include <cstring>
 #include <map>
+#include <tuple>
 #include <string>
 #include <vector>
 
@@ -35,6 +36,8 @@ struct ds4b200_path {
     std::vector<cudaEvent_t> chunk_events;
     // graph cache (one per layer count)
     std::map<int, cudaGraphExec_t> graphs;
+    // per row slice of the chunked host entry point: (first row, rows, layers) -> its layer chain
+    std::map<std::tuple<int64_t, int64_t, int>, cudaGraphExec_t> slice_graphs;
     std::vector<cudaEvent_t> events;
 };
 
@@ -233,6 +236,7 @@ void ds4b200_path_destroy(ds4b200_path *p) {
     if (p->stream) cudaStreamSynchronize(p->stream);
     if (p->side) cudaStreamSynchronize(p->side);
     for (auto &g : p->graphs) cudaGraphExecDestroy(g.second);
+    for (auto &g : p->slice_graphs) cudaGraphExecDestroy(g.second);
     if (p->ev_fork) cudaEventDestroy(p->ev_fork);
     if (p->ev_join) cudaEventDestroy(p->ev_join);
     if (p->side) cudaStreamDestroy(p->side);
@@ -361,7 +365,25 @@ int ds4b200_path_run_host_chunked(ds4b200_path *p, const ds4b200_path_io *h, int
         CUDA_OK(cudaEventRecord(in_ready, in), "path_run_host_chunked: event");
         // ---- the layer chain over this chunk's rows
         CUDA_OK(cudaStreamWaitEvent(s, in_ready, 0), "path_run_host_chunked: wait");
-        for (int layer = 0; layer < n_layers; ++layer) enqueue_layer(p, layer, -1, t0, n);
+        if (c.use_graph) {
+            // the slice's 43-layer chain is several hundred launches and event calls: replay it
+            // from a graph, or the host cannot keep the copy engines and the GPU busy
+            const auto key = std::make_tuple(t0, n, n_layers);
+            auto it = p->slice_graphs.find(key);
+            if (it == p->slice_graphs.end()) {
+                cudaGraph_t g = nullptr;
+                cudaGraphExec_t ge = nullptr;
+                CUDA_OK(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal), "path_run_host_chunked: begin capture");
+                for (int layer = 0; layer < n_layers; ++layer) enqueue_layer(p, layer, -1, t0, n);
+                CUDA_OK(cudaStreamEndCapture(s, &g), "path_run_host_chunked: end capture");
+                CUDA_OK(cudaGraphInstantiate(&ge, g, 0), "path_run_host_chunked: graph instantiate");
+                cudaGraphDestroy(g);
+                it = p->slice_graphs.emplace(key, ge).first;
+            }
+            CUDA_OK(cudaGraphLaunch(it->second, s), "path_run_host_chunked: graph launch");
+        } else {
+            for (int layer = 0; layer < n_layers; ++layer) enqueue_layer(p, layer, -1, t0, n);
+        }
         CUDA_OK(cudaGetLastError(), "path_run_host_chunked: launch");
         CUDA_OK(cudaEventRecord(done, s), "path_run_host_chunked: event");
         // ---- outputs of this chunk, on the copy-out stream
