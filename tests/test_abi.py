@@ -105,6 +105,14 @@ def test_checked_entry_points_reject_bad_arguments_without_a_gpu(lib):
     assert lib.ds4b200_hc_post_rows_f32(p, None, p, None, p, p, 2, 4096, None) == EINVAL
     assert lib.ds4b200_hc_post_rows_f32(None, p, p, None, p, p, 2, 4096, None) == EINVAL
     assert lib.ds4b200_hc_sinkhorn_mix_rows_f32(None, p, p, None, 2, 4096, 20, 1e-6, None) == EINVAL
+    assert lib.ds4b200_swiglu_q8_K_rows_f32(p, p, None, p, p, p, None, 2, 6, 2000, 1, 10.0, 1, None) == EINVAL
+    assert b"256" in lib.ds4b200_last_error()
+    assert lib.ds4b200_swiglu_q8_K_rows_f32(p, p, None, None, p, p, None, 2, 6, 2048, 1, 10.0, 1, None) == EINVAL
+    emitted = C.c_int(-1)
+    assert lib.ds4b200_compressor_step_f32(1, p, p, p, p, 500, 4, 3, 2, p, p, p, C.byref(emitted), None) == EINVAL
+    assert lib.ds4b200_compressor_step_f32(1, p, p, p, p, 512, 4, -1, 2, p, p, p, C.byref(emitted), None) == EINVAL
+    assert lib.ds4b200_compressor_step_f32(1, p, None, p, p, 512, 4, 3, 2, p, p, p, C.byref(emitted), None) == EINVAL
+    assert emitted.value == -1                                # untouched on a rejected call
     assert lib.ds4b200_path_create(None) is None
     from ds4cuda_b200._lib import PathConfig
     bad = PathConfig(n_tokens=0)
