@@ -41,6 +41,12 @@ def golden_inputs():
     d["head_scale"] = inputs.uniform(g, (1,), 0.5, 1.5)
     d["head_base"] = inputs.normal(g, (4,), 0.5)
     d["out_norm_w"] = inputs.uniform(g, (4096,), 0.5, 1.5)
+    # streaming compressor, ratio 4, 128 output columns, 8 steps (two windows)
+    d["comp_x"] = inputs.normal(g, (8, 256))
+    d["comp_w_kv"] = (g.standard_normal((256, 256), dtype=np.float32) / 16).astype(np.float16)
+    d["comp_w_gate"] = (g.standard_normal((256, 256), dtype=np.float32) / 8).astype(np.float16)
+    d["comp_ape"] = (g.standard_normal((4, 256), dtype=np.float32) / 2).astype(np.float16)
+    d["comp_norm_w"] = inputs.uniform(g, (128,), 0.5, 1.5)
     return d
 
 
@@ -103,6 +109,28 @@ def main(out_path):
     hn = torch.empty(4096, device="cuda")
     ref_lib.call("rms_norm_f32", ho, dev(d["out_norm_w"]), hn, 4096, 1e-6)
     out["output_hc_head"], out["output_norm"] = ho.cpu().numpy(), hn.cpu().numpy()
+    # the reference's compressor step launcher (cuda/compressor.cu:357-420), attention flavour
+    # (FP8 round trip on), layer 2; its two projections are stored too: they are the inputs of
+    # everything after them
+    width, in_dim, hd = 256, 256, 128
+    w_kv, w_gate, ape = dev(d["comp_w_kv"].view(np.int16)), dev(d["comp_w_gate"].view(np.int16)), dev(d["comp_ape"].view(np.int16))
+    nw = dev(d["comp_norm_w"])
+    s_kv, s_sc = torch.zeros(8, width, device="cuda"), torch.full((8, width), -1.0e30, device="cuda")
+    emit, sk, ss = torch.zeros(hd, device="cuda"), torch.empty(width, device="cuda"), torch.empty(width, device="cuda")
+    kv_cur, sc_pre, emits = [], [], []
+    for pos in range(8):
+        xx = dev(d["comp_x"][pos])
+        a, b = torch.empty(width, device="cuda"), torch.empty(width, device="cuda")
+        ref_lib.call("mul_mv_f16_f32", w_kv, xx, a, width, in_dim)
+        ref_lib.call("mul_mv_f16_f32", w_gate, xx, b, width, in_dim)
+        kv_cur.append(a.cpu().numpy()); sc_pre.append(b.cpu().numpy())
+        ref_lib.call("compressor_decode_step_prealloc", 1, xx, w_kv, w_gate, ape, nw, in_dim, hd, 4, pos, 2,
+                     s_kv, s_sc, emit, sk, ss)
+        if (pos + 1) % 4 == 0:
+            emits.append(emit.cpu().numpy().copy())
+    out["comp_kv_cur"], out["comp_sc_pre"] = np.stack(kv_cur), np.stack(sc_pre)
+    out["comp_state_kv"], out["comp_state_score"] = s_kv.cpu().numpy(), s_sc.cpu().numpy()
+    out["comp_emit"] = np.stack(emits)
     torch.cuda.synchronize()
     meta = {"gpu": torch.cuda.get_device_name(0), "cuda": torch.version.cuda}
     np.savez_compressed(out_path, __digests__=np.array(repr(digest(d))), __meta__=np.array(repr(meta)), **out)
