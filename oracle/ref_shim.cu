@@ -14,6 +14,7 @@
 #include "fp8_kv.cuh"
 #include "glu.cuh"
 #include "hc_sinkhorn.cuh"
+#include "moe_iq2_pair.cuh"
 #include "norm.cuh"
 #include "output_head.cuh"
 #include "rope.cuh"
@@ -102,6 +103,17 @@ void ds4ref_loop_hc_post(const float *block_out, const float *residual_hc, const
                            out_hc + (size_t)t * 4 * n_embd, 4, n_embd, S(s));
 }
 
+
+// The two activation quantisers: Q8_K has its own launcher; Q8_0 runs inside the Q8_0 matvec and
+// leaves its result in the caller's scratch.
+void ds4ref_quantize_fp32_to_q8_K(const float *x, int8_t *xq, float *xscale, int16_t *xbsums, int n_blocks, void *s) {
+    launch_quantize_fp32_to_q8_K(x, xq, xscale, xbsums, n_blocks, S(s));
+}
+void ds4ref_mul_mv_q8_0_q8_0_f32_prealloc(const void *w_blocks, const float *x, float *y, int n_rows, int n_cols,
+                                          int8_t *scratch_xq, float *scratch_xscale, void *s) {
+    launch_mul_mv_q8_0_q8_0_f32_prealloc(static_cast<const block_q8_0 *>(w_blocks), x, y, n_rows, n_cols, scratch_xq,
+                                         scratch_xscale, S(s));
+}
 
 void ds4ref_mul_mv_f16_f32(const uint16_t *w, const float *x, float *y, int out_dim, int in_dim, void *s) {
     launch_mul_mv_f16_f32(w, x, y, out_dim, in_dim, S(s));

@@ -799,3 +799,36 @@ def test_swiglu_with_fused_q8_K(ops, oracle, T, k, n, fast):
     assert_bits(host(xq2), host(xq), "values, no f32 rows")
     assert_bits(host(xs2), host(xs), "scales, no f32 rows")
     assert_bits(host(bs2), host(bs), "sums, no f32 rows")
+
+
+def test_activation_quantisers_equal_the_reference_kernels(ops, ref):
+    """Q8_K against the reference's launcher, Q8_0 against what its Q8_0 matvec leaves in the caller's
+    scratch (cuda/moe_iq2_pair.cu:159-235, cuda/dense_q8.cu:122-168): bit for bit."""
+    if not ref:
+        pytest.skip("reference kernels not built")
+    g = inputs.rng(970)
+    x = inputs.normal(g, 16 * 256, 2.0)
+    x[:256] = 0.0                                            # an all-zero block
+    x[256:512] = np.clip(x[256:512], -3, 3)
+    x[256 + 200], x[256 + 17] = -3.5, 3.5                    # equal magnitudes: the first one sets the sign
+    dx = dev(x)
+    xq, xs, bs = ops.quantize_q8_K_rows(dx)
+    rq = torch.empty(x.size, dtype=torch.int8, device="cuda")
+    rs = torch.empty(16, dtype=torch.float32, device="cuda")
+    rb = torch.empty(16 * 16, dtype=torch.int16, device="cuda")
+    ref.call("quantize_fp32_to_q8_K", dx, rq, rs, rb, 16)
+    assert_bits(host(xq).ravel(), host(rq), "Q8_K values vs reference kernel")
+    assert_bits(host(xs).ravel(), host(rs), "Q8_K scales vs reference kernel")
+    assert_bits(host(bs).ravel(), host(rb), "Q8_K partial sums vs reference kernel")
+    # Q8_0: a 4-row Q8_0 matrix is enough to make the reference quantise the activation
+    n_cols = 4096
+    xa = inputs.normal(g, n_cols, 1.5)
+    xa[:32] = 0.0
+    w = dev(inputs.q8_0_table(g, 4, n_cols))
+    y = torch.empty(4, device="cuda")
+    sq = torch.empty(n_cols, dtype=torch.int8, device="cuda")
+    ss = torch.empty(n_cols // 32, dtype=torch.float32, device="cuda")
+    ref.call("mul_mv_q8_0_q8_0_f32_prealloc", w, dev(xa), y, 4, n_cols, sq, ss)
+    mq, ms = ops.quantize_q8_0_rows(dev(xa))
+    assert_bits(host(mq).ravel(), host(sq), "Q8_0 values vs reference kernel")
+    assert_bits(host(ms).ravel(), host(ss), "Q8_0 scales vs reference kernel")
