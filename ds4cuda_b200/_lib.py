@@ -36,6 +36,31 @@ class PathIO(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in INPUTS + OUTPUTS]
 
 
+class LayerDims(C.Structure):
+    """Mirror of `ds4b200_layer_dims` (include/ds4b200_layer.h)."""
+    _fields_ = [(n, C.c_int32) for n in ("n_embd", "n_heads", "head_dim", "n_rot", "q_lora", "ff_dim", "top_k",
+                                         "sinkhorn_iters", "il", "glu_fast_exp")] + [("eps", C.c_float),
+                                                                                      ("clamp", C.c_float)]
+
+
+class LayerWeights(C.Structure):
+    """Mirror of `ds4b200_layer_weights` (device pointers)."""
+    NAMES = ("hc_attn_fn", "hc_attn_scale", "hc_attn_base", "attn_norm", "q_a_norm", "kv_a_norm", "hc_ffn_fn",
+             "hc_ffn_scale", "hc_ffn_base", "ffn_norm")
+    _fields_ = [(n, C.c_void_p) for n in NAMES]
+
+
+class LayerBuffers(C.Structure):
+    """Mirror of `ds4b200_layer_buffers` (device pointers)."""
+    NAMES = ("x", "x_norm", "xq", "xscale", "q_lora", "q_lora_norm", "kv_raw", "raw_rows", "q", "kqv", "attn_out",
+             "post", "comb", "resid_mid", "sh_gate", "sh_up", "sh_mid", "gate", "up", "router_w", "mid_q",
+             "mid_scale", "mid_bsums", "moe_out", "shexp_out")
+    _fields_ = [(n, C.c_void_p) for n in NAMES]
+
+
+STAGE_QKV_A, STAGE_Q_B, STAGE_ATTENTION, STAGE_ATTN_OUT, STAGE_FFN_UP, STAGE_FFN_DOWN = range(6)
+StageHook = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int, C.c_int64, C.c_void_p)
+
 TABLE_F16, TABLE_Q8_0 = 0, 1
 FP8_BLOCK64_POW2, FP8_ROW_AMAX = 0, 1
 GLU_PLAIN, GLU_CLAMP_REF, GLU_CLAMP_SYM = 0, 1, 2
@@ -87,6 +112,8 @@ SIGNATURES = {
     "ds4b200_e4m3_encode_f32": (_I, [_P, _P, _L, _P]),
     "ds4b200_e4m3_decode_f32": (_I, [_P, _P, _L, _P]),
     "ds4b200_e4m3_selfcheck": (_I, [C.c_uint32, C.c_uint64, _P, _P]),
+    "ds4b200_layer_rows_f32": (_I, [C.POINTER(LayerDims), C.POINTER(LayerWeights), C.POINTER(LayerBuffers), _P, _P, _L, _P,
+                               StageHook, _P, _P]),
     "ds4b200_swiglu_q8_K_rows_f32": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, C.c_float, _I, _P]),
     "ds4b200_compressor_step_f32": (_I, [_I, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, C.POINTER(C.c_int), _P]),
     "ds4b200_div_selfcheck": (_I, [C.c_uint64, C.c_uint64, _P, _P]),

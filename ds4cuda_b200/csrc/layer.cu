@@ -1,0 +1,88 @@
+// layer.cu — host side of ds4b200_layer_rows_f32: the row stages of one layer for a chunk of
+// tokens, one launch per stage, with the caller's matvec / attention stages run through a
+// hook at the points where ds4_forward_layer calls them (cuda/forward_layer.cu:808-1461).
+// Pure sequencing: every stage is one of the batched kernels of this library.
+#include <cerrno>
+
+#include "../../include/ds4b200_layer.h"
+#include "kernels.cuh"
+
+using ds4b200::set_error;
+
+namespace {
+
+int launch_ok(const char *what) {
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : set_error(-EIO, "layer_rows: %s: %s", what, cudaGetErrorString(e));
+}
+
+}  // namespace
+
+extern "C" int ds4b200_layer_rows_f32(const ds4b200_layer_dims *d, const ds4b200_layer_weights *w,
+                                      const ds4b200_layer_buffers *b, const float *resid_in, const int32_t *pos,
+                                      int64_t T, float *resid_out, ds4b200_stage_hook hook, void *user,
+                                      void *stream) {
+    if (!d || !w || !b || !resid_in || !pos || !resid_out || !hook)
+        return set_error(-EINVAL, "layer_rows: null argument");
+    if (T <= 0) return T == 0 ? 0 : set_error(-EINVAL, "layer_rows: negative token count");
+    if (d->n_embd <= 0 || d->n_embd % 32 || d->n_embd > 8192 || d->n_heads <= 0 || d->head_dim <= 0 ||
+        d->head_dim % 4 || d->head_dim > 1024 || d->n_rot <= 0 || d->n_rot % 64 || (d->head_dim - d->n_rot) % 64 ||
+        d->q_lora <= 0 || d->ff_dim <= 0 || d->ff_dim % 256 || d->top_k <= 0 || d->sinkhorn_iters <= 0)
+        return set_error(-EINVAL, "layer_rows: unsupported geometry");
+    const void *need[] = {w->hc_attn_fn, w->hc_attn_scale, w->hc_attn_base, w->attn_norm, w->q_a_norm, w->kv_a_norm,
+                          w->hc_ffn_fn, w->hc_ffn_scale, w->hc_ffn_base, w->ffn_norm, b->x, b->x_norm, b->xq,
+                          b->xscale, b->q_lora, b->q_lora_norm, b->kv_raw, b->raw_rows, b->q, b->kqv, b->attn_out,
+                          b->post, b->comb, b->resid_mid, b->sh_gate, b->sh_up, b->sh_mid, b->gate, b->up,
+                          b->router_w, b->mid_q, b->mid_scale, b->mid_bsums, b->moe_out, b->shexp_out};
+    for (const void *p : need)
+        if (!p) return set_error(-EINVAL, "layer_rows: null weight or buffer");
+
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int n = d->n_embd, hd = d->head_dim;
+    ds4b200_rope_params rope;
+    ds4b200_rope_params_for_layer(d->il, d->n_rot, &rope);
+    auto call = [&](int stage) {
+        const int rc = hook(user, stage, T, stream);
+        return rc ? set_error(rc, "layer_rows: hook stage %d returned %d", stage, rc) : 0;
+    };
+    int rc;
+
+    // ---- attention half
+    ds4b200::hc_pre_rows(resid_in, w->hc_attn_fn, w->hc_attn_scale, w->hc_attn_base, b->post, b->comb, b->x, T, n,
+                         d->sinkhorn_iters, d->eps, s);
+    ds4b200::rms_norm_rows(b->x, nullptr, w->attn_norm, n, b->x_norm, nullptr, nullptr, T, n, d->eps, s, b->xq,
+                           b->xscale);
+    if ((rc = launch_ok("hc attn pre / attn norm"))) return rc;
+    if ((rc = call(DS4B200_STAGE_QKV_A))) return rc;
+    ds4b200::rms_norm_rows(b->q_lora, nullptr, w->q_a_norm, d->q_lora, b->q_lora_norm, nullptr, nullptr, T, d->q_lora,
+                           d->eps, s);
+    ds4b200::rope_fp8_store_rows(b->kv_raw, T, hd, d->n_rot, pos, &rope, w->kv_a_norm, d->eps,
+                                 DS4B200_FP8_BLOCK64_POW2, nullptr, nullptr, nullptr, nullptr, nullptr, s,
+                                 b->raw_rows);
+    if ((rc = launch_ok("q_a norm / kv chain"))) return rc;
+    if ((rc = call(DS4B200_STAGE_Q_B))) return rc;
+    ds4b200::rope_rows(b->q, b->q, T, d->n_heads, hd, d->n_rot, pos, 0, rope, 0, 1, d->eps, s);
+    if ((rc = launch_ok("q norm + RoPE"))) return rc;
+    if ((rc = call(DS4B200_STAGE_ATTENTION))) return rc;
+    ds4b200::rope_rows(b->kqv, b->kqv, T, d->n_heads, hd, d->n_rot, pos, 0, rope, 1, 0, d->eps, s);
+    if ((rc = launch_ok("inverse RoPE"))) return rc;
+    if ((rc = call(DS4B200_STAGE_ATTN_OUT))) return rc;
+    ds4b200::hc_post_rows(b->attn_out, nullptr, resid_in, b->post, b->comb, nullptr, nullptr, b->resid_mid, T, n, 0,
+                          0.0f, s);
+
+    // ---- feed-forward half
+    ds4b200::hc_pre_rows(b->resid_mid, w->hc_ffn_fn, w->hc_ffn_scale, w->hc_ffn_base, b->post, b->comb, b->x, T, n,
+                         d->sinkhorn_iters, d->eps, s);
+    ds4b200::rms_norm_rows(b->x, nullptr, w->ffn_norm, n, b->x_norm, nullptr, nullptr, T, n, d->eps, s, b->xq,
+                           b->xscale);
+    if ((rc = launch_ok("hc attn post / hc ffn pre / ffn norm"))) return rc;
+    if ((rc = call(DS4B200_STAGE_FFN_UP))) return rc;
+    ds4b200::swiglu_rows(b->sh_gate, b->sh_up, nullptr, b->sh_mid, T, 1, d->ff_dim, DS4B200_GLU_PLAIN, 0.0f, 0, 0, s);
+    ds4b200::swiglu_q8_K_rows(b->gate, b->up, b->router_w, b->mid_q, b->mid_scale, b->mid_bsums, nullptr,
+                              T * d->top_k, d->ff_dim, DS4B200_GLU_CLAMP_REF, d->clamp, d->glu_fast_exp, s);
+    if ((rc = launch_ok("shared silu / routed epilogue"))) return rc;
+    if ((rc = call(DS4B200_STAGE_FFN_DOWN))) return rc;
+    ds4b200::hc_post_rows(b->moe_out, b->shexp_out, b->resid_mid, b->post, b->comb, nullptr, nullptr, resid_out, T, n,
+                          0, 0.0f, s);
+    return launch_ok("add + hc ffn post");
+}

@@ -26,7 +26,7 @@ def _declared(header: str):
 
 def test_every_declared_c_symbol_is_exported_and_bound(lib):
     from ds4cuda_b200 import _lib
-    names = _declared("ds4b200.h") + _declared("ds4b200_path.h")
+    names = _declared("ds4b200.h") + _declared("ds4b200_path.h") + _declared("ds4b200_layer.h")
     assert len(names) > 40
     for n in names:
         assert hasattr(lib, n), f"{n} declared in include/ but not exported"
@@ -113,6 +113,16 @@ def test_checked_entry_points_reject_bad_arguments_without_a_gpu(lib):
     assert lib.ds4b200_compressor_step_f32(1, p, p, p, p, 512, 4, -1, 2, p, p, p, C.byref(emitted), None) == EINVAL
     assert lib.ds4b200_compressor_step_f32(1, p, None, p, p, 512, 4, 3, 2, p, p, p, C.byref(emitted), None) == EINVAL
     assert emitted.value == -1                                # untouched on a rejected call
+    from ds4cuda_b200._lib import LayerBuffers, LayerDims, LayerWeights, StageHook
+    hook = StageHook(lambda user, stage, n, stream: 0)
+    dims = LayerDims(4096, 64, 512, 64, 1024, 2048, 6, 20, 2, 1, 1e-6, 10.0)
+    wts, bufs = LayerWeights(), LayerBuffers()                 # all null
+    assert lib.ds4b200_layer_rows_f32(C.byref(dims), C.byref(wts), C.byref(bufs), p, p, 4, p, hook, None, None) == EINVAL
+    assert b"null weight or buffer" in lib.ds4b200_last_error()
+    assert lib.ds4b200_layer_rows_f32(None, C.byref(wts), C.byref(bufs), p, p, 4, p, hook, None, None) == EINVAL
+    bad_dims = LayerDims(4096, 64, 500, 64, 1024, 2048, 6, 20, 2, 1, 1e-6, 10.0)
+    assert lib.ds4b200_layer_rows_f32(C.byref(bad_dims), C.byref(wts), C.byref(bufs), p, p, 4, p, hook, None, None) == EINVAL
+    assert b"geometry" in lib.ds4b200_last_error()
     assert lib.ds4b200_path_create(None) is None
     from ds4cuda_b200._lib import PathConfig
     bad = PathConfig(n_tokens=0)

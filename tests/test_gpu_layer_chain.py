@@ -95,3 +95,88 @@ def test_layer_row_stages_in_forward_order(ops, oracle, T):
     got_raw = host(raw)
     assert np.array_equal(oracle.f16_round(got_raw), got_raw)
     assert (got_raw != o_raw).mean() < 5e-3 and np.abs(got_raw - o_raw).max() <= 0.07 * np.abs(o_raw).max()
+
+
+def test_layer_rows_entry_point_sequences_the_same_chain(ops):
+    """ds4b200_layer_rows_f32 with a hook that supplies the stand-ins == the same stages called one by one."""
+    import ctypes as C
+    from ds4cuda_b200 import _lib
+    L = _lib.load()
+    T, n, H, hd, ql, ff, k, il = 70, 4096, 64, 512, 1024, 2048, 6, 2
+    g = inputs.rng(995)
+    resid_hc = dev(inputs.normal(g, (T, 4, n)))
+    wa, wf = inputs.hc_pre_weights(6, n), inputs.hc_pre_weights(7, n)
+    W = dict(hc_attn_fn=dev(wa["fn"]), hc_attn_scale=dev(wa["scale"]), hc_attn_base=dev(wa["base"]),
+             attn_norm=dev(inputs.uniform(g, (n,), 0.5, 1.5)), q_a_norm=dev(inputs.uniform(g, (ql,), 0.5, 1.5)),
+             kv_a_norm=dev(inputs.uniform(g, (hd,), 0.5, 1.5)), hc_ffn_fn=dev(wf["fn"]),
+             hc_ffn_scale=dev(wf["scale"]), hc_ffn_base=dev(wf["base"]), ffn_norm=dev(inputs.uniform(g, (n,), 0.5, 1.5)))
+    pos = dev((100 + np.arange(T)).astype(np.int32))
+    S = dict(q_lora=dev(inputs.normal(g, (T, ql))), kv_raw=dev(inputs.normal(g, (T, hd), 1.5)),
+             q=dev(inputs.normal(g, (T, H, hd))), kqv=dev(inputs.normal(g, (T, H, hd))),
+             attn_out=dev(inputs.normal(g, (T, n))), sh_gate=dev(inputs.normal(g, (T, 1, ff), 2.0)),
+             sh_up=dev(inputs.normal(g, (T, 1, ff), 2.0)), gate=dev(inputs.normal(g, (T, k, ff), 2.0)),
+             up=dev(inputs.normal(g, (T, k, ff), 2.0)), router_w=dev(inputs.router_weights(g, T, k)),
+             moe_out=dev(inputs.normal(g, (T, n))), shexp_out=dev(inputs.normal(g, (T, n))))
+    f32 = lambda *shape: torch.zeros(*shape, device="cuda")
+    B = dict(x=f32(T, n), x_norm=f32(T, n), xq=torch.zeros(T, n, dtype=torch.int8, device="cuda"), xscale=f32(T, n // 32),
+             q_lora=f32(T, ql), q_lora_norm=f32(T, ql), kv_raw=f32(T, hd), raw_rows=f32(T, hd), q=f32(T, H, hd),
+             kqv=f32(T, H, hd), attn_out=f32(T, n), post=f32(T, 4), comb=f32(T, 16), resid_mid=f32(T, 4, n),
+             sh_gate=f32(T, 1, ff), sh_up=f32(T, 1, ff), sh_mid=f32(T, 1, ff), gate=f32(T, k, ff), up=f32(T, k, ff),
+             router_w=f32(T, k), mid_q=torch.zeros(T, k, ff, dtype=torch.int8, device="cuda"),
+             mid_scale=f32(T, k, ff // 256), mid_bsums=torch.zeros(T, k, ff // 256, 16, dtype=torch.int16, device="cuda"),
+             moe_out=f32(T, n), shexp_out=f32(T, n))
+    fills = {_lib.STAGE_QKV_A: ("q_lora", "kv_raw"), _lib.STAGE_Q_B: ("q",), _lib.STAGE_ATTENTION: ("kqv",),
+             _lib.STAGE_ATTN_OUT: ("attn_out",), _lib.STAGE_FFN_UP: ("sh_gate", "sh_up", "gate", "up", "router_w"),
+             _lib.STAGE_FFN_DOWN: ("moe_out", "shexp_out")}
+    seen, snap = [], {}
+
+    def hook(user, stage, n_tokens, stream):
+        seen.append(stage)
+        if stage == _lib.STAGE_QKV_A:
+            snap["x_norm"], snap["xq"] = B["x_norm"].clone(), B["xq"].clone()    # the attention half's, before reuse
+        for name in fills[stage]:
+            B[name].copy_(S[name])
+        return 0
+
+    dims = _lib.LayerDims(n, H, hd, 64, ql, ff, k, 20, il, 1, 1e-6, 10.0)
+    weights = _lib.LayerWeights(*[W[nm].data_ptr() for nm in _lib.LayerWeights.NAMES])
+    buffers = _lib.LayerBuffers(*[B[nm].data_ptr() for nm in _lib.LayerBuffers.NAMES])
+    out = torch.zeros(T, 4, n, device="cuda")
+    cb = _lib.StageHook(hook)
+    rc = L.ds4b200_layer_rows_f32(C.byref(dims), C.byref(weights), C.byref(buffers), resid_hc.data_ptr(),
+                                  pos.data_ptr(), T, out.data_ptr(), cb, None, None)
+    assert rc == 0, L.ds4b200_last_error()
+    torch.cuda.synchronize()
+    assert seen == list(range(6))
+
+    # ---- the same stages one by one
+    p = ops.rope_params_for_layer(il)
+    post_a, comb_a, x = ops.hc_pre_rows(resid_hc, W["hc_attn_fn"], W["hc_attn_scale"], W["hc_attn_base"])
+    xn, _, xq, _ = ops.rms_norm_q8_0_rows(x, W["attn_norm"])
+    qn, _, _ = ops.rms_norm_rows(S["q_lora"], W["q_a_norm"])
+    raw = torch.zeros(T, hd, device="cuda")
+    ops.kv_rows_to_raw(S["kv_raw"], pos, p, raw, norm_w=W["kv_a_norm"])
+    q_cur = ops.rope_rows(S["q"], pos, p, unit_rms=True)
+    kqv_back = ops.rope_rows(S["kqv"], pos, p, inverse=True)
+    resid_attn = ops.hc_post_rows(S["attn_out"], resid_hc, post_a, comb_a)
+    post_f, comb_f, xf = ops.hc_pre_rows(resid_attn, W["hc_ffn_fn"], W["hc_ffn_scale"], W["hc_ffn_base"])
+    xfn, _, xfq, _ = ops.rms_norm_q8_0_rows(xf, W["ffn_norm"])
+    sh = ops.swiglu_rows(S["sh_gate"], S["sh_up"])
+    mq, ms, mb, _ = ops.swiglu_q8_K_rows(S["gate"], S["up"], S["router_w"], ops.GLU_CLAMP_REF, 10.0, fast_exp=True)
+    want = ops.hc_post_rows(S["moe_out"], resid_attn, post_f, comb_f, block_out2=S["shexp_out"])
+    torch.cuda.synchronize()
+    eq = lambda a, b, what: (torch.equal(a, b) or pytest.fail(f"{what} differs"))
+    eq(snap["x_norm"], xn, "attn norm"); eq(snap["xq"], xq, "attn norm Q8_0")
+    eq(B["q_lora_norm"], qn, "q_a norm"); eq(B["raw_rows"], raw, "raw KV rows")
+    eq(B["q"], q_cur, "q norm + RoPE"); eq(B["kqv"], kqv_back, "inverse RoPE")
+    eq(B["resid_mid"], resid_attn, "hc attn post"); eq(B["x_norm"], xfn, "ffn norm"); eq(B["xq"], xfq, "ffn norm Q8_0")
+    eq(B["sh_mid"], sh, "shared silu*up"); eq(B["mid_q"], mq, "routed epilogue Q8_K values")
+    eq(B["mid_scale"], ms, "routed epilogue Q8_K scales"); eq(B["mid_bsums"], mb, "routed epilogue Q8_K sums")
+    eq(out, want, "residual streams after the layer")
+
+    # a hook that fails stops the layer with its code
+    bad = _lib.StageHook(lambda user, stage, n_tokens, stream: -7 if stage == _lib.STAGE_Q_B else 0)
+    assert L.ds4b200_layer_rows_f32(C.byref(dims), C.byref(weights), C.byref(buffers), resid_hc.data_ptr(),
+                                    pos.data_ptr(), T, out.data_ptr(), bad, None, None) == -7
+    assert b"stage 1" in L.ds4b200_last_error()
+    torch.cuda.synchronize()
