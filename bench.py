@@ -352,7 +352,41 @@ def layer_row_stages_leg(tokens, peak):
     stage("shared_silu_mul", lambda: ops.swiglu_rows(sh_gate, sh_up))
     stage("expert_swiglu+q8_K", lambda: ops.swiglu_q8_K_rows(gate, up, w_r, ops.GLU_CLAMP_REF, 10.0, fast_exp=True))
     stage("add+hc_ffn_post", lambda: ops.hc_post_rows(moe_out, resid_attn, post_f, comb_f, block_out2=shexp))
+    # the same twelve stages through the one-call entry point (no-op hook: the stand-ins above are
+    # already in place), back to back without flushes: what the row stages of a layer cost in a chunk
+    import ctypes as C
+    from ds4cuda_b200 import _lib
+    L = _lib.load()
+    z = lambda *shape, dt=torch.float32: torch.zeros(*shape, dtype=dt, device=dev)
+    bufs = dict(x=z(T, n), x_norm=z(T, n), xq=z(T, n, dt=torch.int8), xscale=z(T, n // 32), q_lora=q_lora,
+                q_lora_norm=z(T, 1024), kv_raw=kv_raw, raw_rows=raw_rows, q=q_raw, kqv=kqv, attn_out=attn_out,
+                post=z(T, 4), comb=z(T, 16), resid_mid=z(T, 4, n), sh_gate=sh_gate, sh_up=sh_up, sh_mid=z(T, FF_DIM),
+                gate=gate, up=up, router_w=w_r, mid_q=z(T, TOP_K, FF_DIM, dt=torch.int8),
+                mid_scale=z(T, TOP_K, FF_DIM // 256), mid_bsums=z(T, TOP_K, FF_DIM // 256, 16, dt=torch.int16),
+                moe_out=moe_out, shexp_out=shexp)
+    wts = dict(hc_attn_fn=fn_a, hc_attn_scale=scale3, hc_attn_base=base24, attn_norm=w_n, q_a_norm=w_q, kv_a_norm=w_kv,
+               hc_ffn_fn=fn_f, hc_ffn_scale=scale3, hc_ffn_base=base24, ffn_norm=w_n)
+    dims = _lib.LayerDims(n, 64, KV_DIM, N_ROT, 1024, FF_DIM, TOP_K, 20, 2, 1, 1e-6, 10.0)
+    lw = _lib.LayerWeights(*[wts[k].data_ptr() for k in _lib.LayerWeights.NAMES])
+    lb = _lib.LayerBuffers(*[bufs[k].data_ptr() for k in _lib.LayerBuffers.NAMES])
+    hook = _lib.StageHook(lambda user, stage, n_tok, stream: 0)
+    out_hc = torch.empty_like(resid_hc)
+
+    def whole():
+        rc = L.ds4b200_layer_rows_f32(C.byref(dims), C.byref(lw), C.byref(lb), resid_hc.data_ptr(), pos.data_ptr(), T,
+                                      out_hc.data_ptr(), hook, None, None)
+        if rc:
+            raise RuntimeError(L.ds4b200_last_error().decode())
+
+    whole(); torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(5):
+        whole()
+    b.record(); torch.cuda.synchronize()
+    chain_us = round(a.elapsed_time(b) * 1e3 / 5, 1)
     return {"tokens": T, "us_per_stage": st, "us_per_layer": round(sum(st.values()), 1),
+            "us_per_layer_one_call": chain_us,
             "what": "batched row stages of one layer in forward_layer order; matvec / attention outputs are resident stand-ins"}
 
 
