@@ -115,6 +115,7 @@ SIGNATURES = {
     "ds4b200_layer_rows_f32": (_I, [C.POINTER(LayerDims), C.POINTER(LayerWeights), C.POINTER(LayerBuffers), _P, _P, _L, _P,
                                StageHook, _P, _P]),
     "ds4b200_swiglu_q8_K_rows_f32": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, C.c_float, _I, _P]),
+    "ds4b200_compressor_chunk_f32": (_I, [_I, _P, _P, _P, _P, _I, _I, _I, _L, _I, _P, _P, _P, _P]),
     "ds4b200_compressor_step_f32": (_I, [_I, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, C.POINTER(C.c_int), _P]),
     "ds4b200_div_selfcheck": (_I, [C.c_uint64, C.c_uint64, _P, _P]),
     # prefill path object (include/ds4b200_path.h)

@@ -382,6 +382,26 @@ int ds4b200_compressor_step_f32(int is_attn, const float *kv_cur, float *sc_cur,
     return launched("compressor_step");
 }
 
+int ds4b200_compressor_chunk_f32(int is_attn, const float *kv_cur, const float *sc_cur, const uint16_t *ape_f16,
+                                 const float *norm_w, int head_dim, int compress_ratio, int pos0,
+                                 int64_t n_tokens, int il, float *state_kv, float *state_score,
+                                 float *emit_out, void *stream) {
+    REQUIRE(kv_cur && sc_cur && ape_f16 && norm_w && state_kv && state_score && emit_out,
+            "compressor_chunk: null pointer");
+    REQUIRE(head_dim >= 128 && head_dim <= 1024 && head_dim % 64 == 0,
+            "compressor_chunk: head_dim must be a multiple of 64 in [128, 1024], got %d", head_dim);
+    REQUIRE(compress_ratio >= 1 && compress_ratio <= 4096, "compressor_chunk: compress_ratio out of range");
+    REQUIRE(pos0 >= 0 && n_tokens >= 0, "compressor_chunk: negative position or count");
+    REQUIRE(pos0 % compress_ratio == 0 && n_tokens % compress_ratio == 0,
+            "compressor_chunk: the chunk must start and end on window boundaries (use compressor_step for the rest)");
+    if (n_tokens == 0) return 0;
+    ds4b200_rope_params rope;
+    ds4b200_rope_params_for_layer(il, 64, &rope);
+    ds4b200::compressor_chunk(is_attn, kv_cur, sc_cur, ape_f16, norm_w, head_dim, compress_ratio, pos0, n_tokens, rope,
+                              64, 1.0e-6f, state_kv, state_score, emit_out, STREAM(stream));
+    return launched("compressor_chunk");
+}
+
 int ds4b200_div_selfcheck(uint64_t first, uint64_t count, unsigned long long *mismatches, void *stream) {
     REQUIRE(mismatches, "div_selfcheck: null pointer");
     ds4b200::div_selfcheck(first, count, mismatches, STREAM(stream));

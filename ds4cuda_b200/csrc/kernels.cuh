@@ -95,6 +95,11 @@ bool compressor_step(int is_attn, const float *kv_cur, float *sc_cur, const uint
                      const float *norm_w, int head_dim, int ratio, int pos, const ds4b200_rope_params &rope,
                      int n_rot, float eps, float *state_kv, float *state_score, float *emit_out,
                      cudaStream_t s);
+// the same for a chunk of tokens that starts and ends on window boundaries (emit_out [n_tokens/ratio][head_dim])
+void compressor_chunk(int is_attn, const float *kv_cur, const float *sc_cur, const uint16_t *ape_f16,
+                      const float *norm_w, int head_dim, int ratio, int pos0, int64_t n_tokens,
+                      const ds4b200_rope_params &rope, int n_rot, float eps, float *state_kv, float *state_score,
+                      float *emit_out, cudaStream_t s);
 void swiglu_q8_K_rows(const float *gate, const float *up, const float *weights, int8_t *xq, float *xscale,
                       int16_t *xbsums, float *mid_f32, int64_t n_rows, int n, int mode, float clamp,
                       int fast_exp, cudaStream_t s);

@@ -19,7 +19,7 @@ __all__ = [
     "TABLE_F16", "TABLE_Q8_0", "RopeParams", "rope_params_for_layer", "rope_params_explicit",
     "add", "rms_norm_rows", "rms_norm_q8_0_rows", "quantize_q8_0_rows", "quantize_q8_K_rows", "embed_gather_rows", "rope_rows", "fp8_kv_round_trip_rows",
     "rope_fp8_store_rows", "fp8_cache_load_rows", "kv_rows_to_raw", "swa_window_push_rows", "swiglu_rows", "hc_pre_rows", "output_hc_head_rows", "hc_post_rows", "hc_sinkhorn_rows", "hc_sinkhorn_mix_rows",
-    "e4m3_encode", "e4m3_decode", "e4m3_selfcheck", "div_selfcheck", "device_status", "compressor_step", "swiglu_q8_K_rows",
+    "e4m3_encode", "e4m3_decode", "e4m3_selfcheck", "div_selfcheck", "device_status", "compressor_step", "compressor_chunk", "swiglu_q8_K_rows",
 ]
 
 
@@ -168,6 +168,16 @@ def swa_window_push_rows(raw_kv, n_raw, new_rows):
     check(_lib.load().ds4b200_swa_window_push_rows_f32(_p(raw_kv), cap, n_raw, _p(new_rows), new_rows.shape[0], D,
                                                        C.byref(after), _s()))
     return after.value
+
+
+def compressor_chunk(is_attn, kv_cur, sc_cur, ape_f16, norm_w, head_dim, ratio, pos0, il, state_kv, state_score):
+    """A window-aligned chunk of compressor steps at once; returns emits [T / ratio, head_dim]."""
+    T = kv_cur.shape[0]
+    emits = torch.empty((T // ratio, head_dim), dtype=torch.float32, device=kv_cur.device)
+    check(_lib.load().ds4b200_compressor_chunk_f32(int(is_attn), _p(kv_cur), _p(sc_cur), _p(ape_f16), _p(norm_w),
+                                                   head_dim, ratio, pos0, T, il, _p(state_kv), _p(state_score),
+                                                   _p(emits), _s()))
+    return emits
 
 
 def swiglu_q8_K_rows(gate, up, weights=None, mode=GLU_PLAIN, clamp=0.0, fast_exp=False, want_f32=False):

@@ -249,6 +249,16 @@ int ds4b200_compressor_step_f32(int is_attn, const float *kv_cur, float *sc_cur,
                                 float *state_kv, float *state_score, float *emit_out,
                                 int *emitted_host, void *stream);
 
+/* The same for a chunk of n_tokens consecutive positions pos0 .. pos0 + n_tokens - 1 that starts
+ * and ends on window boundaries (pos0 % ratio == 0, n_tokens % ratio == 0): equivalent to
+ * n_tokens calls of ds4b200_compressor_step_f32 (bit for bit: state afterwards and the
+ * n_tokens / ratio emits), in two launches.  kv_cur, sc_cur [n_tokens][width]; sc_cur is not
+ * modified; emit_out [n_tokens / ratio][head_dim]. */
+int ds4b200_compressor_chunk_f32(int is_attn, const float *kv_cur, const float *sc_cur, const uint16_t *ape_f16,
+                                 const float *norm_w, int head_dim, int compress_ratio, int pos0,
+                                 int64_t n_tokens, int il, float *state_kv, float *state_score,
+                                 float *emit_out, void *stream);
+
 /* SwiGLU over gate/up[n_tokens][k][n].  weights[n_tokens][k] nullable.
  * combine != 0: out[n_tokens][n] = sum of the k slots in slot order; else
  * out[n_tokens][k][n].  fast_exp != 0 uses the hardware exp approximation the

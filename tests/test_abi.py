@@ -113,6 +113,10 @@ def test_checked_entry_points_reject_bad_arguments_without_a_gpu(lib):
     assert lib.ds4b200_compressor_step_f32(1, p, p, p, p, 512, 4, -1, 2, p, p, p, C.byref(emitted), None) == EINVAL
     assert lib.ds4b200_compressor_step_f32(1, p, None, p, p, 512, 4, 3, 2, p, p, p, C.byref(emitted), None) == EINVAL
     assert emitted.value == -1                                # untouched on a rejected call
+    assert lib.ds4b200_compressor_chunk_f32(1, p, p, p, p, 512, 4, 6, 64, 2, p, p, p, None) == EINVAL      # pos0 % 4
+    assert b"window boundaries" in lib.ds4b200_last_error()
+    assert lib.ds4b200_compressor_chunk_f32(1, p, p, p, p, 512, 4, 8, 62, 2, p, p, p, None) == EINVAL      # T % 4
+    assert lib.ds4b200_compressor_chunk_f32(1, p, p, p, p, 512, 4, 8, 0, 2, p, p, p, None) == 0            # empty chunk
     from ds4cuda_b200._lib import LayerBuffers, LayerDims, LayerWeights, StageHook
     hook = StageHook(lambda user, stage, n, stream: 0)
     dims = LayerDims(4096, 64, 512, 64, 1024, 2048, 6, 20, 2, 1, 1e-6, 10.0)

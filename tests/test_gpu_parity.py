@@ -832,3 +832,52 @@ def test_activation_quantisers_equal_the_reference_kernels(ops, ref):
     mq, ms = ops.quantize_q8_0_rows(dev(xa))
     assert_bits(host(mq).ravel(), host(sq), "Q8_0 values vs reference kernel")
     assert_bits(host(ms).ravel(), host(ss), "Q8_0 scales vs reference kernel")
+
+
+@pytest.mark.parametrize("head_dim,ratio,is_attn,il,n_windows", [(512, 4, 1, 2, 37), (128, 4, 0, 3, 5), (512, 128, 1, 3, 3),
+                                                                  (128, 16, 0, 5, 9)])
+def test_compressor_chunk_equals_the_steps_one_by_one(ops, oracle, head_dim, ratio, is_attn, il, n_windows):
+    """One call for a window-aligned chunk == the per-token step called T times, bit for bit (state and
+    emits), continuing from a state that already holds an earlier window; and close to the oracle."""
+    g = inputs.rng(960 + head_dim + ratio)
+    coff = 2 if ratio == 4 else 1
+    width, rows = coff * head_dim, (8 if ratio == 4 else ratio)
+    T, pos0 = n_windows * ratio, 3 * ratio
+    kv, sc = inputs.normal(g, (T, width)), inputs.normal(g, (T, width), 2.0)
+    ape = inputs.normal(g, (ratio, width), 0.5).astype(np.float16).view(np.uint16)
+    norm_w = inputs.uniform(g, (head_dim,), 0.5, 1.5)
+    kv0, sc0 = inputs.normal(g, (rows, width)), inputs.normal(g, (rows, width), 2.0)     # an earlier window's state
+    if ratio == 4:
+        kv0[4:], sc0[4:] = kv0[:4], sc0[:4]
+    d_ape, d_w = _i16(ape), dev(norm_w)
+    # steps one by one
+    s_kv, s_sc = dev(kv0), dev(sc0)
+    emit = torch.zeros(head_dim, device="cuda")
+    step_emits = []
+    for t in range(T):
+        if ops.compressor_step(is_attn, dev(kv[t]), dev(sc[t]), d_ape, d_w, head_dim, ratio, pos0 + t, il, s_kv, s_sc, emit):
+            step_emits.append(host(emit).copy())
+    # the chunk at once
+    c_kv, c_sc = dev(kv0), dev(sc0)
+    d_sc = dev(sc)
+    emits = ops.compressor_chunk(is_attn, dev(kv), d_sc, d_ape, d_w, head_dim, ratio, pos0, il, c_kv, c_sc)
+    assert_bits(host(d_sc), sc, "scores are left as they were")
+    assert_bits(host(emits), np.stack(step_emits), "emits: chunk vs steps")
+    assert_bits(host(c_kv), host(s_kv), "state_kv: chunk vs steps")
+    assert_bits(host(c_sc), host(s_sc), "state_score: chunk vs steps")
+    # the oracle's steps on the same inputs
+    p = oracle.rope_params_for_layer(il)
+    o_kv, o_sc = kv0.copy(), sc0.copy()
+    o_emits = [e for t in range(T)
+               if (e := oracle.compressor_step(is_attn, kv[t].copy(), sc[t].copy(), ape, norm_w, head_dim, ratio, pos0 + t, p,
+                                               o_kv, o_sc)) is not None]
+    assert_bits(host(c_kv), o_kv, "state_kv vs oracle")
+    assert_bits(host(c_sc), o_sc, "state_score vs oracle")
+    got, want = host(emits), np.stack(o_emits)
+    n_nope = head_dim - 64
+    if is_attn:
+        assert (got[:, :n_nope] != want[:, :n_nope]).mean() < 0.02
+        assert np.abs(got - want).max() <= 0.07 * np.abs(want).max()
+    else:
+        assert_close(got[:, :n_nope], want[:, :n_nope], rel=2e-5, what="emit prefix")
+    assert_close(got[:, n_nope:], want[:, n_nope:], rel=2e-5, what="emit tail")
