@@ -122,6 +122,7 @@ SIGNATURES = {
     "ds4b200_path_create": (_P, [_P]),
     "ds4b200_path_destroy": (None, [_P]),
     "ds4b200_path_upload_table": (_I, [_P, _P, C.c_size_t]),
+    "ds4b200_path_check_io": (_I, [_P, _P]),
     "ds4b200_path_upload": (_I, [_P, _P]),
     "ds4b200_path_buffer": (_P, [_P, C.c_char_p, C.POINTER(C.c_int64)]),
     "ds4b200_path_stream": (_P, [_P]),

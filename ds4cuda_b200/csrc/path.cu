@@ -174,6 +174,22 @@ std::vector<Copy> input_copies(ds4b200_path *p, const ds4b200_path_io *h) {
     };
 }
 
+// The token ids and positions of a host-side batch index device memory (table rows, cache
+// slots), so they are range-checked here, while they are still in host memory.
+int check_host_indices(const ds4b200_path_config &c, const ds4b200_path_io *h, const char *who) {
+    if (h->ids)
+        for (int64_t t = 0; t < c.n_tokens; ++t)
+            if (h->ids[t] < 0 || h->ids[t] >= c.vocab)
+                return set_error(-EINVAL, "%s: ids[%lld] = %d is outside [0, %d)", who, (long long)t, (int)h->ids[t],
+                                 (int)c.vocab);
+    if (h->pos)
+        for (int64_t t = 0; t < c.n_tokens; ++t)
+            if (h->pos[t] < 0 || h->pos[t] >= c.n_slots)
+                return set_error(-EINVAL, "%s: pos[%lld] = %d is outside [0, %d)", who, (long long)t, (int)h->pos[t],
+                                 (int)c.n_slots);
+    return 0;
+}
+
 }  // namespace
 
 extern "C" {
@@ -257,8 +273,14 @@ int ds4b200_path_upload_table(ds4b200_path *p, const void *host_table, size_t by
     return 0;
 }
 
+int ds4b200_path_check_io(const ds4b200_path_config *cfg, const ds4b200_path_io *host) {
+    if (!cfg || !host) return set_error(-EINVAL, "path_check_io: null argument");
+    return check_host_indices(*cfg, host, "path_check_io");
+}
+
 int ds4b200_path_upload(ds4b200_path *p, const ds4b200_path_io *host) {
     if (!p || !host) return set_error(-EINVAL, "path_upload: null argument");
+    if (int rc = check_host_indices(p->cfg, host, "path_upload")) return rc;
     for (const Copy &c : input_copies(p, host))
         if (c.host) CUDA_OK(cudaMemcpyAsync(c.dev, c.host, (size_t)c.bytes, cudaMemcpyHostToDevice, p->stream), "path_upload");
     CUDA_OK(cudaStreamSynchronize(p->stream), "path_upload: sync");
@@ -282,6 +304,7 @@ int ds4b200_path_run_device(ds4b200_path *p, int n_layers) {
 
 int ds4b200_path_run_host(ds4b200_path *p, const ds4b200_path_io *h, int n_layers, float *ms) {
     if (!p || !h || n_layers < 1) return set_error(-EINVAL, "path_run_host: bad argument");
+    if (int rc = check_host_indices(p->cfg, h, "path_run_host")) return rc;
     const ds4b200_path_config &c = p->cfg;
     const int64_t T = c.n_tokens;
     cudaStream_t s = p->stream;
@@ -326,6 +349,7 @@ int ds4b200_path_run_host(ds4b200_path *p, const ds4b200_path_io *h, int n_layer
 int ds4b200_path_run_host_chunked(ds4b200_path *p, const ds4b200_path_io *h, int n_layers, int n_chunks,
                                   float *ms) {
     if (!p || !h || n_layers < 1 || n_chunks < 1) return set_error(-EINVAL, "path_run_host_chunked: bad argument");
+    if (int rc = check_host_indices(p->cfg, h, "path_run_host_chunked")) return rc;
     const ds4b200_path_config &c = p->cfg;
     const int64_t T = c.n_tokens, E = c.n_embd;
     if (n_chunks > T) n_chunks = (int)T;

@@ -84,6 +84,12 @@ void ds4b200_path_destroy(ds4b200_path *p);
 
 /* The embedding table is a weight: uploaded once, not per call. */
 int ds4b200_path_upload_table(ds4b200_path *p, const void *host_table, size_t bytes);
+/* Range check of the index arrays of a host-side batch: every ids[t] in [0, vocab), every
+ * pos[t] in [0, n_slots).  0, or -EINVAL with the first offending index in
+ * ds4b200_last_error().  Needs no device.  ds4b200_path_upload, ds4b200_path_run_host and
+ * ds4b200_path_run_host_chunked run the same check before their first copy or launch (the
+ * kernels index the table and the cache with these values). */
+int ds4b200_path_check_io(const ds4b200_path_config *cfg, const ds4b200_path_io *host);
 /* Synchronous copy of every non-NULL input of `host` to the device. */
 int ds4b200_path_upload(ds4b200_path *p, const ds4b200_path_io *host);
 /* Device pointer and size of a named buffer ("table", "ids", "pos", "residual",

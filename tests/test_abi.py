@@ -72,6 +72,32 @@ def test_rope_routing_matches_oracle(lib, oracle):
     assert bytes(a) == bytes(oracle.rope_params_explicit(10000.0, 16.0, 4096))
 
 
+def test_path_rejects_out_of_range_ids_and_positions_on_the_host(lib):
+    """The prefill path indexes the embedding table with ids and the KV cache with pos; both are
+    range-checked while still in host memory, before any copy or launch."""
+    import numpy as np
+    from ds4cuda_b200._lib import PathConfig, PathIO
+    EINVAL = -22
+    cfg = PathConfig(n_tokens=8, vocab=100, n_slots=64)
+    ids = np.arange(8, dtype=np.int32)
+    pos = np.arange(8, dtype=np.int32)
+    io = PathIO(ids=ids.ctypes.data, pos=pos.ctypes.data)
+    assert lib.ds4b200_path_check_io(C.byref(cfg), C.byref(io)) == 0
+    ids[5] = 100
+    assert lib.ds4b200_path_check_io(C.byref(cfg), C.byref(io)) == EINVAL
+    assert b"ids[5] = 100" in lib.ds4b200_last_error()
+    ids[5] = -1
+    assert lib.ds4b200_path_check_io(C.byref(cfg), C.byref(io)) == EINVAL
+    ids[5] = 99
+    pos[7] = 64
+    assert lib.ds4b200_path_check_io(C.byref(cfg), C.byref(io)) == EINVAL
+    assert b"pos[7] = 64" in lib.ds4b200_last_error()
+    pos[7] = 63
+    assert lib.ds4b200_path_check_io(C.byref(cfg), C.byref(io)) == 0
+    assert lib.ds4b200_path_check_io(C.byref(cfg), C.byref(PathIO())) == 0      # absent arrays: nothing to check
+    assert lib.ds4b200_path_check_io(None, C.byref(io)) == EINVAL
+
+
 def test_checked_entry_points_reject_bad_arguments_without_a_gpu(lib):
     EINVAL = -22
     p = C.c_void_p(0x1000)       # never dereferenced: every call below fails validation first
