@@ -104,6 +104,7 @@ SIGNATURES = {
     "ds4b200_swa_window_push_rows_f32": (_I, [_P, _I, _I, _P, _I, _I, C.POINTER(C.c_int), _P]),
     "ds4b200_swiglu_rows_f32": (_I, [_P, _P, _P, _P, _L, _I, _I, _I, _F, _I, _I, _P]),
     "ds4b200_hc_pre_rows_f32": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _F, _P]),
+    "ds4b200_hc_pre_norm_rows_f32": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _F, _P]),
     "ds4b200_output_hc_head_rows_f32": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _I, _F, _P]),
     "ds4b200_hc_post_rows_f32": (_I, [_P, _P, _P, _P, _P, _P, _L, _I, _P]),
     "ds4b200_hc_sinkhorn_rows_f32": (_I, [_P, _P, _L, _I, _F, _P]),

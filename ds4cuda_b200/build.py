@@ -19,7 +19,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 INCLUDE = PKG.parent / "include"
 LIB = PKG / "libds4b200.so"
-SOURCES = ["norm.cu", "embedding.cu", "rope_fp8.cu", "glu.cu", "quant.cu", "hc.cu", "hc_pre_cluster.cu", "hc_pre_mma.cu", "compressor.cu", "layer.cu", "noalloc.cu", "path.cu",
+SOURCES = ["norm.cu", "embedding.cu", "rope_fp8.cu", "glu.cu", "quant.cu", "hc.cu", "hc_pre_cluster.cu", "hc_pre_mma.cu", "hc_pre_tc.cu", "compressor.cu", "layer.cu", "noalloc.cu", "path.cu",
            "launchers.cu", "capi.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 

@@ -269,6 +269,25 @@ int ds4b200_hc_pre_rows_f32(const float *residual_hc, const uint16_t *hc_fn,
     return launched("hc_pre_rows");
 }
 
+int ds4b200_hc_pre_norm_rows_f32(const float *residual_hc, const uint16_t *hc_fn, const float *hc_scale,
+                                 const float *hc_base, const float *norm_w, float *post, float *comb, float *out,
+                                 float *normed, int8_t *xq, float *xscale, int64_t n_tokens, int n_embd,
+                                 int sinkhorn_iters, float eps, void *stream) {
+    REQUIRE(n_tokens >= 0, "hc_pre_norm_rows: n_tokens < 0");
+    if (n_tokens == 0) return 0;
+    REQUIRE(n_tokens < ((int64_t)1 << 31), "hc_pre_norm_rows: n_tokens >= 2^31");
+    REQUIRE(residual_hc && hc_fn && hc_scale && hc_base && norm_w && post && comb && out,
+            "hc_pre_norm_rows: null pointer");
+    REQUIRE(normed || xq, "hc_pre_norm_rows: neither normed nor xq given");
+    REQUIRE(!xq == !xscale, "hc_pre_norm_rows: xq and xscale go together");
+    REQUIRE(n_embd > 0 && n_embd % 32 == 0 && n_embd <= 8192,
+            "hc_pre_norm_rows: n_embd must be a multiple of 32, at most 8192");
+    REQUIRE(sinkhorn_iters >= 1, "hc_pre_norm_rows: sinkhorn_iters < 1");
+    ds4b200::hc_pre_norm_rows(residual_hc, hc_fn, hc_scale, hc_base, norm_w, post, comb, out, normed, xq, xscale,
+                              n_tokens, n_embd, sinkhorn_iters, eps, STREAM(stream));
+    return launched("hc_pre_norm_rows");
+}
+
 int ds4b200_output_hc_head_rows_f32(const float *residual_hc, const uint16_t *output_hc_fn,
                                     const float *output_hc_scale, const float *output_hc_base,
                                     const float *norm_w, float *out, float *normed, int64_t n_tokens,

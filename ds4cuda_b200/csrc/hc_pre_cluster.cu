@@ -20,6 +20,8 @@
 // computes the gates redundantly and writes its own column slice of `out`.
 #include <cooperative_groups.h>
 
+#include <mutex>
+
 #include "device_utils.cuh"
 #include "kernels.cuh"
 
@@ -264,14 +266,23 @@ size_t smem_bytes() {
            sizeof(float) * (kWarps * S * M * kSlots + C * S * M * kSlots + S * M * kSlots + S * M * 4);
 }
 
+// Per device and kernel variant, looked up once: the shared-memory opt-in and how many clusters the
+// device holds at once (0: this variant cannot run here).
 template <int C, int VC, int M, int S>
-bool launch(const float *residual_hc, const uint16_t *hc_fn, const float *hc_scale, const float *hc_base,
-            float *post, float *comb, float *out, int64_t n_tokens, int n_embd, float eps, cudaStream_t s) {
+int max_clusters_on_this_device() {
+    constexpr int kMaxDevices = 64;
+    static int cached[kMaxDevices];          // 0 = not asked yet, -1 = cannot run, > 0 = clusters
+    static std::mutex mutex;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return -1; }
+    std::lock_guard<std::mutex> lock(mutex);
+    if (cached[dev] != 0) return cached[dev];
     auto kernel = hc_pre_cluster_kernel<C, VC, M, S>;
     const size_t smem = smem_bytes<C, VC, M, S>();
+    cached[dev] = -1;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
         cudaGetLastError();
-        return false;
+        return -1;
     }
     cudaLaunchConfig_t cfg{};
     cudaLaunchAttribute attr{};
@@ -280,21 +291,43 @@ bool launch(const float *residual_hc, const uint16_t *hc_fn, const float *hc_sca
     attr.val.clusterDim.y = 1;
     attr.val.clusterDim.z = 1;
     cfg.blockDim = dim3(kThreads);
+    cfg.gridDim = dim3(C);
     cfg.dynamicSmemBytes = smem;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n < 1) {
+        cudaGetLastError();
+        return -1;
+    }
+    return cached[dev] = n;
+}
+
+template <int C, int VC, int M, int S>
+bool launch(const float *residual_hc, const uint16_t *hc_fn, const float *hc_scale, const float *hc_base,
+            float *post, float *comb, float *out, int64_t n_tokens, int n_embd, float eps, cudaStream_t s) {
+    const int max_clusters = max_clusters_on_this_device<C, VC, M, S>();
+    if (max_clusters < 1) return false;
+    cudaLaunchConfig_t cfg{};
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = C;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_bytes<C, VC, M, S>();
     cfg.stream = s;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    cfg.gridDim = dim3(C);
-    int max_clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg) != cudaSuccess || max_clusters < 1) {
-        cudaGetLastError();
-        return false;
-    }
     const int64_t n_super = (n_tokens + S * M - 1) / (S * M);
     const int64_t clusters = n_super < max_clusters ? n_super : max_clusters;
     cfg.gridDim = dim3((unsigned)(clusters * C));
-    return cudaLaunchKernelEx(&cfg, kernel, residual_hc, hc_fn, hc_scale, hc_base, post, comb, out, n_tokens,
-                              n_embd, eps) == cudaSuccess;
+    if (cudaLaunchKernelEx(&cfg, hc_pre_cluster_kernel<C, VC, M, S>, residual_hc, hc_fn, hc_scale, hc_base, post, comb,
+                           out, n_tokens, n_embd, eps) != cudaSuccess) {
+        cudaGetLastError();        // the caller falls back to another kernel: do not leave the error behind
+        return false;
+    }
+    return true;
 }
 
 }  // namespace

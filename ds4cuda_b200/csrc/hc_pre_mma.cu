@@ -43,6 +43,8 @@
 #include <cooperative_groups.h>
 #include <cuda.h>
 
+#include <mutex>
+
 #include "device_utils.cuh"
 #include "kernels.cuh"
 
@@ -321,7 +323,7 @@ hc_pre_mma_kernel(const __grid_constant__ CUtensorMap x_map, const float *__rest
             const int m = tid >> 2, h = tid & 3;
             const float rms = rms_scale(total(m, kMixN), (float)hc_dim, eps);
             const float zp = (total(m, h) * rms) * hc_scale[0] + hc_base[h];
-            pre_cur[m * 4 + h] = __fdividef(1.0f, 1.0f + expf(-zp)) + eps;
+            pre_cur[m * 4 + h] = 1.0f / (1.0f + expf(-zp)) + eps;
         } else if (tid >= 128 && tid < 128 + 4 * kTokensPerRank) {
             const int m = rank * kTokensPerRank + ((tid - 128) >> 2), h = tid & 3;
             const int64_t t = step * kStepTokens + m;
@@ -364,16 +366,17 @@ bool encode_rows_map(CUtensorMap *map, const float *residual_hc, int64_t n_token
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
     static EncodeFn encode = nullptr;
-    if (!encode) {
+    static std::once_flag once;
+    std::call_once(once, [] {
         void *fn = nullptr;
         cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess || !fn) {
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            encode = reinterpret_cast<EncodeFn>(fn);
+        else
             cudaGetLastError();
-            return false;
-        }
-        encode = reinterpret_cast<EncodeFn>(fn);
-    }
+    });
+    if (!encode) return false;
     const cuuint64_t dims[4] = {16, (cuuint64_t)n_embd / 16, 4, (cuuint64_t)n_tokens};
     const cuuint64_t strides[3] = {64, (cuuint64_t)n_embd * 4, (cuuint64_t)n_embd * 16};
     const cuuint32_t box[4] = {16, kRowStride / 64, 1, kStepTokens};
@@ -383,43 +386,75 @@ bool encode_rows_map(CUtensorMap *map, const float *residual_hc, int64_t n_token
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Per device and cluster width, looked up once: the status word's address, the shared-memory opt-in
+// and how many clusters the device holds at once.  Only the tensor map is built per call.
+struct DeviceSetup { int *status = nullptr; int max_clusters = 0; bool done = false; };
+constexpr int kMaxDevices = 64;
+DeviceSetup g_setup[kMaxDevices][2];
+std::mutex g_setup_mutex;
+
 template <int C>
-bool launch(const float *residual_hc, const uint16_t *hc_fn, const float *hc_scale, const float *hc_base,
-            float *post, float *comb, float *out, int64_t n_tokens, float eps, cudaStream_t s) {
-    auto kernel = hc_pre_mma_kernel<C>;
-    const size_t smem = (size_t)kStages * kStageBytes + sizeof(uint32_t) * kWEntries +
-                        sizeof(float) * (8 * kStepTokens * kPartStride + C * kStepTokens * kVals +
-                                         2 * kStepTokens * 4);
-    int *status = device_status_word();
-    if (!status) return false;
-    CUtensorMap x_map;
-    if (!encode_rows_map(&x_map, residual_hc, n_tokens, C * kColsPerCta)) return false;
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-        cudaGetLastError();
-        return false;
-    }
-    cudaLaunchConfig_t cfg{};
-    cudaLaunchAttribute attr{};
+constexpr size_t smem_bytes() {
+    return (size_t)kStages * kStageBytes + sizeof(uint32_t) * kWEntries +
+           sizeof(float) * (8 * kStepTokens * kPartStride + C * kStepTokens * kVals + 2 * kStepTokens * 4);
+}
+
+template <int C>
+void cluster_config(cudaLaunchConfig_t &cfg, cudaLaunchAttribute &attr, unsigned grid, cudaStream_t s) {
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim.x = C;
     attr.val.clusterDim.y = 1;
     attr.val.clusterDim.z = 1;
     cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = smem;
+    cfg.gridDim = dim3(grid);
+    cfg.dynamicSmemBytes = smem_bytes<C>();
     cfg.stream = s;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    cfg.gridDim = dim3(C);
-    int max_clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg) != cudaSuccess || max_clusters < 1) {
+}
+
+template <int C>
+const DeviceSetup *device_setup() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return nullptr; }
+    DeviceSetup &d = g_setup[dev][C == 8 ? 0 : 1];
+    std::lock_guard<std::mutex> lock(g_setup_mutex);
+    if (d.done) return &d;
+    d.done = true;
+    d.status = device_status_word();
+    if (!d.status) return &d;
+    auto kernel = hc_pre_mma_kernel<C>;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<C>()) != cudaSuccess) {
         cudaGetLastError();
+        return &d;
+    }
+    cudaLaunchConfig_t cfg{};
+    cudaLaunchAttribute attr{};
+    cluster_config<C>(cfg, attr, C, nullptr);
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+    d.max_clusters = n;
+    return &d;
+}
+
+template <int C>
+bool launch(const float *residual_hc, const uint16_t *hc_fn, const float *hc_scale, const float *hc_base,
+            float *post, float *comb, float *out, int64_t n_tokens, float eps, cudaStream_t s) {
+    const DeviceSetup *d = device_setup<C>();
+    if (!d || !d->status || d->max_clusters < 1) return false;
+    CUtensorMap x_map;
+    if (!encode_rows_map(&x_map, residual_hc, n_tokens, C * kColsPerCta)) return false;
+    const int64_t n_steps = (n_tokens + kStepTokens - 1) / kStepTokens;
+    const int64_t clusters = n_steps < d->max_clusters ? n_steps : d->max_clusters;
+    cudaLaunchConfig_t cfg{};
+    cudaLaunchAttribute attr{};
+    cluster_config<C>(cfg, attr, (unsigned)(clusters * C), s);
+    if (cudaLaunchKernelEx(&cfg, hc_pre_mma_kernel<C>, x_map, residual_hc, hc_fn, hc_scale, hc_base, post, comb, out,
+                           n_tokens, eps, d->status) != cudaSuccess) {
+        cudaGetLastError();        // the caller falls back to another kernel: do not leave the error behind
         return false;
     }
-    const int64_t n_steps = (n_tokens + kStepTokens - 1) / kStepTokens;
-    const int64_t clusters = n_steps < max_clusters ? n_steps : max_clusters;
-    cfg.gridDim = dim3((unsigned)(clusters * C));
-    return cudaLaunchKernelEx(&cfg, kernel, x_map, residual_hc, hc_fn, hc_scale, hc_base, post, comb, out, n_tokens,
-                              eps, status) == cudaSuccess;
+    return true;
 }
 
 }  // namespace

@@ -18,7 +18,7 @@ __all__ = [
     "FP8_BLOCK64_POW2", "FP8_ROW_AMAX", "GLU_CLAMP_REF", "GLU_CLAMP_SYM", "GLU_PLAIN",
     "TABLE_F16", "TABLE_Q8_0", "RopeParams", "rope_params_for_layer", "rope_params_explicit",
     "add", "rms_norm_rows", "rms_norm_q8_0_rows", "quantize_q8_0_rows", "quantize_q8_K_rows", "embed_gather_rows", "rope_rows", "fp8_kv_round_trip_rows",
-    "rope_fp8_store_rows", "fp8_cache_load_rows", "kv_rows_to_raw", "swa_window_push_rows", "swiglu_rows", "hc_pre_rows", "output_hc_head_rows", "hc_post_rows", "hc_sinkhorn_rows", "hc_sinkhorn_mix_rows",
+    "rope_fp8_store_rows", "fp8_cache_load_rows", "kv_rows_to_raw", "swa_window_push_rows", "swiglu_rows", "hc_pre_rows", "hc_pre_norm_rows", "output_hc_head_rows", "hc_post_rows", "hc_sinkhorn_rows", "hc_sinkhorn_mix_rows",
     "e4m3_encode", "e4m3_decode", "e4m3_selfcheck", "div_selfcheck", "device_status", "compressor_step", "compressor_chunk", "swiglu_q8_K_rows",
 ]
 
@@ -223,6 +223,23 @@ def hc_pre_rows(resid, fn_f16, scale3, base24, iters=20, eps=1e-6):
     check(_lib.load().ds4b200_hc_pre_rows_f32(_p(resid), _p(fn_f16), _p(scale3), _p(base24), _p(post),
                                               _p(comb), _p(out), T, n, iters, eps, _s()))
     return post, comb, out
+
+
+def hc_pre_norm_rows(resid, fn_f16, scale3, base24, norm_w, iters=20, eps=1e-6, want_normed=True, want_q8=True):
+    """hc_pre_rows followed by RMSNorm(out) * norm_w and its Q8_0 blocks.
+    Returns (post, comb, out, normed or None, xq int8 [T, n] or None, xscale [T, n/32] or None)."""
+    T, _, n = resid.shape
+    dev = resid.device
+    post = torch.empty((T, 4), dtype=torch.float32, device=dev)
+    comb = torch.empty((T, 16), dtype=torch.float32, device=dev)
+    out = torch.empty((T, n), dtype=torch.float32, device=dev)
+    normed = torch.empty((T, n), dtype=torch.float32, device=dev) if want_normed else None
+    xq = torch.empty((T, n), dtype=torch.int8, device=dev) if want_q8 else None
+    xscale = torch.empty((T, n // 32), dtype=torch.float32, device=dev) if want_q8 else None
+    check(_lib.load().ds4b200_hc_pre_norm_rows_f32(_p(resid), _p(fn_f16), _p(scale3), _p(base24), _p(norm_w), _p(post),
+                                                   _p(comb), _p(out), _p(normed), _p(xq), _p(xscale), T, n, iters,
+                                                   eps, _s()))
+    return post, comb, out, normed, xq, xscale
 
 
 def output_hc_head_rows(resid, fn_f16, scale1, base4, norm_w=None, eps=1e-6, want_out=True):

@@ -275,6 +275,18 @@ int ds4b200_hc_pre_rows_f32(const float *residual_hc, const uint16_t *hc_fn,
                             float *comb, float *out, int64_t n_tokens, int n_embd,
                             int sinkhorn_iters, float eps, void *stream);
 
+/* The pre step and what the reference runs right behind it (cuda/forward_layer.cu:808->822 for the
+ * attention half, :1235->1249 for the FFN half): normed = RMSNorm(out) * norm_w (cuda/norm.cu:52-113)
+ * and its Q8_0 activation blocks (cuda/dense_q8.cu:122-152): xq int8 [t][n_embd], xscale
+ * [t][n_embd/32].  normed and the xq / xscale pair are each optional (at least one is required); out,
+ * post and comb are written as by ds4b200_hc_pre_rows_f32.  One call, the kernels of the two stages
+ * back to back on `stream`.  The results of this call and of ds4b200_hc_pre_rows_f32 are invalid if
+ * ds4b200_device_status() reports the time-out bit afterwards. */
+int ds4b200_hc_pre_norm_rows_f32(const float *residual_hc, const uint16_t *hc_fn, const float *hc_scale,
+                                 const float *hc_base, const float *norm_w, float *post, float *comb,
+                                 float *out, float *normed, int8_t *xq, float *xscale, int64_t n_tokens,
+                                 int n_embd, int sinkhorn_iters, float eps, void *stream);
+
 /* Hyper-connection post step (cuda/hc_sinkhorn.cu:619-672) for n_tokens tokens.
  * block_out nullable (term dropped); block_out2 nullable (when given the block
  * term is block_out+block_out2, the add of cuda/forward_layer.cu:1447 fused). */

@@ -457,6 +457,55 @@ def test_hc_pre_rows(ops, oracle, n_embd, T):
     assert_close(host(out), wout, what="hc_pre out")
 
 
+@pytest.mark.parametrize("T", [65, 449, 1000, 1344])
+def test_hc_pre_rows_token_batches_on_the_tensor_cores(ops, oracle, T):
+    """More than 64 tokens of width 4096 take the tcgen05 kernel: a step is 64 tokens per cluster, so these
+    sizes cover one to three steps per cluster, a ragged last step, and the double-buffered accumulators
+    and exchange buffers coming round again.  Two runs must agree bit for bit (fixed summation orders)."""
+    g = inputs.rng(7100 + T)
+    resid = inputs.normal(g, (T, 4, 4096))
+    wts = inputs.hc_pre_weights(6, 4096)
+    d = [dev(resid), dev(wts["fn"]), dev(wts["scale"]), dev(wts["base"])]
+    post, comb, out = ops.hc_pre_rows(*d)
+    assert ops.device_status() == 0
+    wpost, wcomb, wout, _ = oracle.hc_pre_rows(resid, wts["fn"], wts["scale"], wts["base"])
+    assert_close(host(post), wpost, what="hc_pre post")
+    assert_close(host(comb), wcomb, what="hc_pre comb")
+    assert_close(host(out), wout, what="hc_pre out")
+    for _ in range(3):
+        post2, comb2, out2 = ops.hc_pre_rows(*d)
+        assert torch.equal(post2, post) and torch.equal(comb2, comb) and torch.equal(out2, out)
+
+
+@pytest.mark.parametrize("n_embd,T", [(4096, 200), (4096, 7), (1024, 5)])
+def test_hc_pre_norm_rows(ops, oracle, n_embd, T):
+    """HC pre -> RMSNorm -> Q8_0 as one call: the f32 rows against the oracle, the Q8_0 blocks exact on the
+    GPU's own normalised row."""
+    g = inputs.rng(7200 + n_embd + T)
+    resid = inputs.normal(g, (T, 4, n_embd))
+    wts = inputs.hc_pre_weights(6, n_embd)
+    w = inputs.uniform(g, (n_embd,), 0.5, 1.5)
+    post, comb, out, normed, xq, xs = ops.hc_pre_norm_rows(dev(resid), dev(wts["fn"]), dev(wts["scale"]),
+                                                           dev(wts["base"]), dev(w))
+    assert ops.device_status() == 0
+    wpost, wcomb, wout, _ = oracle.hc_pre_rows(resid, wts["fn"], wts["scale"], wts["base"])
+    assert_close(host(post), wpost, what="post")
+    assert_close(host(comb), wcomb, what="comb")
+    assert_close(host(out), wout, what="out")
+    wnorm, _, _ = oracle.rms_norm_rows(wout, w)
+    assert_close(host(normed), wnorm, what="normed")
+    wq, ws = oracle.quantize_q8_0_rows(host(normed))
+    assert_bits(host(xq).ravel(), wq, "fused Q8_0 values")
+    assert_bits(host(xs).ravel(), ws, "fused Q8_0 scales")
+    # the same outputs one at a time
+    _, _, _, n2, q2, s2 = ops.hc_pre_norm_rows(dev(resid), dev(wts["fn"]), dev(wts["scale"]), dev(wts["base"]), dev(w),
+                                               want_normed=False)
+    assert n2 is None and torch.equal(q2, xq) and torch.equal(s2, xs)
+    _, _, o3, n3, q3, _ = ops.hc_pre_norm_rows(dev(resid), dev(wts["fn"]), dev(wts["scale"]), dev(wts["base"]), dev(w),
+                                               want_q8=False)
+    assert q3 is None and torch.equal(n3, normed) and torch.equal(o3, out)
+
+
 def test_hc_pre_drop_in_launchers_and_reference_kernels(ops, oracle, ref):
     from ds4cuda_b200 import _lib
     L = _lib.load()
