@@ -34,12 +34,20 @@ OP_NAMES = ("gather", "kvstore", "swiglu", "hcmix", "sinkhorn")
 METRIC, UNIT = "fused_path_tokens_per_s", "tokens/s"
 FALLBACK_HBM_GBS = 6650.0      # earlier measurement on this pool, used only without MEASURED_PEAKS.json
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel
-# at the benchmark shape, from the ncu capture summarised under profiles/.
-# Captured at 2048 tokens (profiles/ncu_full_set_small_case_2048tok.md) and scaled x2 to the
-# 4096-token launch; reads scale exactly, writes are undercounted by what the L2 still holds.
-NCU_TRAFFIC_BYTES = {"hcmix": 2 * (134360320 + 79656192), "swiglu": 2 * (201404160 + 10429952),
-                     "gather": 2 * (42454528 + 3300864), "kvstore": 2 * 4270848, "sinkhorn": 2 * 140032}
+TRAFFIC_FILE = ROOT / "profiles" / "dram_traffic_prefill_path.txt"
+
+
+def ncu_traffic_bytes(kernel, tokens):
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch of `kernel`, from the committed ncu figures
+    (captured at a smaller token count), scaled in proportion to `tokens`; None when there is no figure."""
+    try:
+        for line in TRAFFIC_FILE.read_text().splitlines():
+            f = line.split()
+            if len(f) == 4 and f[0] == kernel:
+                return int((int(f[2]) + int(f[3])) * tokens / int(f[1]))
+    except (OSError, ValueError):
+        pass
+    return None
 
 
 def parse_args():
@@ -56,6 +64,10 @@ def parse_args():
     ap.add_argument("--e2e-chunks", type=int, default=8, help="row slices pipelined over H2D / compute / D2H")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU work budget of the baseline sample")
+    ap.add_argument("--only", default=None, help="run ONE batched op in a loop (for a one-kernel ncu capture) "
+                                                 "and print its median time; see ONLY_OPS")
+    ap.add_argument("--only-tokens", type=int, default=2048)
+    ap.add_argument("--only-reps", type=int, default=6)
     return ap.parse_args()
 
 
@@ -248,56 +260,233 @@ def reference_kernels_leg(tokens, n_layers):
     return out
 
 
-def standalone_ops_leg(tokens, peak):
-    """The batched forms the layer chain does not contain, one launch each between L2 flushes.
+# ----------------------------------------------------------------------------- parity of the timed run
 
-    Full HC pre (24 x 16384 f16 matvec + gates + weighted stream sum), HC post with the block
-    term, and the FP8 cache store at a row count that fills the GPU.  CUDA events on torch's
-    current stream, which is the stream these wrappers launch on; median of 15.
-    """
+def parity_leg(x, table, out, n_layers, rows=64):
+    """Per-op error figures of THIS run: the outputs the end-to-end call just copied back, first `rows`
+    token rows, against the CPU oracle on the same inputs.  Runs after the timed regions."""
+    import numpy as np
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import oracle_lib as oracle
+    r = min(rows, len(x["ids"]))
+    sl = {k: (v if k == "norm_w" else v[:r]) for k, v in x.items()}
+    rope = oracle.rope_params_explicit(10000.0, 16.0, 4096)
+    res = {"rows": r}
+    want_rows, want_norm, want_bf16 = oracle.embed_gather_rows(table, oracle.TABLE_Q8_0, sl["ids"], N_EMBD, residual=sl["residual"],
+                                                               norm_w=sl["norm_w"], want_bf16=True)
+    got = np.asarray(out["residual_out"])[:r]
+    res["gather_residual_mismatching_values"] = int((got.view(np.uint32) != want_rows[:, 0, :].view(np.uint32)).sum())
+    got_b = np.asarray(out["normed_bf16"])[:r].view(np.uint16)
+    res["gather_normed_bf16_mismatching_values"] = int((got_b != np.asarray(want_bf16).view(np.uint16).reshape(got_b.shape)).sum())
+    codes, scales, _, _ = oracle.rope_fp8_store_rows(sl["kv"], sl["pos"], rope, N_ROT, oracle.FP8_ROW_AMAX)
+    res["kvstore_mismatching_code_bytes"] = int((np.asarray(out["kv_codes"])[:r] != codes).sum())
+    res["kvstore_code_bytes"] = int(codes.size)
+    res["kvstore_mismatching_scales"] = int((np.asarray(out["kv_scales"])[:r].view(np.uint32) != scales.view(np.uint32)).sum())
+    want_ffn = oracle.swiglu_rows(sl["gate"], sl["up"], sl["router_w"], oracle.GLU_CLAMP_REF, 10.0, True)
+    err = np.abs(np.asarray(out["ffn_out"])[:r].astype(np.float64) - want_ffn).max()
+    res["swiglu_max_abs_err_over_max"] = float(err / np.abs(want_ffn).max())
+    hc = sl["hc_resid"]
+    for _ in range(n_layers):
+        hc, _ = oracle.hc_sinkhorn_mix_rows(sl["hc_logits"], hc)
+    err = np.abs(np.asarray(out["hc_out"])[:r].astype(np.float64) - hc).max()
+    res["hcmix_max_abs_err_over_max_after_all_layers"] = float(err / np.abs(hc).max())
+    res["bar"] = "gather residual bit-exact; bf16 and FP8 codes differ only at rounding boundaries; f32 ops <= 1e-5 x max per op"
+    return res
+
+
+# ----------------------------------------------------------------------------- strong split and copy floor
+
+def strong_split_leg(args, rank, world, table, weak_value):
+    """The same `--tokens` batch split T/N rows per rank (no collective): ms per step, whole-job tokens/s."""
+    import torch
+    from ds4cuda_b200 import shard
+    from ds4cuda_b200.path import PrefillPath
+    a, b = shard.token_range(rank, world, args.tokens)
+    n = b - a
+    path = PrefillPath(n_tokens=max(n, 1), max_layers=args.layers, use_graph=args.graph, glu_fast_exp=1)
+    path.upload_table(table)
+    x = make_inputs(max(n, 1), seed=500 + rank)
+    path.upload({k: torch.from_numpy(v).pin_memory() for k, v in x.items()})
+    for _ in range(args.warmup):
+        path.run_device(args.layers)
+    torch.cuda.synchronize()
+    shard.barrier()
+    ms = path.time_device(args.layers, 0, args.steps)
+    torch.cuda.synchronize()
+    shard.barrier()
+    ms_step = shard.max_over_ranks(ms) / args.steps
+    path.close()
+    value = args.tokens / (ms_step * 1e-3)
+    return {"tokens_per_rank": n, "ms_per_step": ms_step, "value": value, "unit": UNIT,
+            "what": f"one {args.tokens}-token batch split into contiguous row ranges, one per rank",
+            "bound": "at 512 rows per GPU the three dependent kernels of a layer move 22 us of traffic "
+                     "but each launch has a latency floor of a few us: the step is launch/latency bound"
+                     if n <= 1024 else "HBM"}
+
+
+def copy_floor_leg(h2d_tensors, d2h_tensors, reps=3):
+    """The end-to-end step's copies alone: the same pinned host buffers in and out with plain
+    cudaMemcpyAsync on two streams and no kernel, every rank at once.  ms per step, max over ranks."""
+    import torch
+    from ds4cuda_b200 import shard
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    dev_in = [torch.empty(t.shape, dtype=t.dtype, device="cuda") for t in h2d_tensors]
+    dev_out = [torch.empty(t.shape, dtype=t.dtype, device="cuda") for t in d2h_tensors]
+    torch.cuda.synchronize()
+    shard.barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        with torch.cuda.stream(s_in):
+            for d, h in zip(dev_in, h2d_tensors):
+                d.copy_(h, non_blocking=True)
+        with torch.cuda.stream(s_out):
+            for h, d in zip(d2h_tensors, dev_out):
+                h.copy_(d, non_blocking=True)
+    torch.cuda.current_stream().wait_stream(s_in)
+    torch.cuda.current_stream().wait_stream(s_out)
+    b.record()
+    torch.cuda.synchronize()
+    shard.barrier()
+    return shard.max_over_ranks(a.elapsed_time(b) / reps)
+
+
+# ----------------------------------------------------------------------------- one op in a loop
+
+def only_ops(tokens):
+    """name -> (callable, algorithmic bytes, description) for `--only`: every batched op outside the
+    five-kernel chain, at `tokens` token rows, on resident synthetic inputs."""
     import torch
     from ds4cuda_b200 import ops
-    dev = "cuda"
-    g = torch.Generator(device=dev).manual_seed(7)
-    flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    dev, T, n = "cuda", tokens, N_EMBD
+    g = torch.Generator(device=dev).manual_seed(13)
+    rnd = lambda *shape, s=1.0: torch.randn(*shape, device=dev, generator=g) * s
+    reg = {}
 
-    def timed(fn):
+    def add(name, make):
+        reg[name] = make
+
+    def hc_pre():
+        resid, fn = rnd(T, 4, n), (rnd(24, 4 * n) / 128).half()
+        sc, base = torch.ones(3, device=dev), torch.zeros(24, device=dev)
+        return (lambda: ops.hc_pre_rows(resid, fn, sc, base)), T * (4 * n * 4 + n * 4 + 80) + fn.numel() * 2, \
+            "full HC pre: 24 dots per token on the tensor cores + gates + stream sum + Sinkhorn rows"
+
+    def hc_post_block():
+        resid, block = rnd(T, 4, n), rnd(T, n)
+        post, comb = torch.rand(T, 4, device=dev, generator=g), torch.rand(T, 16, device=dev, generator=g)
+        return (lambda: ops.hc_post_rows(block, resid, post, comb)), T * (2 * 4 * n * 4 + n * 4 + 80), "HC post with the block term"
+
+    def hc_head():
+        resid, fn = rnd(T, 4, n), (rnd(4, 4 * n) / 128).half()
+        sc, base, w = torch.ones(1, device=dev), torch.zeros(4, device=dev), torch.rand(n, device=dev, generator=g) + 0.5
+        return (lambda: ops.output_hc_head_rows(resid, fn, sc, base, norm_w=w)), T * (4 * n * 4 + 2 * n * 4), "output HC head + output norm"
+
+    def rms_norm_cta():
+        x, w = rnd(T, n), torch.rand(n, device=dev, generator=g) + 0.5
+        return (lambda: ops.rms_norm_rows(x, w)), T * n * 8, "RMSNorm, 4096-wide rows (one CTA per row)"
+
+    def rms_norm_q8_0():
+        x, w = rnd(T, n), torch.rand(n, device=dev, generator=g) + 0.5
+        return (lambda: ops.rms_norm_q8_0_rows(x, w, want_f32=False)), T * (n * 4 + n + n // 8), "RMSNorm with the Q8_0 blocks as only output"
+
+    def rms_norm_warp():
+        x = rnd(T * 64, 512)
+        return (lambda: ops.rms_norm_rows(x, None)), T * 64 * 512 * 8, "unit-gain RMSNorm, 512-wide head rows (one warp per row)"
+
+    def rope_rows():
+        q, pos = rnd(T, 64, KV_DIM), torch.arange(T, device=dev, dtype=torch.int32)
+        rp = ops.rope_params_for_layer(2)
+        return (lambda: ops.rope_rows(q, pos, rp, unit_rms=True, out=q)), T * 64 * KV_DIM * 8, "q_norm + tail RoPE over 64 heads per token"
+
+    def rope_inverse():
+        q, pos = rnd(T, 64, KV_DIM), torch.arange(T, device=dev, dtype=torch.int32)
+        rp = ops.rope_params_for_layer(2)
+        return (lambda: ops.rope_rows(q, pos, rp, inverse=True, out=q)), T * 64 * KV_DIM * 8, "inverse tail RoPE over 64 heads per token"
+
+    def fp8_round_trip():
+        rows = T * 16
+        kv = rnd(rows, KV_DIM, s=1.5)
+        return (lambda: ops.fp8_kv_round_trip_rows(kv)), rows * KV_DIM * 8, "FP8 E4M3 round trip (reference scale mode), 16 rows per token"
+
+    def rope_fp8_store():
+        rows = T * 16
+        kv = rnd(rows, KV_DIM, s=1.5)
+        pos = (torch.arange(rows, device=dev, dtype=torch.int32) % 4096).contiguous()
+        slots = torch.arange(rows, device=dev, dtype=torch.int32)
+        codes, scales = torch.zeros(rows, KV_DIM, dtype=torch.uint8, device=dev), torch.zeros(rows, 1, device=dev)
+        rp = ops.rope_params_explicit(10000.0, 16.0, 4096, N_ROT)
+        return (lambda: ops.rope_fp8_store_rows(kv, pos, rp, N_ROT, ops.FP8_ROW_AMAX, codes, scales, slots=slots)), \
+            rows * (KV_DIM * 4 + KV_DIM + 8), "RoPE + E4M3 cache store, 16 rows per token"
+
+    def swiglu_q8k():
+        gate, up = rnd(T, TOP_K, FF_DIM, s=2.0), rnd(T, TOP_K, FF_DIM, s=2.0)
+        w = torch.softmax(rnd(T, TOP_K), -1)
+        return (lambda: ops.swiglu_q8_K_rows(gate, up, w, ops.GLU_CLAMP_REF, 10.0, fast_exp=True)), \
+            T * TOP_K * (FF_DIM * 8 + FF_DIM + FF_DIM // 256 * 36), "expert epilogue leaving as Q8_K blocks"
+
+    def quantize_q8_K():
+        x = rnd(T * TOP_K, FF_DIM)
+        return (lambda: ops.quantize_q8_K_rows(x)), T * TOP_K * (FF_DIM * 4 + FF_DIM + FF_DIM // 256 * 36), "Q8_K activation quantiser"
+
+    for f in (hc_pre, hc_post_block, hc_head, rms_norm_cta, rms_norm_q8_0, rms_norm_warp, rope_rows, rope_inverse,
+              fp8_round_trip, rope_fp8_store, swiglu_q8k, quantize_q8_K):
+        add(f.__name__, f)
+    return reg
+
+
+def run_only(args):
+    """`--only OP`: a few launches of one op between L2 flushes; one JSON line with its median time."""
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product path has no CPU fallback")
+    reg = only_ops(args.only_tokens)
+    if args.only not in reg:
+        raise SystemExit(f"--only: unknown op {args.only!r}; one of {sorted(reg)}")
+    fn, nbytes, what = reg[args.only]()
+    flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    ts = []
+    for i in range(args.only_reps):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); fn(); b.record(); torch.cuda.synchronize()
+        if i >= 2:
+            ts.append(a.elapsed_time(b) * 1e3)
+    us = sorted(ts)[len(ts) // 2]
+    peak = measured_peak()[0]
+    print(json.dumps({"only": args.only, "tokens": args.only_tokens, "us_per_launch": round(us, 1),
+                      "algorithmic_bytes": int(nbytes), "gbs": round(nbytes / us / 1e3, 1),
+                      "frac_of_peak": round(nbytes / us / 1e3 / peak, 4), "what": what}), flush=True)
+
+
+def measured_peak():
+    peaks_file = ROOT / "MEASURED_PEAKS.json"
+    if peaks_file.exists():
+        return float(json.loads(peaks_file.read_text())["hbm_gbs"]), "measured"
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+def standalone_ops_leg(tokens, peak):
+    """The batched forms the layer chain does not contain, one launch each between L2 flushes: CUDA events
+    on torch's current stream, which is the stream these wrappers launch on; median of 9."""
+    import torch
+    flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    out = {}
+    for name, make in only_ops(tokens).items():
+        fn, nbytes, what = make()
         ts = []
-        for i in range(18):
+        for i in range(12):
             flush.zero_()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(); fn(); b.record(); torch.cuda.synchronize()
             if i >= 3:
                 ts.append(a.elapsed_time(b) * 1e3)
-        return sorted(ts)[len(ts) // 2]
-
-    def entry(us, nbytes, what):
+        us = sorted(ts)[len(ts) // 2]
         gbs = nbytes / us / 1e3
-        return {"us_per_launch": round(us, 1), "algorithmic_bytes": int(nbytes), "gbs": round(gbs, 1),
-                "frac_of_peak": round(gbs / peak, 4), "what": what}
-
-    out = {}
-    resid = torch.randn(tokens, 4, N_EMBD, device=dev, generator=g)
-    fn = (torch.randn(24, 4 * N_EMBD, device=dev, generator=g) / 128).half()
-    scale, base = torch.ones(3, device=dev), torch.zeros(24, device=dev)
-    us = timed(lambda: ops.hc_pre_rows(resid, fn, scale, base))
-    out["hc_pre_rows"] = entry(us, tokens * (4 * N_EMBD * 4 + N_EMBD * 4 + 80) + fn.numel() * 2,
-                               "24 dots per token on the tensor cores + gates + stream sum + Sinkhorn rows")
-    block = torch.randn(tokens, N_EMBD, device=dev, generator=g)
-    post = torch.rand(tokens, 4, device=dev, generator=g)
-    comb = torch.rand(tokens, 16, device=dev, generator=g)
-    us = timed(lambda: ops.hc_post_rows(block, resid, post, comb))
-    out["hc_post_rows_with_block"] = entry(us, tokens * (2 * 4 * N_EMBD * 4 + N_EMBD * 4 + 80), "config 5 with the block term")
-    del resid, block
-    rows = 65536
-    kv = torch.randn(rows, KV_DIM, device=dev, generator=g) * 1.5
-    pos = (torch.arange(rows, device=dev, dtype=torch.int32) % 4096).contiguous()
-    slots = torch.arange(rows, device=dev, dtype=torch.int32)
-    codes = torch.zeros(rows, KV_DIM, dtype=torch.uint8, device=dev)
-    scales = torch.zeros(rows, 1, device=dev)
-    rp = ops.rope_params_explicit(10000.0, 16.0, 4096, N_ROT)
-    us = timed(lambda: ops.rope_fp8_store_rows(kv, pos, rp, N_ROT, ops.FP8_ROW_AMAX, codes, scales, slots=slots))
-    out["rope_fp8_store_65536_rows"] = entry(us, rows * (KV_DIM * 4 + KV_DIM + 4 + 4), "config 3 kernel at a row count that fills the GPU")
+        out[name] = {"us_per_launch": round(us, 1), "algorithmic_bytes": int(nbytes), "gbs": round(gbs, 1),
+                     "frac_of_peak": round(gbs / peak, 4), "what": what}
+        del fn
+        torch.cuda.empty_cache()
     return out
 
 
@@ -419,8 +608,14 @@ def run_reference_arm(args):
         "config": workload_config(args, args.tokens),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "extrapolated": True,
+        "measured_sample": {"tokens": tokens, "layers": layers, "seconds_per_step": dt,
+                            "tokens_x_layers_per_s": tokens * layers / dt},
+        "what_this_is": "own CPU oracle (scalar C restatement of the reference kernels' arithmetic) on all host "
+                        "threads; NOT the upstream GPU code.  The reference's own kernels rebuilt for sm_100a are "
+                        "timed in the main arm's reference_kernels_sm100a leg (vs_reference_kernels_sm100a)",
         "note": "the reference ships no CPU implementation of this path (its CPU model, antirez/ds4, is not "
-                "in its tree); this is the scalar C restatement of its kernels' arithmetic",
+                "in its tree); the value scales the measured sample linearly in rows and layers",
     }
     print(json.dumps(line), flush=True)
 
@@ -476,11 +671,7 @@ def run_ours(args):
     # one launch of each kernel on its own (events around a single launch; includes the launch gap)
     single_ms = path.profile_ops(1)
     ops_table = {}
-    peaks_file = ROOT / "MEASURED_PEAKS.json"
-    if peaks_file.exists():
-        peak, peak_src = float(json.loads(peaks_file.read_text())["hbm_gbs"]), "measured"
-    else:
-        peak, peak_src = FALLBACK_HBM_GBS, "fallback"
+    peak, peak_src = measured_peak()
     for i, name in enumerate(OP_NAMES):
         us = per_op_ms[name] * 1e3
         gbs = path.op_bytes(i) / (us * 1e-6) / 1e9
@@ -491,7 +682,7 @@ def run_ours(args):
     dominant = max(OP_NAMES, key=lambda n: ops_table[n]["us_per_launch"])
     roofline = {"bound": "hbm", "kernel": dominant, "achieved": ops_table[dominant]["gbs"], "peak": peak,
                 "peak_source": peak_src, "unit": "GB/s", "frac": ops_table[dominant]["frac_of_peak"],
-                "traffic": NCU_TRAFFIC_BYTES[dominant]}
+                "traffic": ncu_traffic_bytes(dominant, tokens)}
     step_bytes = sum(path.op_bytes(i) for i in range(len(OP_NAMES))) * args.layers
     hbm_gbs_step = step_bytes / (ms_step * 1e-3) / 1e9
 
@@ -515,18 +706,31 @@ def run_ours(args):
     shard.barrier()
     e2e_ms_step = shard.max_over_ranks(e2e_ms) / max(1, args.e2e_steps)
     e2e_value = job_tokens / (e2e_ms_step * 1e-3)
+    # the same bytes with no kernels: what the host's memory / PCIe complex allows when every rank copies at once
+    copy_floor_ms = copy_floor_leg(list(pinned_in.values()), list(pinned_out.values()))
 
     sampler.stop_flag = True
     sampler.join(timeout=2)
     clocks = sampler.summary()
 
-    cpu, ref_kernels = None, None
+    cpu, ref_kernels, parity = None, None, None
+    if rank == 0:
+        try:      # error figures of the outputs this run produced (checker only, after the timed regions)
+            parity = parity_leg(x, table, {k: v.numpy() for k, v in pinned_out.items()}, args.layers)
+        except Exception as e:                      # noqa: BLE001
+            parity = {"error": f"{type(e).__name__}: {e}"}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline_leg(x, table, args.cpu_seconds, args.layers)
         ref_kernels = reference_kernels_leg(tokens, args.layers)
 
     launches = path.launches_per_run(args.layers) * args.steps
     path.close()
+    strong = None
+    if world > 1 and args.scaling == "weak":
+        try:
+            strong = strong_split_leg(args, rank, world, table, value)
+        except Exception as e:                      # noqa: BLE001
+            strong = {"error": f"{type(e).__name__}: {e}"}
     # extra single-GPU legs; a failure there must not cost the main line
     standalone = layer_stages = None
     if rank == 0 and world == 1:
@@ -553,7 +757,12 @@ def run_ours(args):
         "reference_kernels_sm100a": ref_kernels, "standalone_ops": standalone, "layer_row_stages": layer_stages,
         "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms_step,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "pipeline": f"{args.e2e_chunks} row slices over copy-in / compute / copy-out streams"},
+                "copy_floor_ms": copy_floor_ms, "ms_per_step_over_copy_floor": round(e2e_ms_step / copy_floor_ms, 3),
+                "pipeline": f"{args.e2e_chunks} row slices over copy-in / compute / copy-out streams; copy_floor_ms "
+                            "is the same host buffers copied in and out with no kernel, all ranks at once"},
+        "parity": parity, "strong_split": strong,
+        "vs_reference_kernels_sm100a": (round(value / ref_kernels["tokens_per_s"], 1)
+                                        if ref_kernels and ref_kernels.get("tokens_per_s") else None),
         "gpu_launches": launches, "cuda_graph": bool(args.graph), "clocks": clocks,
     }
     print(json.dumps(line), flush=True)
@@ -568,7 +777,9 @@ def main():
                "--master-addr", "127.0.0.1", "--master-port", str(29400 + os.getpid() % 500),
                str(Path(__file__).resolve())] + sys.argv[1:]
         raise SystemExit(subprocess.call(cmd))
-    if args.impl == "reference":
+    if args.only:
+        run_only(args)
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_ours(args)

@@ -14,6 +14,15 @@ LIB_PATH = Path(__file__).resolve().parent / "_ref" / "libds4ref.so"
 _lib = None
 
 
+def reference_tree() -> Path | None:
+    """Where the reference's sources are, if they are reachable from here: $DS4_REFERENCE, else a
+    directory named `reference` beside this repository.  None on a box that only has the built library."""
+    import os
+    cand = os.environ.get("DS4_REFERENCE")
+    path = Path(cand) if cand else Path(__file__).resolve().parent.parent.parent / "reference"
+    return path if (path / "cuda" / "norm.cu").exists() else None
+
+
 def available() -> bool:
     return LIB_PATH.exists()
 

@@ -32,6 +32,11 @@ def ops():
 
 @pytest.fixture(scope="session")
 def ref():
-    """Reference kernels rebuilt for sm_100a (oracle/_ref); None when not built."""
+    """Reference kernels rebuilt for sm_100a (oracle/_ref/libds4ref.so).  The built library travels with
+    the tree to the GPU box, so a GPU run without it means the build step failed: that is a test failure,
+    not a skip (otherwise every bit-for-bit comparison with the reference would silently drop out)."""
     import ref_lib
-    return ref_lib if ref_lib.available() else None
+    assert ref_lib.available(), (
+        "oracle/_ref/libds4ref.so is missing: run `make -C oracle ref REF=<reference tree>` "
+        "(__graft_entry__.build() does it when the reference tree is reachable)")
+    return ref_lib

@@ -188,7 +188,9 @@ def test_ops_refuse_cpu_tensors():
         ops.add(torch.zeros(4), torch.zeros(4))
 
 
-REFERENCE = Path(__import__("os").environ.get("DS4_REFERENCE", "/root/reference"))
+import ref_lib  # noqa: E402  (oracle/ is on sys.path through conftest)
+
+REFERENCE = ref_lib.reference_tree() or Path("reference-tree-not-reachable")
 CALLERS = ["forward_layer.cu", "forward_token.cu", "forward_batch.cu", "compressor.cu"]
 STAR = ("launch_rms_norm_f32", "launch_rms_norm_batch_f32", "launch_add_f32", "launch_tail_rope_yarn_f32",
         "launch_tail_rope_yarn_inverse_f32", "launch_fp8_kv_quantize_round_trip_f32", "launch_silu_mul_f32",

@@ -5,7 +5,8 @@ then already run every other test.  The entry point keeps its intermediate in a
 fixed device array inside the library, for callers that may not allocate device
 memory and have no spare buffer to lend; this test drives it through the C ABI,
 twice in a row with different batch sizes, and compares each result with the
-ordinary entry point (caller-provided intermediate) on the same inputs.
+ordinary entry point (caller-provided intermediate) on the same inputs and with
+the CPU oracle.
 """
 import ctypes as C
 
@@ -38,6 +39,12 @@ def _run_both(L, T, n_embd, seed):
     assert np.isfinite(got).all()
     err = np.abs(got - want).max()
     assert err <= REL_TOL * np.abs(want).max(), f"T={T}: max-abs error {err:.3e}"
+    # and against the CPU oracle, not only against the sibling entry point
+    import oracle_lib as oracle
+    oracle.lib()
+    mixed, _ = oracle.hc_sinkhorn_mix_rows(logits.cpu().numpy(), resid.cpu().numpy())
+    err = np.abs(got - mixed).max()
+    assert err <= REL_TOL * np.abs(mixed).max(), f"T={T}: max-abs error vs the oracle {err:.3e}"
 
 
 def test_static_scratch_entry_point_matches_the_ordinary_one_twice_in_a_row():
