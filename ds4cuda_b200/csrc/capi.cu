@@ -6,6 +6,7 @@
 #include <cstdio>
 
 #include "../../include/ds4b200.h"
+#include "device_utils.cuh"
 #include "kernels.cuh"
 
 namespace ds4b200 {
@@ -153,6 +154,25 @@ int ds4b200_rope_rows_f32(const float *x_in, float *x_out, int64_t n_tokens, int
     ds4b200::rope_rows(x_in, x_out, n_tokens, n_heads, head_dim, n_rot, pos, 0, *params, inverse,
                        unit_rms, eps, STREAM(stream));
     return launched("rope_rows");
+}
+
+int ds4b200_rope_q8_0_rows_f32(const float *x_in, float *x_out, int8_t *xq, float *xscale, int64_t n_tokens,
+                               int n_heads, int head_dim, int n_rot, const int32_t *pos,
+                               const ds4b200_rope_params *params, int inverse, int unit_rms, float eps,
+                               void *stream) {
+    REQUIRE(n_tokens >= 0 && n_heads >= 0 && head_dim >= 0, "rope_q8_0_rows: negative size");
+    if (n_tokens == 0 || n_heads == 0 || head_dim == 0) return 0;
+    REQUIRE(n_tokens * n_heads < ((int64_t)1 << 31), "rope_q8_0_rows: too many rows");
+    REQUIRE(x_in && xq && xscale && pos && params, "rope_q8_0_rows: null pointer");
+    REQUIRE(head_dim % 32 == 0 && head_dim <= 1024, "rope_q8_0_rows: head_dim must be a multiple of 32, at most 1024");
+    REQUIRE(n_rot >= 0 && n_rot <= head_dim && (n_rot & 3) == 0, "rope_q8_0_rows: n_rot must be a multiple of 4 and <= head_dim");
+    REQUIRE(params->theta_scale > 0.0f || params->freq_base > 0.0f, "rope_q8_0_rows: no theta_scale and no freq_base");
+    REQUIRE(ds4b200::aligned16(x_in) && (!x_out || ds4b200::aligned16(x_out)) &&
+                (reinterpret_cast<uintptr_t>(xq) & 3u) == 0,
+            "rope_q8_0_rows: alignment (16 bytes for the f32 rows, 4 for xq)");
+    ds4b200::rope_rows(x_in, x_out, n_tokens, n_heads, head_dim, n_rot, pos, 0, *params, inverse, unit_rms, eps,
+                       STREAM(stream), xq, xscale);
+    return launched("rope_q8_0_rows");
 }
 
 int ds4b200_fp8_kv_round_trip_rows_f32(const float *kv_in, float *kv_out, int64_t n_rows,

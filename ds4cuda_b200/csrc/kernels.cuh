@@ -35,9 +35,12 @@ int *device_status_word();            // its device address on the current devic
 void selftest_bounded_wait(int max_polls, int *gave_up_dev, cudaStream_t s);
 
 // pos == nullptr: every token uses single_pos.
+// xq != nullptr: the rotated rows also leave as Q8_0 blocks (xq int8, xscale one per 32); x_out may then
+// be null.  That form needs head_dim % 32 == 0, n_rot % 4 == 0 and 16-byte aligned rows.
 void rope_rows(const float *x_in, float *x_out, int64_t n_tokens, int n_heads, int head_dim,
                int n_rot, const int32_t *pos, int single_pos, const ds4b200_rope_params &p,
-               int inverse, int unit_rms, float eps, cudaStream_t s);
+               int inverse, int unit_rms, float eps, cudaStream_t s, int8_t *xq = nullptr,
+               float *xscale = nullptr);
 
 void fp8_kv_round_trip_rows(const float *kv_in, float *kv_out, int64_t n_rows, int head_dim,
                             int n_rot, cudaStream_t s);

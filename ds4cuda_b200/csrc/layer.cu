@@ -36,6 +36,10 @@ extern "C" int ds4b200_layer_rows_f32(const ds4b200_layer_dims *d, const ds4b200
                           b->router_w, b->mid_q, b->mid_scale, b->mid_bsums, b->moe_out, b->shexp_out};
     for (const void *p : need)
         if (!p) return set_error(-EINVAL, "layer_rows: null weight or buffer");
+    if (!b->kqv_q != !b->kqv_scale) return set_error(-EINVAL, "layer_rows: kqv_q and kqv_scale go together");
+    if (b->kqv_q && (d->head_dim % 32 || (reinterpret_cast<uintptr_t>(b->kqv) & 15u) ||
+                     (reinterpret_cast<uintptr_t>(b->kqv_q) & 3u)))
+        return set_error(-EINVAL, "layer_rows: the Q8_0 form of the inverse RoPE needs head_dim % 32 == 0 and aligned rows");
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int n = d->n_embd, hd = d->head_dim;
@@ -64,7 +68,11 @@ extern "C" int ds4b200_layer_rows_f32(const ds4b200_layer_dims *d, const ds4b200
     ds4b200::rope_rows(b->q, b->q, T, d->n_heads, hd, d->n_rot, pos, 0, rope, 0, 1, d->eps, s);
     if ((rc = launch_ok("q norm + RoPE"))) return rc;
     if ((rc = call(DS4B200_STAGE_ATTENTION))) return rc;
-    ds4b200::rope_rows(b->kqv, b->kqv, T, d->n_heads, hd, d->n_rot, pos, 0, rope, 1, 0, d->eps, s);
+    if (b->kqv_q)      // rotated rows straight into the out-projection's activation blocks, no f32 round trip
+        ds4b200::rope_rows(b->kqv, nullptr, T, d->n_heads, hd, d->n_rot, pos, 0, rope, 1, 0, d->eps, s, b->kqv_q,
+                           b->kqv_scale);
+    else
+        ds4b200::rope_rows(b->kqv, b->kqv, T, d->n_heads, hd, d->n_rot, pos, 0, rope, 1, 0, d->eps, s);
     if ((rc = launch_ok("inverse RoPE"))) return rc;
     if ((rc = call(DS4B200_STAGE_ATTN_OUT))) return rc;
     ds4b200::hc_post_rows(b->attn_out, nullptr, resid_in, b->post, b->comb, nullptr, nullptr, b->resid_mid, T, n, 0,

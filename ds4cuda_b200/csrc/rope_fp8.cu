@@ -76,11 +76,14 @@ __device__ __forceinline__ void rope_tail_warp(float4 (&v)[VPT], int lane, int n
 }
 
 // ------------------------------- RoPE rows ---------------------------------
-template <int VPT>
+// Q8: the rotated row also (or only, x_out == nullptr) leaves as Q8_0 blocks, the activation form of
+// the matvec that consumes it (cuda/attn_out.cu:119-145 for the rows behind the inverse RoPE): 32
+// elements = 8 consecutive lanes of one float4 slot, amax by shuffles, d = amax / 127, RNE, clamp.
+template <int VPT, bool Q8>
 __global__ void __launch_bounds__(kRowsPerCta * 32)
 rope_rows_kernel(const float *x_in, float *x_out, int64_t n_rows, int n_heads, int head_dim,
                  int n_rot, const int32_t *pos, int single_pos, RopeDev p, int inverse,
-                 int unit_rms, float eps) {
+                 int unit_rms, float eps, int8_t *xq, float *xscale) {
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * kRowsPerCta + (threadIdx.x >> 5);
     if (row >= n_rows) return;
@@ -106,7 +109,22 @@ rope_rows_kernel(const float *x_in, float *x_out, int64_t n_rows, int n_heads, i
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
         const int i = lane + 32 * j;
-        if (i < n4) st_stream4(yr + 4 * i, v[j]);
+        const bool live = i < n4;
+        if (live && (!Q8 || x_out)) st_stream4(yr + 4 * i, v[j]);
+        if (Q8) {
+            // head_dim % 32 == 0, so a group of 8 lanes is live or dead as a whole
+            float amax = live ? amax4(v[j]) : 0.0f;
+#pragma unroll
+            for (int off = 4; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+            const float d = amax / 127.0f;
+            const float id = (d != 0.0f) ? 1.0f / d : 0.0f;
+            if (live) {
+                auto q8 = [](float t) { const int q = __float2int_rn(t); return (uint32_t)((q > 127 ? 127 : (q < -128 ? -128 : q)) & 0xff); };
+                const uint32_t packed = q8(v[j].x * id) | (q8(v[j].y * id) << 8) | (q8(v[j].z * id) << 16) | (q8(v[j].w * id) << 24);
+                reinterpret_cast<uint32_t *>(xq + row * head_dim)[i] = packed;
+                if ((i & 7) == 0) xscale[row * (head_dim >> 5) + (i >> 3)] = d;
+            }
+        }
     }
 }
 
@@ -441,10 +459,23 @@ unsigned warp_row_grid(int64_t n_rows) { return (unsigned)((n_rows + kRowsPerCta
 
 void rope_rows(const float *x_in, float *x_out, int64_t n_tokens, int n_heads, int head_dim,
                int n_rot, const int32_t *pos, int single_pos, const ds4b200_rope_params &p,
-               int inverse, int unit_rms, float eps, cudaStream_t s) {
+               int inverse, int unit_rms, float eps, cudaStream_t s, int8_t *xq, float *xscale) {
     const int64_t n_rows = n_tokens * n_heads;
     if (n_rows <= 0 || head_dim <= 0) return;
     const RopeDev d = to_dev(p);
+    if (xq) {
+        // checked by the caller: head_dim % 32 == 0, head_dim <= 1024, n_rot % 4 == 0, 16-byte rows
+        const int vpt = ((head_dim >> 2) + 31) / 32;
+        const unsigned grid = warp_row_grid(n_rows);
+#define DS4B200_ROPEQ(V) rope_rows_kernel<V, true><<<grid, kRowsPerCta * 32, 0, s>>>( \
+        x_in, x_out, n_rows, n_heads, head_dim, n_rot, pos, single_pos, d, inverse, unit_rms, eps, xq, xscale)
+        if (vpt <= 1) DS4B200_ROPEQ(1);
+        else if (vpt <= 2) DS4B200_ROPEQ(2);
+        else if (vpt <= 4) DS4B200_ROPEQ(4);
+        else DS4B200_ROPEQ(8);
+#undef DS4B200_ROPEQ
+        return;
+    }
     const bool vec = (head_dim & 3) == 0 && (n_rot & 3) == 0 && head_dim <= 1024 &&
                      aligned16(x_in) && aligned16(x_out);
     if (!vec) {
@@ -454,8 +485,8 @@ void rope_rows(const float *x_in, float *x_out, int64_t n_tokens, int n_heads, i
     }
     const int vpt = ((head_dim >> 2) + 31) / 32;
     const unsigned grid = warp_row_grid(n_rows);
-#define DS4B200_ROPE(V) rope_rows_kernel<V><<<grid, kRowsPerCta * 32, 0, s>>>( \
-        x_in, x_out, n_rows, n_heads, head_dim, n_rot, pos, single_pos, d, inverse, unit_rms, eps)
+#define DS4B200_ROPE(V) rope_rows_kernel<V, false><<<grid, kRowsPerCta * 32, 0, s>>>( \
+        x_in, x_out, n_rows, n_heads, head_dim, n_rot, pos, single_pos, d, inverse, unit_rms, eps, nullptr, nullptr)
     if (vpt <= 1) DS4B200_ROPE(1);
     else if (vpt <= 2) DS4B200_ROPE(2);
     else if (vpt <= 4) DS4B200_ROPE(4);

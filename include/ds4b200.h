@@ -179,6 +179,17 @@ int ds4b200_rope_rows_f32(const float *x_in, float *x_out, int64_t n_tokens, int
                           const ds4b200_rope_params *params, int inverse, int unit_rms,
                           float eps, void *stream);
 
+/* The same rotation with the rows leaving as Q8_0 activation blocks, the form the grouped
+ * out-projection quantises its input to right behind the inverse RoPE (cuda/forward_layer.cu:1179
+ * then cuda/attn_out.cu:119-145): xq int8 [n_tokens][n_heads][head_dim], xscale
+ * [n_tokens][n_heads][head_dim/32] (d = amax/127 per 32 values, round to nearest even, clamp to
+ * [-128, 127]).  x_out is optional: NULL drops the f32 copy, which is then never written to memory.
+ * head_dim a multiple of 32 (<= 1024), n_rot a multiple of 4, 16-byte aligned f32 rows. */
+int ds4b200_rope_q8_0_rows_f32(const float *x_in, float *x_out, int8_t *xq, float *xscale,
+                               int64_t n_tokens, int n_heads, int head_dim, int n_rot,
+                               const int32_t *pos, const ds4b200_rope_params *params, int inverse,
+                               int unit_rms, float eps, void *stream);
+
 /* FP8 E4M3FN quantise/dequantise round trip, cuda/fp8_kv.cu:144-195. */
 int ds4b200_fp8_kv_round_trip_rows_f32(const float *kv_in, float *kv_out, int64_t n_rows,
                                        int head_dim, int n_rot, void *stream);

@@ -15,7 +15,7 @@
  *   Q_B                caller: q_lora_norm -> q                        (:879)
  *   q norm + RoPE      q in place                                      (:890, :901)
  *   ATTENTION          caller: q, raw_rows, caches -> kqv              (:997-1166)
- *   inverse RoPE       kqv in place                                    (:1179)
+ *   inverse RoPE       kqv in place, or -> kqv_q, kqv_scale (Q8_0)     (:1179)
  *   ATTN_OUT           caller: kqv -> attn_out                         (:1190, :1205)
  *   hc attn post       attn_out, resid_in, post, comb -> resid_mid     (:1217)
  *   hc ffn pre         resid_mid -> x, post, comb                      (:1235)
@@ -85,6 +85,11 @@ typedef struct ds4b200_layer_buffers {      /* caller-owned device workspace for
     float *mid_scale;                       /* [T][top_k][ff_dim/256] */
     int16_t *mid_bsums;                     /* [T][top_k][ff_dim/256][16] */
     float *moe_out, *shexp_out;             /* [T][n_embd] */
+    /* Optional (both or neither): when given, the inverse RoPE leaves its rows as the Q8_0 blocks
+     * the grouped out-projection quantises them to (cuda/attn_out.cu:119-145) and kqv is NOT
+     * rewritten: ATTN_OUT then reads kqv_q / kqv_scale instead of rotated f32 rows. */
+    int8_t *kqv_q;                          /* [T][n_heads][head_dim] */
+    float *kqv_scale;                       /* [T][n_heads][head_dim/32] */
 } ds4b200_layer_buffers;
 
 /* Called on the issuing thread between row stages; must enqueue its work on `stream` (or

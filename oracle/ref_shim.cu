@@ -115,6 +115,14 @@ void ds4ref_mul_mv_q8_0_q8_0_f32_prealloc(const void *w_blocks, const float *x, 
                                          scratch_xscale, S(s));
 }
 
+// The grouped out-projection quantises its input (the rows behind the inverse RoPE) into caller scratch.
+void ds4ref_mul_mv_q8_0_q8_0_grouped_f32_prealloc(const void *w_blocks, const float *x, float *y, int n_groups,
+                                                  int group_dim, int rank, int8_t *scratch_xq, float *scratch_xscale,
+                                                  void *s) {
+    launch_mul_mv_q8_0_q8_0_grouped_f32_prealloc(static_cast<const block_q8_0 *>(w_blocks), x, y, n_groups, group_dim,
+                                                 rank, scratch_xq, scratch_xscale, S(s));
+}
+
 void ds4ref_mul_mv_f16_f32(const uint16_t *w, const float *x, float *y, int out_dim, int in_dim, void *s) {
     launch_mul_mv_f16_f32(w, x, y, out_dim, in_dim, S(s));
 }

@@ -174,6 +174,20 @@ def test_layer_rows_entry_point_sequences_the_same_chain(ops):
     eq(B["mid_scale"], ms, "routed epilogue Q8_K scales"); eq(B["mid_bsums"], mb, "routed epilogue Q8_K sums")
     eq(out, want, "residual streams after the layer")
 
+    # ---- with the optional Q8_0 buffers the inverse RoPE leaves the out-projection's activation blocks and
+    # does not rewrite kqv; everything else is unchanged
+    kq = torch.zeros(T, H, hd, dtype=torch.int8, device="cuda")
+    ks = torch.zeros(T, H, hd // 32, device="cuda")
+    buffers_q = _lib.LayerBuffers(*[B[nm].data_ptr() for nm in _lib.LayerBuffers.NAMES], kq.data_ptr(), ks.data_ptr())
+    out_q = torch.zeros(T, 4, n, device="cuda")
+    rc = L.ds4b200_layer_rows_f32(C.byref(dims), C.byref(weights), C.byref(buffers_q), resid_hc.data_ptr(),
+                                  pos.data_ptr(), T, out_q.data_ptr(), cb, None, None)
+    assert rc == 0, L.ds4b200_last_error()
+    torch.cuda.synchronize()
+    wq, ws = ops.quantize_q8_0_rows(kqv_back)
+    eq(kq.view(-1), wq.view(-1), "inverse RoPE Q8_0 values"); eq(ks.view(-1), ws.view(-1), "inverse RoPE Q8_0 scales")
+    eq(B["kqv"], S["kqv"], "kqv left as the attention stage wrote it"); eq(out_q, want, "residual streams (Q8_0 form)")
+
     # a hook that fails stops the layer with its code
     bad = _lib.StageHook(lambda user, stage, n_tokens, stream: -7 if stage == _lib.STAGE_Q_B else 0)
     assert L.ds4b200_layer_rows_f32(C.byref(dims), C.byref(weights), C.byref(buffers), resid_hc.data_ptr(),

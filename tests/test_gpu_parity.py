@@ -714,6 +714,39 @@ def test_rms_norm_with_fused_q8_0(ops, oracle, rows, n):
     assert torch.equal(xq3, xq) and torch.equal(xs3, xs)
 
 
+def test_inverse_rope_with_q8_0_output(ops, ref):
+    """The inverse RoPE whose rows leave as Q8_0 blocks: the f32 copy equals rope_rows bit for bit, the
+    blocks equal the stand-alone quantiser on those rows, and both equal what the reference's grouped
+    out-projection leaves in its caller's scratch after its own inverse RoPE (cuda/forward_layer.cu:1179,
+    cuda/attn_out.cu:119-145)."""
+    g = inputs.rng(981)
+    T, H, D, il = 5, 64, 512, 2
+    kqv = inputs.normal(g, (T, H, D), 1.5)
+    kqv[1, 3, 32:64] = 0.0                      # an all-zero block: scale 0, values 0
+    pos = np.array([0, 1, 77, 4095, 65535], dtype=np.int32)
+    rp = ops.rope_params_for_layer(il)
+    want = ops.rope_rows(dev(kqv), dev(pos), rp, inverse=True)
+    out, xq, xs = ops.rope_q8_0_rows(dev(kqv), dev(pos), rp, inverse=True, want_f32=True)
+    assert torch.equal(out, want)
+    q2, s2 = ops.quantize_q8_0_rows(want)
+    assert torch.equal(xq.view(-1), q2.view(-1)) and torch.equal(xs.view(-1), s2.view(-1))
+    none, xq3, xs3 = ops.rope_q8_0_rows(dev(kqv), dev(pos), rp, inverse=True)
+    assert none is None and torch.equal(xq3, xq) and torch.equal(xs3, xs)
+    # the reference, token by token: inverse RoPE launcher, then the grouped matvec's quantiser
+    n_groups, rank = 8, 4
+    group_dim = H * D // n_groups
+    w = dev(inputs.q8_0_table(g, n_groups * rank, group_dim))
+    for t in range(T):
+        back = torch.empty(H * D, device="cuda")
+        ref.call("tail_rope_yarn_inverse_f32", dev(kqv[t]), back, H, D, 64, int(pos[t]), il)
+        y = torch.empty(n_groups * rank, device="cuda")
+        sq = torch.empty(H * D, dtype=torch.int8, device="cuda")
+        ss = torch.empty(H * D // 32, dtype=torch.float32, device="cuda")
+        ref.call("mul_mv_q8_0_q8_0_grouped_f32_prealloc", w, back, y, n_groups, group_dim, rank, sq, ss)
+        assert_bits(host(xq[t]).ravel(), host(sq), f"token {t}: Q8_0 values vs the reference's grouped quantiser")
+        assert_bits(host(xs[t]).ravel(), host(ss), f"token {t}: Q8_0 scales vs the reference's grouped quantiser")
+
+
 def test_reference_kernel_library_present(ref):
     """The bit-for-bit comparisons above need the reference's kernels rebuilt for sm_100a: the `ref`
     fixture fails when the library is missing, and it must load."""
