@@ -410,6 +410,23 @@ def only_ops(tokens):
         return (lambda: ops.rope_q8_0_rows(q, pos, rp, inverse=True)), T * 64 * (KV_DIM * 4 + KV_DIM + KV_DIM // 8), \
             "inverse tail RoPE leaving as the out-projection's Q8_0 blocks (no f32 copy)"
 
+    def rope_inverse_q8_0_table():
+        q, pos = rnd(T, 64, KV_DIM), torch.arange(T, device=dev, dtype=torch.int32)
+        table = ops.rope_table_rows(pos, ops.rope_params_for_layer(2))
+        return (lambda: ops.rope_q8_0_rows(q, None, None, inverse=True, table=table)), \
+            T * (64 * (KV_DIM * 4 + KV_DIM + KV_DIM // 8) + 256), "the same, angles from the chunk's table"
+
+    def rope_rows_table():
+        q, pos = rnd(T, 64, KV_DIM), torch.arange(T, device=dev, dtype=torch.int32)
+        table = ops.rope_table_rows(pos, ops.rope_params_for_layer(2))
+        return (lambda: ops.rope_rows(q, None, None, unit_rms=True, out=q, table=table)), T * (64 * KV_DIM * 8 + 256), \
+            "q_norm + tail RoPE over 64 heads per token, angles from the chunk's table"
+
+    def rope_table():
+        pos = torch.arange(T, device=dev, dtype=torch.int32)
+        rp = ops.rope_params_for_layer(2)
+        return (lambda: ops.rope_table_rows(pos, rp)), T * (4 + 256), "the chunk's angle table (once per chunk and parameter set)"
+
     def fp8_round_trip():
         rows = T * 16
         kv = rnd(rows, KV_DIM, s=1.5)
@@ -436,7 +453,7 @@ def only_ops(tokens):
         return (lambda: ops.quantize_q8_K_rows(x)), T * TOP_K * (FF_DIM * 4 + FF_DIM + FF_DIM // 256 * 36), "Q8_K activation quantiser"
 
     for f in (hc_pre, hc_post_block, hc_head, rms_norm_cta, rms_norm_q8_0, rms_norm_warp, rope_rows, rope_inverse,
-              rope_inverse_q8_0, fp8_round_trip, rope_fp8_store, swiglu_q8k, quantize_q8_K):
+              rope_inverse_q8_0, rope_inverse_q8_0_table, rope_rows_table, rope_table, fp8_round_trip, rope_fp8_store, swiglu_q8k, quantize_q8_K):
         add(f.__name__, f)
     return reg
 
@@ -539,8 +556,9 @@ def layer_row_stages_leg(tokens, peak):
     stage("attn_norm+q8_0", lambda: ops.rms_norm_q8_0_rows(x, w_n))
     stage("q_a_norm", lambda: ops.rms_norm_rows(q_lora, w_q))
     stage("kv_norm+rope+fp8+f16", lambda: ops.kv_rows_to_raw(kv_raw, pos, rope, raw_rows, norm_w=w_kv))
-    stage("q_norm+rope", lambda: ops.rope_rows(q_raw, pos, rope, unit_rms=True, out=q_raw))
-    stage("attn_out_inverse_rope+q8_0", lambda: ops.rope_q8_0_rows(kqv, pos, rope, inverse=True))
+    table = stage("rope_angle_table", lambda: ops.rope_table_rows(pos, rope))
+    stage("q_norm+rope", lambda: ops.rope_rows(q_raw, None, None, unit_rms=True, out=q_raw, table=table))
+    stage("attn_out_inverse_rope+q8_0", lambda: ops.rope_q8_0_rows(kqv, None, None, inverse=True, table=table))
     resid_attn = stage("hc_attn_post", lambda: ops.hc_post_rows(attn_out, resid_hc, post_a, comb_a))
     post_f, comb_f, xf = stage("hc_ffn_pre", lambda: ops.hc_pre_rows(resid_attn, fn_f, scale3, base24))
     stage("ffn_norm+q8_0", lambda: ops.rms_norm_q8_0_rows(xf, w_n))
@@ -558,7 +576,8 @@ def layer_row_stages_leg(tokens, peak):
                 post=z(T, 4), comb=z(T, 16), resid_mid=z(T, 4, n), sh_gate=sh_gate, sh_up=sh_up, sh_mid=z(T, FF_DIM),
                 gate=gate, up=up, router_w=w_r, mid_q=z(T, TOP_K, FF_DIM, dt=torch.int8),
                 mid_scale=z(T, TOP_K, FF_DIM // 256), mid_bsums=z(T, TOP_K, FF_DIM // 256, 16, dt=torch.int16),
-                moe_out=moe_out, shexp_out=shexp, kqv_q=z(T, 64, KV_DIM, dt=torch.int8), kqv_scale=z(T, 64, KV_DIM // 32))
+                moe_out=moe_out, shexp_out=shexp, kqv_q=z(T, 64, KV_DIM, dt=torch.int8), kqv_scale=z(T, 64, KV_DIM // 32),
+                rope_cs=z(T, N_ROT // 2, 2))
     wts = dict(hc_attn_fn=fn_a, hc_attn_scale=scale3, hc_attn_base=base24, attn_norm=w_n, q_a_norm=w_q, kv_a_norm=w_kv,
                hc_ffn_fn=fn_f, hc_ffn_scale=scale3, hc_ffn_base=base24, ffn_norm=w_n)
     dims = _lib.LayerDims(n, 64, KV_DIM, N_ROT, 1024, FF_DIM, TOP_K, 20, 2, 1, 1e-6, 10.0)

@@ -55,7 +55,7 @@ class LayerBuffers(C.Structure):
     NAMES = ("x", "x_norm", "xq", "xscale", "q_lora", "q_lora_norm", "kv_raw", "raw_rows", "q", "kqv", "attn_out",
              "post", "comb", "resid_mid", "sh_gate", "sh_up", "sh_mid", "gate", "up", "router_w", "mid_q",
              "mid_scale", "mid_bsums", "moe_out", "shexp_out")
-    OPTIONAL = ("kqv_q", "kqv_scale")
+    OPTIONAL = ("kqv_q", "kqv_scale", "rope_cs")
     _fields_ = [(n, C.c_void_p) for n in NAMES + OPTIONAL]
 
 
@@ -98,7 +98,9 @@ SIGNATURES = {
     "ds4b200_quantize_q8_K_rows_f32": (_I, [_P, _P, _P, _P, _L, _P]),
     "ds4b200_embed_gather_rows": (_I, [_P, _I, _P, _L, _I, _P, _P, _F, _P, _I, _P, _P, _P]),
     "ds4b200_rope_rows_f32": (_I, [_P, _P, _L, _I, _I, _I, _P, _RP, _I, _I, _F, _P]),
-    "ds4b200_rope_q8_0_rows_f32": (_I, [_P, _P, _P, _P, _L, _I, _I, _I, _P, _RP, _I, _I, _F, _P]),
+    "ds4b200_rope_q8_0_rows_f32": (_I, [_P, _P, _P, _P, _L, _I, _I, _I, _P, _RP, _P, _I, _I, _F, _P]),
+    "ds4b200_rope_table_rows": (_I, [_P, _RP, _L, _I, _P, _P]),
+    "ds4b200_rope_rows_table_f32": (_I, [_P, _P, _L, _I, _I, _I, _P, _I, _I, _F, _P]),
     "ds4b200_fp8_kv_round_trip_rows_f32": (_I, [_P, _P, _L, _I, _I, _P]),
     "ds4b200_rope_fp8_store_rows": (_I, [_P, _L, _I, _I, _P, _RP, _P, _F, _I, _P, _P, _P, _P, _P, _P]),
     "ds4b200_fp8_cache_load_rows": (_I, [_P, _P, _P, _P, _L, _I, _I, _I, _I, _P, _P]),

@@ -156,22 +156,57 @@ int ds4b200_rope_rows_f32(const float *x_in, float *x_out, int64_t n_tokens, int
     return launched("rope_rows");
 }
 
+int ds4b200_rope_table_rows(const int32_t *pos, const ds4b200_rope_params *params, int64_t n_tokens, int n_rot,
+                            float *cs_table, void *stream) {
+    REQUIRE(n_tokens >= 0, "rope_table_rows: n_tokens < 0");
+    if (n_tokens == 0) return 0;
+    REQUIRE(pos && params && cs_table, "rope_table_rows: null pointer");
+    REQUIRE(n_rot > 0 && n_rot <= 64 && (n_rot & 1) == 0, "rope_table_rows: n_rot must be even, at most 64");
+    REQUIRE(params->theta_scale > 0.0f || params->freq_base > 0.0f, "rope_table_rows: no theta_scale and no freq_base");
+    REQUIRE((reinterpret_cast<uintptr_t>(cs_table) & 7u) == 0, "rope_table_rows: cs_table must be 8-byte aligned");
+    ds4b200::rope_table_rows(pos, n_tokens, n_rot, *params, cs_table, STREAM(stream));
+    return launched("rope_table_rows");
+}
+
+int ds4b200_rope_rows_table_f32(const float *x_in, float *x_out, int64_t n_tokens, int n_heads, int head_dim,
+                                int n_rot, const float *cs_table, int inverse, int unit_rms, float eps,
+                                void *stream) {
+    REQUIRE(n_tokens >= 0 && n_heads >= 0 && head_dim >= 0, "rope_rows_table: negative size");
+    if (n_tokens == 0 || n_heads == 0 || head_dim == 0) return 0;
+    REQUIRE(n_tokens * n_heads < ((int64_t)1 << 31), "rope_rows_table: too many rows");
+    REQUIRE(x_in && x_out && cs_table, "rope_rows_table: null pointer");
+    REQUIRE(head_dim % 4 == 0 && head_dim <= 1024, "rope_rows_table: head_dim must be a multiple of 4, at most 1024");
+    REQUIRE(n_rot > 0 && n_rot <= 64 && n_rot <= head_dim && (n_rot & 3) == 0,
+            "rope_rows_table: n_rot must be a multiple of 4, at most 64 and head_dim");
+    REQUIRE(ds4b200::aligned16(x_in) && ds4b200::aligned16(x_out) && (reinterpret_cast<uintptr_t>(cs_table) & 7u) == 0,
+            "rope_rows_table: alignment (16 bytes for the rows, 8 for cs_table)");
+    ds4b200_rope_params unused{};
+    unused.theta_scale = 1.0f;
+    ds4b200::rope_rows(x_in, x_out, n_tokens, n_heads, head_dim, n_rot, nullptr, 0, unused, inverse, unit_rms, eps,
+                       STREAM(stream), nullptr, nullptr, cs_table);
+    return launched("rope_rows_table");
+}
+
 int ds4b200_rope_q8_0_rows_f32(const float *x_in, float *x_out, int8_t *xq, float *xscale, int64_t n_tokens,
                                int n_heads, int head_dim, int n_rot, const int32_t *pos,
-                               const ds4b200_rope_params *params, int inverse, int unit_rms, float eps,
-                               void *stream) {
+                               const ds4b200_rope_params *params, const float *cs_table, int inverse,
+                               int unit_rms, float eps, void *stream) {
     REQUIRE(n_tokens >= 0 && n_heads >= 0 && head_dim >= 0, "rope_q8_0_rows: negative size");
     if (n_tokens == 0 || n_heads == 0 || head_dim == 0) return 0;
     REQUIRE(n_tokens * n_heads < ((int64_t)1 << 31), "rope_q8_0_rows: too many rows");
-    REQUIRE(x_in && xq && xscale && pos && params, "rope_q8_0_rows: null pointer");
+    REQUIRE(x_in && xq && xscale && ((pos && params) || cs_table), "rope_q8_0_rows: null pointer");
+    REQUIRE(!cs_table || (n_rot <= 64 && (reinterpret_cast<uintptr_t>(cs_table) & 7u) == 0),
+            "rope_q8_0_rows: a table needs n_rot <= 64 and 8-byte alignment");
     REQUIRE(head_dim % 32 == 0 && head_dim <= 1024, "rope_q8_0_rows: head_dim must be a multiple of 32, at most 1024");
     REQUIRE(n_rot >= 0 && n_rot <= head_dim && (n_rot & 3) == 0, "rope_q8_0_rows: n_rot must be a multiple of 4 and <= head_dim");
-    REQUIRE(params->theta_scale > 0.0f || params->freq_base > 0.0f, "rope_q8_0_rows: no theta_scale and no freq_base");
+    REQUIRE(cs_table || params->theta_scale > 0.0f || params->freq_base > 0.0f, "rope_q8_0_rows: no theta_scale and no freq_base");
     REQUIRE(ds4b200::aligned16(x_in) && (!x_out || ds4b200::aligned16(x_out)) &&
                 (reinterpret_cast<uintptr_t>(xq) & 3u) == 0,
             "rope_q8_0_rows: alignment (16 bytes for the f32 rows, 4 for xq)");
-    ds4b200::rope_rows(x_in, x_out, n_tokens, n_heads, head_dim, n_rot, pos, 0, *params, inverse, unit_rms, eps,
-                       STREAM(stream), xq, xscale);
+    ds4b200_rope_params none{};
+    none.theta_scale = 1.0f;
+    ds4b200::rope_rows(x_in, x_out, n_tokens, n_heads, head_dim, n_rot, pos, 0, params ? *params : none, inverse,
+                       unit_rms, eps, STREAM(stream), xq, xscale, cs_table);
     return launched("rope_q8_0_rows");
 }
 

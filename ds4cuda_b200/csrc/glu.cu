@@ -110,29 +110,45 @@ swiglu_vec_kernel(const float *__restrict__ gate, const float *__restrict__ up,
 // second kernel).  One warp per 256-element block of one (token, slot) row: the eight values
 // of a lane go from the epilogue straight into the block quantiser, so the f32 rows are
 // neither written nor read back (mid_f32 is optional, for callers that want them too).
-template <int MODE, bool FAST>
+template <int MODE, bool FAST, int NB>
 __global__ void __launch_bounds__(256)
 swiglu_q8k_kernel(const float *__restrict__ gate, const float *__restrict__ up,
                   const float *__restrict__ weights, int8_t *__restrict__ xq, float *__restrict__ xscale,
                   int16_t *__restrict__ xbsums, float *__restrict__ mid_f32, int64_t n_blocks,
                   int blocks_per_row, float clamp) {
     const int lane = threadIdx.x & 31;
-    const int64_t b = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (b >= n_blocks) return;
-    const int64_t base = b * 256;
-    float4 v0 = glu4<MODE, FAST>(ld_stream4(gate + base + 4 * lane), ld_stream4(up + base + 4 * lane), clamp);
-    float4 v1 = glu4<MODE, FAST>(ld_stream4(gate + base + 128 + 4 * lane), ld_stream4(up + base + 128 + 4 * lane), clamp);
-    if (weights) {
-        const float w = __ldg(weights + b / blocks_per_row);        // one weight per (token, slot) row
-        v0 = mul4_rn(v0, w);
-        v1 = mul4_rn(v1, w);
+    const int64_t b0 = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * NB;
+    if (b0 >= n_blocks) return;
+    // a warp takes NB consecutive blocks and issues all 4*NB loads of a lane before the first
+    // epilogue, so every thread keeps 64*NB bytes in flight
+    float4 g[NB][2], u[NB][2];
+#pragma unroll
+    for (int i = 0; i < NB; ++i) {
+        if (b0 + i < n_blocks) {
+            const int64_t base = (b0 + i) * 256;
+            g[i][0] = ld_stream4(gate + base + 4 * lane); g[i][1] = ld_stream4(gate + base + 128 + 4 * lane);
+            u[i][0] = ld_stream4(up + base + 4 * lane);   u[i][1] = ld_stream4(up + base + 128 + 4 * lane);
+        }
     }
-    if (mid_f32) {
-        st_stream4(mid_f32 + base + 4 * lane, v0);
-        st_stream4(mid_f32 + base + 128 + 4 * lane, v1);
+#pragma unroll
+    for (int i = 0; i < NB; ++i) {
+        const int64_t b = b0 + i;
+        if (b >= n_blocks) break;
+        const int64_t base = b * 256;
+        float4 v0 = glu4<MODE, FAST>(g[i][0], u[i][0], clamp);
+        float4 v1 = glu4<MODE, FAST>(g[i][1], u[i][1], clamp);
+        if (weights) {
+            const float w = __ldg(weights + b / blocks_per_row);        // one weight per (token, slot) row
+            v0 = mul4_rn(v0, w);
+            v1 = mul4_rn(v1, w);
+        }
+        if (mid_f32) {
+            st_stream4(mid_f32 + base + 4 * lane, v0);
+            st_stream4(mid_f32 + base + 128 + 4 * lane, v1);
+        }
+        const float e[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        q8k_block_store(e, lane, xq + base, xscale + b, xbsums + b * 16);
     }
-    const float e[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-    q8k_block_store(e, lane, xq + base, xscale + b, xbsums + b * 16);
 }
 
 template <int MODE, bool FAST>
@@ -224,9 +240,16 @@ void swiglu_q8_K_rows(const float *gate, const float *up, const float *weights, 
     const int blocks_per_row = n / 256;
     const int64_t n_blocks = n_rows * blocks_per_row;
     if (n_blocks <= 0) return;
-    const unsigned grid = (unsigned)((n_blocks + 7) / 8);
-#define DS4B200_Q8K(M, F) swiglu_q8k_kernel<M, F><<<grid, 256, 0, s>>>(gate, up, weights, xq, xscale, xbsums, mid_f32, \
-                                                                        n_blocks, blocks_per_row, clamp)
+    // few blocks: one per warp (more warps); many: two per warp (more bytes in flight per thread)
+    const bool many = n_blocks >= 148 * 64;
+    const unsigned grid = (unsigned)(many ? (n_blocks + 15) / 16 : (n_blocks + 7) / 8);
+#define DS4B200_Q8K(M, F)                                                                                              \
+    do {                                                                                                               \
+        if (many) swiglu_q8k_kernel<M, F, 2><<<grid, 256, 0, s>>>(gate, up, weights, xq, xscale, xbsums, mid_f32,      \
+                                                                  n_blocks, blocks_per_row, clamp);                    \
+        else swiglu_q8k_kernel<M, F, 1><<<grid, 256, 0, s>>>(gate, up, weights, xq, xscale, xbsums, mid_f32, n_blocks, \
+                                                             blocks_per_row, clamp);                                   \
+    } while (0)
     if (mode == DS4B200_GLU_PLAIN) { if (fast_exp) DS4B200_Q8K(DS4B200_GLU_PLAIN, true); else DS4B200_Q8K(DS4B200_GLU_PLAIN, false); }
     else if (mode == DS4B200_GLU_CLAMP_REF) { if (fast_exp) DS4B200_Q8K(DS4B200_GLU_CLAMP_REF, true); else DS4B200_Q8K(DS4B200_GLU_CLAMP_REF, false); }
     else { if (fast_exp) DS4B200_Q8K(DS4B200_GLU_CLAMP_SYM, true); else DS4B200_Q8K(DS4B200_GLU_CLAMP_SYM, false); }

@@ -40,7 +40,12 @@ void selftest_bounded_wait(int max_polls, int *gave_up_dev, cudaStream_t s);
 void rope_rows(const float *x_in, float *x_out, int64_t n_tokens, int n_heads, int head_dim,
                int n_rot, const int32_t *pos, int single_pos, const ds4b200_rope_params &p,
                int inverse, int unit_rms, float eps, cudaStream_t s, int8_t *xq = nullptr,
-               float *xscale = nullptr);
+               float *xscale = nullptr, const float *cs_table = nullptr);
+
+// cs_table[t][n_rot/2][2]: the (cos, sin) multipliers of every tail pair at pos[t] (n_rot <= 64), the same bits the
+// RoPE kernels evaluate per head row; those kernels take it in place of pos + params.
+void rope_table_rows(const int32_t *pos, int64_t n_tokens, int n_rot, const ds4b200_rope_params &p, float *cs_table,
+                     cudaStream_t s);
 
 void fp8_kv_round_trip_rows(const float *kv_in, float *kv_out, int64_t n_rows, int head_dim,
                             int n_rot, cudaStream_t s);
@@ -49,7 +54,7 @@ void rope_fp8_store_rows(const float *kv_in, int64_t n_rows, int head_dim, int n
                          const int32_t *pos, const ds4b200_rope_params *p, const float *norm_w,
                          float eps, int scale_mode, const int32_t *slots, uint8_t *codes,
                          float *scales, float *tail_out, float *rope_out, cudaStream_t s,
-                         float *raw_out = nullptr);
+                         float *raw_out = nullptr, const float *cs_table = nullptr);
 
 // Read side of the FP8 byte cache: rows at slots[] -> f32 (optionally f16-rounded).
 void fp8_cache_load_rows(const uint8_t *codes, const float *scales, const float *tail, const int32_t *slots,

@@ -50,6 +50,8 @@ extern "C" int ds4b200_layer_rows_f32(const ds4b200_layer_dims *d, const ds4b200
         return rc ? set_error(rc, "layer_rows: hook stage %d returned %d", stage, rc) : 0;
     };
     int rc;
+    const float *cs = (b->rope_cs && d->n_rot <= 64) ? b->rope_cs : nullptr;
+    if (cs) ds4b200::rope_table_rows(pos, T, d->n_rot, rope, b->rope_cs, s);
 
     // ---- attention half
     ds4b200::hc_pre_rows(resid_in, w->hc_attn_fn, w->hc_attn_scale, w->hc_attn_base, b->post, b->comb, b->x, T, n,
@@ -62,17 +64,18 @@ extern "C" int ds4b200_layer_rows_f32(const ds4b200_layer_dims *d, const ds4b200
                            d->eps, s);
     ds4b200::rope_fp8_store_rows(b->kv_raw, T, hd, d->n_rot, pos, &rope, w->kv_a_norm, d->eps,
                                  DS4B200_FP8_BLOCK64_POW2, nullptr, nullptr, nullptr, nullptr, nullptr, s,
-                                 b->raw_rows);
+                                 b->raw_rows, cs);
     if ((rc = launch_ok("q_a norm / kv chain"))) return rc;
     if ((rc = call(DS4B200_STAGE_Q_B))) return rc;
-    ds4b200::rope_rows(b->q, b->q, T, d->n_heads, hd, d->n_rot, pos, 0, rope, 0, 1, d->eps, s);
+    ds4b200::rope_rows(b->q, b->q, T, d->n_heads, hd, d->n_rot, pos, 0, rope, 0, 1, d->eps, s, nullptr, nullptr, cs);
     if ((rc = launch_ok("q norm + RoPE"))) return rc;
     if ((rc = call(DS4B200_STAGE_ATTENTION))) return rc;
     if (b->kqv_q)      // rotated rows straight into the out-projection's activation blocks, no f32 round trip
         ds4b200::rope_rows(b->kqv, nullptr, T, d->n_heads, hd, d->n_rot, pos, 0, rope, 1, 0, d->eps, s, b->kqv_q,
-                           b->kqv_scale);
+                           b->kqv_scale, cs);
     else
-        ds4b200::rope_rows(b->kqv, b->kqv, T, d->n_heads, hd, d->n_rot, pos, 0, rope, 1, 0, d->eps, s);
+        ds4b200::rope_rows(b->kqv, b->kqv, T, d->n_heads, hd, d->n_rot, pos, 0, rope, 1, 0, d->eps, s, nullptr,
+                           nullptr, cs);
     if ((rc = launch_ok("inverse RoPE"))) return rc;
     if ((rc = call(DS4B200_STAGE_ATTN_OUT))) return rc;
     ds4b200::hc_post_rows(b->attn_out, nullptr, resid_in, b->post, b->comb, nullptr, nullptr, b->resid_mid, T, n, 0,

@@ -102,12 +102,10 @@ __device__ __forceinline__ void store_row(const NormArgs &a, int64_t row, int fi
             float amax = live ? amax4(y) : 0.0f;
 #pragma unroll
             for (int off = 4; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-            const float d = amax / 127.0f;
-            const float id = (d != 0.0f) ? 1.0f / d : 0.0f;
+            float d, id;
+            q8_0_block_scale(amax, d, id);
             if (live) {
-                const uint32_t packed = (uint32_t)(q8_round(y.x * id) & 0xff) | ((uint32_t)(q8_round(y.y * id) & 0xff) << 8) |
-                                        ((uint32_t)(q8_round(y.z * id) & 0xff) << 16) | ((uint32_t)(q8_round(y.w * id) & 0xff) << 24);
-                reinterpret_cast<uint32_t *>(a.xq + row * a.n)[i] = packed;
+                reinterpret_cast<uint32_t *>(a.xq + row * a.n)[i] = q8_pack4_sat(y.x * id, y.y * id, y.z * id, y.w * id);
                 if ((i & 7) == 0) a.xscale[row * (a.n >> 5) + (i >> 3)] = d;
             }
         }

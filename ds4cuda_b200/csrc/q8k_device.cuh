@@ -50,13 +50,12 @@ __device__ __forceinline__ void q8k_block_store(const float (&e)[8], int lane, i
     for (int k = 1; k < 8; ++k) mine = (k == k_own) ? e[k] : mine;
     const float smax = __shfl_sync(0xffffffffu, mine, (int)((idx & 127u) >> 2));
     const float iscale = -127.0f / smax;
-    int q[8];
-#pragma unroll
-    for (int k = 0; k < 8; ++k) q[k] = q8k_round(iscale * e[k]);
-    reinterpret_cast<uint32_t *>(qb)[lane] = q8k_pack4(q[0], q[1], q[2], q[3]);
-    reinterpret_cast<uint32_t *>(qb)[32 + lane] = q8k_pack4(q[4], q[5], q[6], q[7]);
-    // 16 consecutive values = 4 consecutive lanes of one half
-    int s0 = q[0] + q[1] + q[2] + q[3], s1 = q[4] + q[5] + q[6] + q[7];
+    const uint32_t p0 = q8_pack4_sat(iscale * e[0], iscale * e[1], iscale * e[2], iscale * e[3]);
+    const uint32_t p1 = q8_pack4_sat(iscale * e[4], iscale * e[5], iscale * e[6], iscale * e[7]);
+    reinterpret_cast<uint32_t *>(qb)[lane] = p0;
+    reinterpret_cast<uint32_t *>(qb)[32 + lane] = p1;
+    // 16 consecutive values = 4 consecutive lanes of one half; a lane's four bytes add up in one dp4a
+    int s0 = __dp4a((int)p0, 0x01010101, 0), s1 = __dp4a((int)p1, 0x01010101, 0);
     s0 += __shfl_xor_sync(0xffffffffu, s0, 1); s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
     s0 += __shfl_xor_sync(0xffffffffu, s0, 2); s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
     if ((lane & 3) == 0) {

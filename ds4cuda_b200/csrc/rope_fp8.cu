@@ -42,16 +42,25 @@ __device__ __forceinline__ void rope_float4(float4 &v, int e_tail, float posf, f
 // cosf / sinf as rope_float4) and the lanes that hold the tail fetch the two (cos, sin) they
 // need by shuffle, instead of 16 lanes doing two pairs each; more pairs fall back to
 // rope_float4 per lane.  Every lane of the warp must call this.
+// cs_row (optional, only with n_rot <= 64): the token's (cos, sin) multipliers as rope_table_kernel
+// wrote them, pair k at cs_row[k]; the same bits as evaluating them here, at the cost of one load.
 template <int VPT>
 __device__ __forceinline__ void rope_tail_warp(float4 (&v)[VPT], int lane, int n4, int n_nope, int n_rot,
-                                               float posf, const RopeDev &p, bool inverse) {
-    const float ts = rope_theta_scale(p, n_rot);
+                                               float posf, const RopeDev &p, bool inverse,
+                                               const float2 *cs_row = nullptr) {
     if (n_rot <= 64) {
         float c = 1.0f, sn = 0.0f;
         if (2 * lane < n_rot) {
-            float te = posf;
-            for (int k = 0; k < lane; ++k) te *= ts;
-            rope_cs(p, lane, te, inverse, c, sn);
+            if (cs_row) {
+                const float2 cs = __ldg(cs_row + lane);
+                c = cs.x;
+                sn = inverse ? -cs.y : cs.y;
+            } else {
+                const float ts = rope_theta_scale(p, n_rot);
+                float te = posf;
+                for (int k = 0; k < lane; ++k) te *= ts;
+                rope_cs(p, lane, te, inverse, c, sn);
+            }
         }
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
@@ -67,12 +76,30 @@ __device__ __forceinline__ void rope_tail_warp(float4 (&v)[VPT], int lane, int n
             }
         }
     } else {
+        const float ts = rope_theta_scale(p, n_rot);
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
             const int i = lane + 32 * j;
             if (i < n4 && 4 * i >= n_nope) rope_float4(v[j], 4 * i - n_nope, posf, ts, p, inverse);
         }
     }
+}
+
+// The (cos, sin) multipliers of every tail pair of every token, computed once per chunk: they depend on the
+// position and the layer's parameter set only, yet each of a layer's 64 + 64 + 1 head rows per token needs
+// them (cuda/rope.cu:165-200 evaluates them per head row).  One thread per (token, pair); the same
+// multiply chain and the same cosf / sinf as rope_tail_warp, so the rotated rows keep their bits.
+__global__ void rope_table_kernel(const int32_t *pos, int64_t n_tokens, int n_pairs, int n_rot, RopeDev p, float2 *cs) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_tokens * n_pairs) return;
+    const int64_t t = i / n_pairs;
+    const int k = (int)(i - t * n_pairs);
+    const float ts = rope_theta_scale(p, n_rot);
+    float te = (float)pos[t];
+    for (int q = 0; q < k; ++q) te *= ts;
+    float c, s;
+    rope_cs(p, k, te, false, c, s);
+    cs[i] = make_float2(c, s);
 }
 
 // ------------------------------- RoPE rows ---------------------------------
@@ -83,7 +110,7 @@ template <int VPT, bool Q8>
 __global__ void __launch_bounds__(kRowsPerCta * 32)
 rope_rows_kernel(const float *x_in, float *x_out, int64_t n_rows, int n_heads, int head_dim,
                  int n_rot, const int32_t *pos, int single_pos, RopeDev p, int inverse,
-                 int unit_rms, float eps, int8_t *xq, float *xscale) {
+                 int unit_rms, float eps, int8_t *xq, float *xscale, const float2 *cs_table) {
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * kRowsPerCta + (threadIdx.x >> 5);
     if (row >= n_rows) return;
@@ -104,8 +131,9 @@ rope_rows_kernel(const float *x_in, float *x_out, int64_t n_rows, int n_heads, i
 #pragma unroll
         for (int j = 0; j < VPT; ++j) { v[j].x *= scale; v[j].y *= scale; v[j].z *= scale; v[j].w *= scale; }
     }
-    const float posf = (float)(pos ? pos[row / n_heads] : single_pos);
-    rope_tail_warp<VPT>(v, lane, n4, n_nope, n_rot, posf, p, inverse != 0);
+    const float posf = cs_table ? 0.0f : (float)(pos ? pos[row / n_heads] : single_pos);
+    rope_tail_warp<VPT>(v, lane, n4, n_nope, n_rot, posf, p, inverse != 0,
+                        cs_table ? cs_table + (row / n_heads) * (n_rot >> 1) : nullptr);
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
         const int i = lane + 32 * j;
@@ -116,12 +144,10 @@ rope_rows_kernel(const float *x_in, float *x_out, int64_t n_rows, int n_heads, i
             float amax = live ? amax4(v[j]) : 0.0f;
 #pragma unroll
             for (int off = 4; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-            const float d = amax / 127.0f;
-            const float id = (d != 0.0f) ? 1.0f / d : 0.0f;
+            float d, id;
+            q8_0_block_scale(amax, d, id);
             if (live) {
-                auto q8 = [](float t) { const int q = __float2int_rn(t); return (uint32_t)((q > 127 ? 127 : (q < -128 ? -128 : q)) & 0xff); };
-                const uint32_t packed = q8(v[j].x * id) | (q8(v[j].y * id) << 8) | (q8(v[j].z * id) << 16) | (q8(v[j].w * id) << 24);
-                reinterpret_cast<uint32_t *>(xq + row * head_dim)[i] = packed;
+                reinterpret_cast<uint32_t *>(xq + row * head_dim)[i] = q8_pack4_sat(v[j].x * id, v[j].y * id, v[j].z * id, v[j].w * id);
                 if ((i & 7) == 0) xscale[row * (head_dim >> 5) + (i >> 3)] = d;
             }
         }
@@ -231,6 +257,7 @@ struct StoreArgs {
     float *tail_out;
     float *rope_out;
     float *raw_out;     // BLOCK64_POW2 only: f16-rounded round-trip row, the raw-KV cache form
+    const float2 *cs_table;   // optional [n_rows][n_rot / 2] from rope_table_kernel (replaces pos + rope)
 };
 
 // f32 -> f16 -> f32, the rounding the reference applies when a row enters its raw KV cache
@@ -268,7 +295,8 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) rope_fp8_store_kernel(StoreA
         }
     }
     if (a.do_rope)                                    // cuda/forward_layer.cu:910 KV RoPE
-        rope_tail_warp<VPT>(v, lane, n4, n_nope, a.n_rot, (float)a.pos[row], a.rope, false);
+        rope_tail_warp<VPT>(v, lane, n4, n_nope, a.n_rot, a.cs_table ? 0.0f : (float)a.pos[row], a.rope, false,
+                            a.cs_table ? a.cs_table + row * (a.n_rot >> 1) : nullptr);
     if (a.rope_out) {
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
@@ -459,16 +487,18 @@ unsigned warp_row_grid(int64_t n_rows) { return (unsigned)((n_rows + kRowsPerCta
 
 void rope_rows(const float *x_in, float *x_out, int64_t n_tokens, int n_heads, int head_dim,
                int n_rot, const int32_t *pos, int single_pos, const ds4b200_rope_params &p,
-               int inverse, int unit_rms, float eps, cudaStream_t s, int8_t *xq, float *xscale) {
+               int inverse, int unit_rms, float eps, cudaStream_t s, int8_t *xq, float *xscale,
+               const float *cs_table) {
     const int64_t n_rows = n_tokens * n_heads;
     if (n_rows <= 0 || head_dim <= 0) return;
     const RopeDev d = to_dev(p);
+    const float2 *cs = (n_rot <= 64) ? reinterpret_cast<const float2 *>(cs_table) : nullptr;
     if (xq) {
         // checked by the caller: head_dim % 32 == 0, head_dim <= 1024, n_rot % 4 == 0, 16-byte rows
         const int vpt = ((head_dim >> 2) + 31) / 32;
         const unsigned grid = warp_row_grid(n_rows);
 #define DS4B200_ROPEQ(V) rope_rows_kernel<V, true><<<grid, kRowsPerCta * 32, 0, s>>>( \
-        x_in, x_out, n_rows, n_heads, head_dim, n_rot, pos, single_pos, d, inverse, unit_rms, eps, xq, xscale)
+        x_in, x_out, n_rows, n_heads, head_dim, n_rot, pos, single_pos, d, inverse, unit_rms, eps, xq, xscale, cs)
         if (vpt <= 1) DS4B200_ROPEQ(1);
         else if (vpt <= 2) DS4B200_ROPEQ(2);
         else if (vpt <= 4) DS4B200_ROPEQ(4);
@@ -486,12 +516,21 @@ void rope_rows(const float *x_in, float *x_out, int64_t n_tokens, int n_heads, i
     const int vpt = ((head_dim >> 2) + 31) / 32;
     const unsigned grid = warp_row_grid(n_rows);
 #define DS4B200_ROPE(V) rope_rows_kernel<V, false><<<grid, kRowsPerCta * 32, 0, s>>>( \
-        x_in, x_out, n_rows, n_heads, head_dim, n_rot, pos, single_pos, d, inverse, unit_rms, eps, nullptr, nullptr)
+        x_in, x_out, n_rows, n_heads, head_dim, n_rot, pos, single_pos, d, inverse, unit_rms, eps, nullptr, nullptr, cs)
     if (vpt <= 1) DS4B200_ROPE(1);
     else if (vpt <= 2) DS4B200_ROPE(2);
     else if (vpt <= 4) DS4B200_ROPE(4);
     else DS4B200_ROPE(8);
 #undef DS4B200_ROPE
+}
+
+void rope_table_rows(const int32_t *pos, int64_t n_tokens, int n_rot, const ds4b200_rope_params &p, float *cs_table,
+                     cudaStream_t s) {
+    const int n_pairs = n_rot >> 1;
+    const int64_t n = n_tokens * n_pairs;
+    if (n <= 0) return;
+    rope_table_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(pos, n_tokens, n_pairs, n_rot, to_dev(p),
+                                                                  reinterpret_cast<float2 *>(cs_table));
 }
 
 void fp8_kv_round_trip_rows(const float *kv_in, float *kv_out, int64_t n_rows, int head_dim,
@@ -516,10 +555,12 @@ void fp8_kv_round_trip_rows(const float *kv_in, float *kv_out, int64_t n_rows, i
 void rope_fp8_store_rows(const float *kv_in, int64_t n_rows, int head_dim, int n_rot,
                          const int32_t *pos, const ds4b200_rope_params *p, const float *norm_w,
                          float eps, int scale_mode, const int32_t *slots, uint8_t *codes,
-                         float *scales, float *tail_out, float *rope_out, cudaStream_t s, float *raw_out) {
+                         float *scales, float *tail_out, float *rope_out, cudaStream_t s, float *raw_out,
+                         const float *cs_table) {
     if (n_rows <= 0) return;
     StoreArgs a{};
     a.raw_out = raw_out;
+    a.cs_table = (p && n_rot <= 64) ? reinterpret_cast<const float2 *>(cs_table) : nullptr;
     a.kv_in = kv_in; a.n_rows = n_rows; a.head_dim = head_dim; a.n_rot = n_rot; a.pos = pos;
     a.do_rope = p != nullptr;
     if (p) a.rope = to_dev(*p);

@@ -17,7 +17,7 @@ from ._lib import (FP8_BLOCK64_POW2, FP8_ROW_AMAX, GLU_CLAMP_REF, GLU_CLAMP_SYM,
 __all__ = [
     "FP8_BLOCK64_POW2", "FP8_ROW_AMAX", "GLU_CLAMP_REF", "GLU_CLAMP_SYM", "GLU_PLAIN",
     "TABLE_F16", "TABLE_Q8_0", "RopeParams", "rope_params_for_layer", "rope_params_explicit",
-    "add", "rms_norm_rows", "rms_norm_q8_0_rows", "quantize_q8_0_rows", "quantize_q8_K_rows", "embed_gather_rows", "rope_rows", "rope_q8_0_rows", "fp8_kv_round_trip_rows",
+    "add", "rms_norm_rows", "rms_norm_q8_0_rows", "quantize_q8_0_rows", "quantize_q8_K_rows", "embed_gather_rows", "rope_rows", "rope_table_rows", "rope_q8_0_rows", "fp8_kv_round_trip_rows",
     "rope_fp8_store_rows", "fp8_cache_load_rows", "kv_rows_to_raw", "swa_window_push_rows", "swiglu_rows", "hc_pre_rows", "hc_pre_norm_rows", "output_hc_head_rows", "hc_post_rows", "hc_sinkhorn_rows", "hc_sinkhorn_mix_rows",
     "e4m3_encode", "e4m3_decode", "e4m3_selfcheck", "div_selfcheck", "device_status", "compressor_step", "compressor_chunk", "swiglu_q8_K_rows",
 ]
@@ -118,23 +118,37 @@ def embed_gather_rows(table, table_dtype, ids, n_embd, residual=None, norm_w=Non
     return rows, nf, nb
 
 
-def rope_rows(x, pos, params, n_rot=64, inverse=False, unit_rms=False, eps=1e-6, out=None):
-    """x [T, H, D], pos [T] int32."""
+def rope_rows(x, pos, params, n_rot=64, inverse=False, unit_rms=False, eps=1e-6, out=None, table=None):
+    """x [T, H, D], pos [T] int32; table: rope_table_rows(pos, params), in place of pos + params."""
     T, H, D = x.shape
     out = torch.empty_like(x) if out is None else out
+    if table is not None:
+        check(_lib.load().ds4b200_rope_rows_table_f32(_p(x), _p(out), T, H, D, n_rot, _p(table), int(inverse),
+                                                      int(unit_rms), eps, _s()))
+        return out
     check(_lib.load().ds4b200_rope_rows_f32(_p(x), _p(out), T, H, D, n_rot, _p(pos),
                                             C.byref(params), int(inverse), int(unit_rms), eps, _s()))
     return out
 
 
-def rope_q8_0_rows(x, pos, params, n_rot=64, inverse=False, unit_rms=False, eps=1e-6, want_f32=False):
-    """rope_rows whose result leaves as Q8_0 blocks: (out f32 or None, xq int8 [T, H, D], xscale [T, H, D/32])."""
+def rope_table_rows(pos, params, n_rot=64):
+    """(cos, sin) multipliers of the n_rot/2 tail pairs at every position: [T, n_rot/2, 2]."""
+    T = pos.numel()
+    cs = torch.empty((T, n_rot // 2, 2), dtype=torch.float32, device=pos.device)
+    check(_lib.load().ds4b200_rope_table_rows(_p(pos), C.byref(params), T, n_rot, _p(cs), _s()))
+    return cs
+
+
+def rope_q8_0_rows(x, pos, params, n_rot=64, inverse=False, unit_rms=False, eps=1e-6, want_f32=False, table=None):
+    """rope_rows whose result leaves as Q8_0 blocks: (out f32 or None, xq int8 [T, H, D], xscale [T, H, D/32]).
+    table: rope_table_rows(pos, params), in place of pos + params."""
     T, H, D = x.shape
     out = torch.empty_like(x) if want_f32 else None
     xq = torch.empty((T, H, D), dtype=torch.int8, device=x.device)
     xs = torch.empty((T, H, D // 32), dtype=torch.float32, device=x.device)
     check(_lib.load().ds4b200_rope_q8_0_rows_f32(_p(x), _p(out), _p(xq), _p(xs), T, H, D, n_rot, _p(pos),
-                                                 C.byref(params), int(inverse), int(unit_rms), eps, _s()))
+                                                 None if params is None else C.byref(params), _p(table),
+                                                 int(inverse), int(unit_rms), eps, _s()))
     return out, xq, xs
 
 

@@ -179,16 +179,30 @@ int ds4b200_rope_rows_f32(const float *x_in, float *x_out, int64_t n_tokens, int
                           const ds4b200_rope_params *params, int inverse, int unit_rms,
                           float eps, void *stream);
 
+/* The (cos, sin) multipliers of the n_rot/2 tail pairs of every token, cs_table[t][n_rot/2][2] floats
+ * (n_rot <= 64).  They depend on pos[t] and the parameter set only, yet the reference evaluates them
+ * for every head row (cuda/rope.cu:165-200): per layer 64 query rows, 64 attention-output rows and
+ * the KV row of each token share them.  Computed here once per chunk by the same device code, so a
+ * RoPE entry point given the table produces the same bits as one given pos + params. */
+int ds4b200_rope_table_rows(const int32_t *pos, const ds4b200_rope_params *params, int64_t n_tokens,
+                            int n_rot, float *cs_table, void *stream);
+/* ds4b200_rope_rows_f32 with the table in place of pos + params. */
+int ds4b200_rope_rows_table_f32(const float *x_in, float *x_out, int64_t n_tokens, int n_heads,
+                                int head_dim, int n_rot, const float *cs_table, int inverse,
+                                int unit_rms, float eps, void *stream);
+
 /* The same rotation with the rows leaving as Q8_0 activation blocks, the form the grouped
  * out-projection quantises its input to right behind the inverse RoPE (cuda/forward_layer.cu:1179
  * then cuda/attn_out.cu:119-145): xq int8 [n_tokens][n_heads][head_dim], xscale
  * [n_tokens][n_heads][head_dim/32] (d = amax/127 per 32 values, round to nearest even, clamp to
  * [-128, 127]).  x_out is optional: NULL drops the f32 copy, which is then never written to memory.
+ * cs_table is optional (ds4b200_rope_table_rows); with it pos and params may be NULL.
  * head_dim a multiple of 32 (<= 1024), n_rot a multiple of 4, 16-byte aligned f32 rows. */
 int ds4b200_rope_q8_0_rows_f32(const float *x_in, float *x_out, int8_t *xq, float *xscale,
                                int64_t n_tokens, int n_heads, int head_dim, int n_rot,
-                               const int32_t *pos, const ds4b200_rope_params *params, int inverse,
-                               int unit_rms, float eps, void *stream);
+                               const int32_t *pos, const ds4b200_rope_params *params,
+                               const float *cs_table, int inverse, int unit_rms, float eps,
+                               void *stream);
 
 /* FP8 E4M3FN quantise/dequantise round trip, cuda/fp8_kv.cu:144-195. */
 int ds4b200_fp8_kv_round_trip_rows_f32(const float *kv_in, float *kv_out, int64_t n_rows,

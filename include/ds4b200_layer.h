@@ -90,6 +90,10 @@ typedef struct ds4b200_layer_buffers {      /* caller-owned device workspace for
      * rewritten: ATTN_OUT then reads kqv_q / kqv_scale instead of rotated f32 rows. */
     int8_t *kqv_q;                          /* [T][n_heads][head_dim] */
     float *kqv_scale;                       /* [T][n_heads][head_dim/32] */
+    /* Optional: room for the chunk's RoPE angle table (ds4b200_rope_table_rows).  When given, the
+     * layer fills it once and its three RoPE stages read it instead of evaluating 32 cos / sin pairs
+     * per head row; the rotated rows keep their bits. */
+    float *rope_cs;                         /* [T][n_rot/2][2] */
 } ds4b200_layer_buffers;
 
 /* Called on the issuing thread between row stages; must enqueue its work on `stream` (or

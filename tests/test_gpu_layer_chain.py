@@ -178,7 +178,9 @@ def test_layer_rows_entry_point_sequences_the_same_chain(ops):
     # does not rewrite kqv; everything else is unchanged
     kq = torch.zeros(T, H, hd, dtype=torch.int8, device="cuda")
     ks = torch.zeros(T, H, hd // 32, device="cuda")
-    buffers_q = _lib.LayerBuffers(*[B[nm].data_ptr() for nm in _lib.LayerBuffers.NAMES], kq.data_ptr(), ks.data_ptr())
+    cs = torch.zeros(T, 32, 2, device="cuda")       # and the angle table: same bits in every RoPE stage
+    buffers_q = _lib.LayerBuffers(*[B[nm].data_ptr() for nm in _lib.LayerBuffers.NAMES], kq.data_ptr(), ks.data_ptr(),
+                                  cs.data_ptr())
     out_q = torch.zeros(T, 4, n, device="cuda")
     rc = L.ds4b200_layer_rows_f32(C.byref(dims), C.byref(weights), C.byref(buffers_q), resid_hc.data_ptr(),
                                   pos.data_ptr(), T, out_q.data_ptr(), cb, None, None)
@@ -187,6 +189,8 @@ def test_layer_rows_entry_point_sequences_the_same_chain(ops):
     wq, ws = ops.quantize_q8_0_rows(kqv_back)
     eq(kq.view(-1), wq.view(-1), "inverse RoPE Q8_0 values"); eq(ks.view(-1), ws.view(-1), "inverse RoPE Q8_0 scales")
     eq(B["kqv"], S["kqv"], "kqv left as the attention stage wrote it"); eq(out_q, want, "residual streams (Q8_0 form)")
+    eq(B["q"], q_cur, "q norm + RoPE from the table"); eq(B["raw_rows"], raw, "raw KV rows from the table")
+    eq(cs, ops.rope_table_rows(pos, p), "angle table")
 
     # a hook that fails stops the layer with its code
     bad = _lib.StageHook(lambda user, stage, n_tokens, stream: -7 if stage == _lib.STAGE_Q_B else 0)

@@ -747,6 +747,24 @@ def test_inverse_rope_with_q8_0_output(ops, ref):
         assert_bits(host(xs[t]).ravel(), host(ss), f"token {t}: Q8_0 scales vs the reference's grouped quantiser")
 
 
+@pytest.mark.parametrize("il", [0, 2, 3])
+def test_rope_angle_table_keeps_the_bits(ops, il):
+    """A RoPE kernel given the chunk's angle table produces exactly what it produces from pos + params:
+    forward with q_norm, inverse, and the inverse with Q8_0 output."""
+    g = inputs.rng(990 + il)
+    T, H, D = 9, 64, 512
+    x = dev(inputs.normal(g, (T, H, D), 1.5))
+    pos = dev(np.array([0, 1, 2, 77, 1234, 4095, 4096, 40000, 65535], dtype=np.int32))
+    rp = ops.rope_params_for_layer(il)
+    table = ops.rope_table_rows(pos, rp)
+    assert table.shape == (T, 32, 2)
+    for kw in (dict(unit_rms=True), dict(inverse=True), dict()):
+        assert torch.equal(ops.rope_rows(x, pos, rp, table=table, **kw), ops.rope_rows(x, pos, rp, **kw)), kw
+    a = ops.rope_q8_0_rows(x, pos, rp, inverse=True, want_f32=True)
+    b = ops.rope_q8_0_rows(x, None, None, inverse=True, want_f32=True, table=table)
+    assert all(torch.equal(u, v) for u, v in zip(a, b))
+
+
 def test_reference_kernel_library_present(ref):
     """The bit-for-bit comparisons above need the reference's kernels rebuilt for sm_100a: the `ref`
     fixture fails when the library is missing, and it must load."""
