@@ -318,6 +318,7 @@ def strong_split_leg(args, rank, world, table, weak_value):
     path.close()
     value = args.tokens / (ms_step * 1e-3)
     return {"tokens_per_rank": n, "ms_per_step": ms_step, "value": value, "unit": UNIT,
+            "efficiency_vs_weak": round(value / weak_value, 4),     # weak_value = world x the per-GPU rate at full batches
             "what": f"one {args.tokens}-token batch split into contiguous row ranges, one per rank",
             "bound": "at 512 rows per GPU the three dependent kernels of a layer move 22 us of traffic "
                      "but each launch has a latency floor of a few us: the step is launch/latency bound"
