@@ -443,6 +443,17 @@ def only_ops(tokens):
         return (lambda: ops.rope_fp8_store_rows(kv, pos, rp, N_ROT, ops.FP8_ROW_AMAX, codes, scales, slots=slots)), \
             rows * (KV_DIM * 4 + KV_DIM + 8), "RoPE + E4M3 cache store, 16 rows per token"
 
+    def rope_fp8_store_table():
+        rows = T * 16
+        kv = rnd(rows, KV_DIM, s=1.5)
+        pos = (torch.arange(rows, device=dev, dtype=torch.int32) % 4096).contiguous()
+        slots = torch.arange(rows, device=dev, dtype=torch.int32)
+        codes, scales = torch.zeros(rows, KV_DIM, dtype=torch.uint8, device=dev), torch.zeros(rows, 1, device=dev)
+        table = ops.rope_table_rows(pos, ops.rope_params_explicit(10000.0, 16.0, 4096, N_ROT))
+        return (lambda: ops.rope_fp8_store_rows(kv, None, None, N_ROT, ops.FP8_ROW_AMAX, codes, scales, slots=slots,
+                                                table=table)), \
+            rows * (KV_DIM * 4 + KV_DIM + 8 + N_ROT * 4), "the same, angles from a table (one row of 32 pairs per KV row)"
+
     def swiglu_q8k():
         gate, up = rnd(T, TOP_K, FF_DIM, s=2.0), rnd(T, TOP_K, FF_DIM, s=2.0)
         w = torch.softmax(rnd(T, TOP_K), -1)
@@ -454,7 +465,7 @@ def only_ops(tokens):
         return (lambda: ops.quantize_q8_K_rows(x)), T * TOP_K * (FF_DIM * 4 + FF_DIM + FF_DIM // 256 * 36), "Q8_K activation quantiser"
 
     for f in (hc_pre, hc_post_block, hc_head, rms_norm_cta, rms_norm_q8_0, rms_norm_warp, rope_rows, rope_inverse,
-              rope_inverse_q8_0, rope_inverse_q8_0_table, rope_rows_table, rope_table, fp8_round_trip, rope_fp8_store, swiglu_q8k, quantize_q8_K):
+              rope_inverse_q8_0, rope_inverse_q8_0_table, rope_rows_table, rope_table, fp8_round_trip, rope_fp8_store, rope_fp8_store_table, swiglu_q8k, quantize_q8_K):
         add(f.__name__, f)
     return reg
 

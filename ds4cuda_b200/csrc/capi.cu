@@ -282,6 +282,54 @@ int ds4b200_kv_rows_to_raw_f32(const float *kv_in, int64_t n_rows, int head_dim,
     return launched("kv_rows_to_raw");
 }
 
+// The two KV-row entry points with the chunk's angle table in place of pos + params: cs_table holds one
+// row of n_rot/2 (cos, sin) pairs per input row.
+static ds4b200_rope_params table_only_params() {
+    ds4b200_rope_params p{};
+    p.freq_base = 1.0f;            // marks "rotate"; the angles come from the table
+    return p;
+}
+
+int ds4b200_rope_fp8_store_rows_table(const float *kv_in, int64_t n_rows, int head_dim, int n_rot,
+                                      const float *cs_table, const float *norm_w, float eps, int scale_mode,
+                                      const int32_t *slots, uint8_t *codes, float *scales, float *tail_out,
+                                      float *rope_out, void *stream) {
+    REQUIRE(n_rows >= 0, "rope_fp8_store_rows_table: n_rows < 0");
+    if (n_rows == 0) return 0;
+    REQUIRE(kv_in && codes && scales && cs_table, "rope_fp8_store_rows_table: null pointer");
+    REQUIRE(head_dim > 0 && head_dim <= 1024 && head_dim % 4 == 0,
+            "rope_fp8_store_rows_table: head_dim must be a multiple of 4, at most 1024");
+    REQUIRE(n_rot > 0 && n_rot <= 64 && n_rot <= head_dim && n_rot % 4 == 0,
+            "rope_fp8_store_rows_table: n_rot must be a multiple of 4, at most 64");
+    REQUIRE(scale_mode == DS4B200_FP8_BLOCK64_POW2 || scale_mode == DS4B200_FP8_ROW_AMAX,
+            "rope_fp8_store_rows_table: unknown scale mode");
+    REQUIRE(scale_mode != DS4B200_FP8_BLOCK64_POW2 || ((head_dim - n_rot) % 64 == 0 && n_rot % 64 == 0),
+            "rope_fp8_store_rows_table: BLOCK64_POW2 needs head_dim - n_rot and n_rot multiples of 64");
+    REQUIRE(a16(kv_in) && a16(norm_w) && a16(tail_out) && a16(rope_out) && a4(codes) &&
+                (reinterpret_cast<uintptr_t>(cs_table) & 7u) == 0,
+            "rope_fp8_store_rows_table: kv_in, norm_w, tail_out, rope_out need 16-byte, cs_table 8-byte, codes 4-byte alignment");
+    const ds4b200_rope_params p = table_only_params();
+    ds4b200::rope_fp8_store_rows(kv_in, n_rows, head_dim, n_rot, nullptr, &p, norm_w, eps, scale_mode, slots, codes,
+                                 scales, tail_out, rope_out, STREAM(stream), nullptr, cs_table);
+    return launched("rope_fp8_store_rows_table");
+}
+
+int ds4b200_kv_rows_to_raw_table_f32(const float *kv_in, int64_t n_rows, int head_dim, int n_rot,
+                                     const float *cs_table, const float *norm_w, float eps, const int32_t *slots,
+                                     float *raw_out, void *stream) {
+    REQUIRE(n_rows >= 0, "kv_rows_to_raw_table: n_rows < 0");
+    if (n_rows == 0) return 0;
+    REQUIRE(kv_in && raw_out && cs_table, "kv_rows_to_raw_table: null pointer");
+    REQUIRE(head_dim > 0 && head_dim <= 1024 && head_dim % 64 == 0 && n_rot == 64 && n_rot <= head_dim,
+            "kv_rows_to_raw_table: head_dim must be a multiple of 64, at most 1024, and n_rot 64");
+    REQUIRE(a16(kv_in) && a16(norm_w) && a16(raw_out) && (reinterpret_cast<uintptr_t>(cs_table) & 7u) == 0,
+            "kv_rows_to_raw_table: buffers need 16-byte alignment (cs_table 8)");
+    const ds4b200_rope_params p = table_only_params();
+    ds4b200::rope_fp8_store_rows(kv_in, n_rows, head_dim, n_rot, nullptr, &p, norm_w, eps, DS4B200_FP8_BLOCK64_POW2,
+                                 slots, nullptr, nullptr, nullptr, nullptr, STREAM(stream), raw_out, cs_table);
+    return launched("kv_rows_to_raw_table");
+}
+
 int ds4b200_swa_window_push_rows_f32(float *raw_kv, int cap, int n_raw, const float *new_rows, int n_new,
                                      int head_dim, int *n_raw_after, void *stream) {
     REQUIRE(cap > 0 && n_raw >= 0 && n_raw <= cap && n_new >= 0, "swa_window_push_rows: bad window state");

@@ -119,7 +119,17 @@ __global__ void rms_norm_cta_kernel(NormArgs a) {
     const int64_t row = blockIdx.x;
     float4 v[VPT];
     float ss = load_row<VPT>(a, row, threadIdx.x, blockDim.x, v);
-    ss = block_sum(ss, red);
+    if (blockDim.x == 256) {
+        // one barrier instead of three: every thread adds the eight warp sums itself, in the order the
+        // butterfly of block_sum adds them (same bits)
+        ss = warp_sum(ss);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        ss = __fadd_rn(__fadd_rn(__fadd_rn(red[0], red[4]), __fadd_rn(red[2], red[6])),
+                       __fadd_rn(__fadd_rn(red[1], red[5]), __fadd_rn(red[3], red[7])));
+    } else {
+        ss = block_sum(ss, red);
+    }
     const float scale = rms_scale(ss, (float)a.n, a.eps);
     store_row<VPT>(a, row, threadIdx.x, blockDim.x, v, scale);
 }

@@ -21,21 +21,12 @@ __device__ __forceinline__ uint32_t q8k_pack4(int a, int b, int c, int d) {
 // e[4..7].  Writes qb[256], *scale_b and sums_b[16].
 __device__ __forceinline__ void q8k_block_store(const float (&e)[8], int lane, int8_t *qb, float *scale_b,
                                                 int16_t *sums_b) {
-    // key = magnitude bits in the high word, inverted index in the low word: the maximum key
-    // is the largest magnitude and, among equals, the smallest index
-    unsigned long long key = 0;
+    // largest magnitude of the block
+    const float a_lo = fmaxf(fmaxf(fabsf(e[0]), fabsf(e[1])), fmaxf(fabsf(e[2]), fabsf(e[3])));
+    const float a_hi = fmaxf(fmaxf(fabsf(e[4]), fabsf(e[5])), fmaxf(fabsf(e[6]), fabsf(e[7])));
+    float amax = fmaxf(a_lo, a_hi);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        const uint32_t idx = (k < 4 ? 4 * lane + k : 128 + 4 * lane + (k - 4));
-        const unsigned long long cand = ((unsigned long long)__float_as_uint(fabsf(e[k])) << 32) | (0xffffffffu - idx);
-        key = cand > key ? cand : key;
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-        const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, off);
-        key = other > key ? other : key;
-    }
-    const float amax = __uint_as_float((uint32_t)(key >> 32));
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
     if (amax == 0.0f) {
         reinterpret_cast<uint32_t *>(qb)[lane] = 0u;
         reinterpret_cast<uint32_t *>(qb)[32 + lane] = 0u;
@@ -43,12 +34,18 @@ __device__ __forceinline__ void q8k_block_store(const float (&e)[8], int lane, i
         if (lane == 0) *scale_b = 0.0f;
         return;
     }
-    const uint32_t idx = 0xffffffffu - (uint32_t)key;
-    const int k_own = (idx < 128 ? (int)(idx & 3u) : 4 + (int)(idx & 3u));
-    float mine = e[0];
-#pragma unroll
-    for (int k = 1; k < 8; ++k) mine = (k == k_own) ? e[k] : mine;
-    const float smax = __shfl_sync(0xffffffffu, mine, (int)((idx & 127u) >> 2));
+    // the first element in index order that has it: elements 4l..4l+3 of every lane come before 128+4l..,
+    // so the lowest lane with a hit in its low quad wins, else the lowest lane with one in its high quad
+    const unsigned lo_lanes = __ballot_sync(0xffffffffu, a_lo == amax);
+    const unsigned hi_lanes = __ballot_sync(0xffffffffu, a_hi == amax);
+    const bool in_lo = lo_lanes != 0u;
+    const int src = __ffs(in_lo ? lo_lanes : hi_lanes) - 1;
+    const float c0 = in_lo ? e[0] : e[4], c1 = in_lo ? e[1] : e[5], c2 = in_lo ? e[2] : e[6], c3 = in_lo ? e[3] : e[7];
+    float mine = c3;
+    mine = fabsf(c2) == amax ? c2 : mine;
+    mine = fabsf(c1) == amax ? c1 : mine;
+    mine = fabsf(c0) == amax ? c0 : mine;
+    const float smax = __shfl_sync(0xffffffffu, mine, src);
     const float iscale = -127.0f / smax;
     const uint32_t p0 = q8_pack4_sat(iscale * e[0], iscale * e[1], iscale * e[2], iscale * e[3]);
     const uint32_t p1 = q8_pack4_sat(iscale * e[4], iscale * e[5], iscale * e[6], iscale * e[7]);

@@ -160,9 +160,15 @@ def fp8_kv_round_trip_rows(kv, n_rot=64, out=None):
 
 
 def rope_fp8_store_rows(kv, pos, params, n_rot, scale_mode, codes, scales, slots=None,
-                        norm_w=None, eps=1e-6, tail_out=None, rope_out=None):
-    """Writes into the caller's cache tensors `codes` (uint8) and `scales` (f32)."""
+                        norm_w=None, eps=1e-6, tail_out=None, rope_out=None, table=None):
+    """Writes into the caller's cache tensors `codes` (uint8) and `scales` (f32).  `table` (rope_table_rows,
+    one row per kv row) replaces pos + params."""
     rows, D = kv.shape
+    if table is not None:
+        check(_lib.load().ds4b200_rope_fp8_store_rows_table(
+            _p(kv), rows, D, n_rot, _p(table), _p(norm_w), eps, scale_mode, _p(slots), _p(codes), _p(scales),
+            _p(tail_out), _p(rope_out), _s()))
+        return
     check(_lib.load().ds4b200_rope_fp8_store_rows(
         _p(kv), rows, D, n_rot, _p(pos), None if params is None else C.byref(params), _p(norm_w),
         eps, scale_mode, _p(slots), _p(codes), _p(scales), _p(tail_out), _p(rope_out), _s()))
@@ -177,9 +183,14 @@ def fp8_cache_load_rows(codes, scales, slots, n_rot, scale_mode, tail=None, f16_
     return out
 
 
-def kv_rows_to_raw(kv, pos, params, raw_out, n_rot=64, slots=None, norm_w=None, eps=1e-6):
-    """norm -> RoPE -> FP8 round trip -> f16 round, written to raw_out[slot] (f32 rows)."""
+def kv_rows_to_raw(kv, pos, params, raw_out, n_rot=64, slots=None, norm_w=None, eps=1e-6, table=None):
+    """norm -> RoPE -> FP8 round trip -> f16 round, written to raw_out[slot] (f32 rows).  `table`
+    (rope_table_rows, one row per kv row) replaces pos + params."""
     rows, D = kv.shape
+    if table is not None:
+        check(_lib.load().ds4b200_kv_rows_to_raw_table_f32(_p(kv), rows, D, n_rot, _p(table), _p(norm_w), eps,
+                                                           _p(slots), _p(raw_out), _s()))
+        return raw_out
     check(_lib.load().ds4b200_kv_rows_to_raw_f32(_p(kv), rows, D, n_rot, _p(pos),
                                                  None if params is None else C.byref(params), _p(norm_w), eps,
                                                  _p(slots), _p(raw_out), _s()))

@@ -240,6 +240,17 @@ int ds4b200_kv_rows_to_raw_f32(const float *kv_in, int64_t n_rows, int head_dim,
                                const float *norm_w, float eps, const int32_t *slots,
                                float *raw_out, void *stream);
 
+/* ds4b200_rope_fp8_store_rows and ds4b200_kv_rows_to_raw_f32 with the chunk's angle table
+ * (ds4b200_rope_table_rows; one row of n_rot/2 (cos, sin) pairs per input row, n_rot <= 64) in place of
+ * pos + params: the same bits, without 32 cos / sin evaluations per row. */
+int ds4b200_rope_fp8_store_rows_table(const float *kv_in, int64_t n_rows, int head_dim, int n_rot,
+                                      const float *cs_table, const float *norm_w, float eps, int scale_mode,
+                                      const int32_t *slots, uint8_t *codes, float *scales, float *tail_out,
+                                      float *rope_out, void *stream);
+int ds4b200_kv_rows_to_raw_table_f32(const float *kv_in, int64_t n_rows, int head_dim, int n_rot,
+                                     const float *cs_table, const float *norm_w, float eps, const int32_t *slots,
+                                     float *raw_out, void *stream);
+
 /* Sliding raw-KV window [cap][head_dim] holding n_raw rows: push n_new rows at once
  * (f16-rounded on entry).  Equivalent to n_new single-row pushes of the reference
  * (append while there is room, else shift every row down by one and write last,

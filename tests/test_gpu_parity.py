@@ -65,7 +65,8 @@ def test_add_unaligned_pointers(ops, oracle):
 
 
 @pytest.mark.parametrize("rows,n", [(1, 4096), (1, 1024), (1, 512), (64, 512), (300, 4096), (7, 8192),
-                                    (5, 16384), (3, 100), (2, 7), (513, 128), (9, 1020)])
+                                    (5, 16384), (3, 100), (2, 7), (513, 128), (9, 1020),
+                                    (1500, 4096), (1189, 2048), (2500, 3072)])   # many rows of CTA-wide length
 def test_rms_norm_rows_shapes(ops, oracle, rows, n):
     g = inputs.rng(200 + rows + n)
     x, w = inputs.normal(g, (rows, n)), inputs.uniform(g, (n,), 0.5, 1.5)
@@ -74,9 +75,10 @@ def test_rms_norm_rows_shapes(ops, oracle, rows, n):
     assert_close(host(y), want, what=f"rms_norm {rows}x{n}")
 
 
-def test_rms_norm_weight_modes_and_fused_residual_bf16(ops, oracle):
+@pytest.mark.parametrize("rows", [37, 1300])       # few rows: 1024-thread CTAs; many rows: 256-thread CTAs
+def test_rms_norm_weight_modes_and_fused_residual_bf16(ops, oracle, rows):
     g = inputs.rng(201)
-    rows, n = 37, 4096
+    n = 4096
     x, r = inputs.normal(g, (rows, n)), inputs.normal(g, (rows, n))
     w_shared, w_rows = inputs.uniform(g, (n,), 0.5, 1.5), inputs.uniform(g, (rows, n), 0.5, 1.5)
     for w in (None, w_shared, w_rows):
@@ -312,6 +314,27 @@ def test_fp8_round_trip_bit_exact(ops, oracle, ref, rows):
         r = torch.empty_like(dkv)
         ref.call("fp8_kv_quantize_round_trip_f32", dkv, r, rows, 512, 64)
         assert_bits(host(out), host(r), "fp8 round trip vs reference kernel")
+
+
+def test_fp8_round_trip_block_maxima_at_and_next_to_powers_of_two(ops, oracle, ref):
+    """The block scale is 2^ceil(log2(amax / 448)): block maxima of exactly 448 * 2^k, and one or a few ulps
+    above and below, are where that expression's rounding decides; all must match the reference kernel."""
+    rows = []
+    for k in (-12, -3, 0, 1, 5, 20):
+        base = np.float32(448.0 * 2.0 ** k)
+        for steps in (0, 1, 2, 3, 100, 8191, 8192, 8193, -1, -2, -100):
+            amax = base
+            for _ in range(abs(steps)):
+                amax = np.nextafter(amax, np.float32(np.inf if steps > 0 else 0.0), dtype=np.float32)
+            row = np.linspace(-1.0, 1.0, 512, dtype=np.float32) * amax * np.float32(0.99)
+            row[::64] = amax                              # every 64-block has this maximum
+            rows.append(row)
+    kv = np.stack(rows).astype(np.float32)
+    out = ops.fp8_kv_round_trip_rows(dev(kv))
+    assert_bits(host(out), oracle.fp8_kv_round_trip_rows(kv), "fp8 round trip at scale boundaries vs oracle")
+    r = torch.empty_like(out)
+    ref.call("fp8_kv_quantize_round_trip_f32", dev(kv), r, kv.shape[0], 512, 64)
+    assert_bits(host(out), host(r), "fp8 round trip at scale boundaries vs reference kernel")
 
 
 def test_fp8_round_trip_other_geometries_and_scalar_path(ops, oracle):
@@ -763,6 +786,21 @@ def test_rope_angle_table_keeps_the_bits(ops, il):
     a = ops.rope_q8_0_rows(x, pos, rp, inverse=True, want_f32=True)
     b = ops.rope_q8_0_rows(x, None, None, inverse=True, want_f32=True, table=table)
     assert all(torch.equal(u, v) for u, v in zip(a, b))
+    # the KV row chain and the byte-cache store: one table row per KV row
+    kv, w = dev(inputs.normal(g, (T, D), 1.5)), dev(inputs.uniform(g, (D,), 0.5, 1.5))
+    raw_a, raw_b = torch.zeros(T, D, device="cuda"), torch.zeros(T, D, device="cuda")
+    ops.kv_rows_to_raw(kv, pos, rp, raw_a, norm_w=w)
+    ops.kv_rows_to_raw(kv, None, None, raw_b, norm_w=w, table=table)
+    assert torch.equal(raw_a, raw_b)
+    for mode in (ops.FP8_BLOCK64_POW2, ops.FP8_ROW_AMAX):
+        outs = []
+        for kw in (dict(pos=pos, params=rp), dict(pos=None, params=None, table=table)):
+            codes = torch.zeros(T, D, dtype=torch.uint8, device="cuda")
+            scales, tail = torch.zeros(T, 8, device="cuda"), torch.zeros(T, 64, device="cuda")
+            ops.rope_fp8_store_rows(kv, n_rot=64, scale_mode=mode, codes=codes, scales=scales, norm_w=w,
+                                    tail_out=tail, **kw)
+            outs.append((codes, scales, tail))
+        assert all(torch.equal(u, v) for u, v in zip(*outs)), mode
 
 
 def test_reference_kernel_library_present(ref):
