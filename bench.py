@@ -502,8 +502,12 @@ def measured_peak():
 
 
 def standalone_ops_leg(tokens, peak):
-    """The batched forms the layer chain does not contain, one launch each between L2 flushes: CUDA events
-    on torch's current stream, which is the stream these wrappers launch on; median of 9."""
+    """The batched forms the layer chain does not contain.  Two figures per op, CUDA events on torch's current
+    stream (the stream these wrappers launch on):
+    `us_per_launch`: one launch on its own between L2 flushes, median of 9; it carries the launch latency and
+    the ramp of a cold, empty GPU (about 8 us whatever the op);
+    `us_back_to_back`: several instances of the op on their own buffers (together more than twice the L2)
+    replayed back to back from one CUDA graph, the way a stage runs inside a layer; time per instance."""
     import torch
     flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device="cuda")
     out = {}
@@ -520,6 +524,32 @@ def standalone_ops_leg(tokens, peak):
         gbs = nbytes / us / 1e3
         out[name] = {"us_per_launch": round(us, 1), "algorithmic_bytes": int(nbytes), "gbs": round(gbs, 1),
                      "frac_of_peak": round(gbs / peak, 4), "what": what}
+        # back to back: enough instances that no buffer is still in L2 when its turn comes again
+        n_sets = max(2, min(8, int(300e6 // max(nbytes, 1)) + 2))
+        try:
+            fns = [fn] + [make()[0] for _ in range(n_sets - 1)]
+            for f in fns:
+                f()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for f in fns:
+                    f()
+            graph.replay()
+            torch.cuda.synchronize()
+            rounds = 5
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(rounds):
+                graph.replay()
+            b.record(); torch.cuda.synchronize()
+            us_b2b = a.elapsed_time(b) * 1e3 / (rounds * n_sets)
+            out[name].update({"us_back_to_back": round(us_b2b, 1), "instances": n_sets,
+                              "frac_back_to_back": round(nbytes / us_b2b / 1e3 / peak, 4)})
+            del graph, fns
+        except Exception as e:                                    # noqa: BLE001 — report, keep the single-launch figure
+            out[name]["us_back_to_back"] = None
+            out[name]["back_to_back_error"] = str(e)[:120]
         del fn
         torch.cuda.empty_cache()
     return out
