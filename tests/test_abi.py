@@ -125,6 +125,19 @@ def test_checked_entry_points_reject_bad_arguments_without_a_gpu(lib):
     assert lib.ds4b200_rope_fp8_store_rows(C.c_void_p(0x1004), 2, 512, 64, p, C.byref(rp), None, 1e-6, 1,
                                            None, p, p, None, None, None) == EINVAL
     assert b"alignment" in lib.ds4b200_last_error()
+    # the entry points that take the chunk's angle table in place of pos + params
+    assert lib.ds4b200_rope_table_rows(None, C.byref(rp), 4, 64, p, None) == EINVAL
+    assert lib.ds4b200_rope_rows_table_f32(p, p, 4, 64, 512, 64, None, 0, 0, 1e-6, None) == EINVAL
+    assert lib.ds4b200_rope_q8_0_rows_f32(p, None, p, p, 4, 64, 512, 64, None, None, None, 1, 0, 1e-6, None) == EINVAL
+    assert lib.ds4b200_rope_fp8_store_rows_table(p, 2, 512, 64, None, None, 1e-6, 1, None, p, p, None, None, None) == EINVAL
+    assert lib.ds4b200_rope_fp8_store_rows_table(p, 2, 512, 128, p, None, 1e-6, 1, None, p, p, None, None, None) == EINVAL
+    assert b"at most 64" in lib.ds4b200_last_error()
+    assert lib.ds4b200_rope_fp8_store_rows_table(p, 2, 512, 64, C.c_void_p(0x1004), None, 1e-6, 1, None, p, p, None, None,
+                                                 None) == EINVAL
+    assert b"alignment" in lib.ds4b200_last_error()
+    assert lib.ds4b200_kv_rows_to_raw_table_f32(p, 2, 512, 64, None, None, 1e-6, None, p, None) == EINVAL
+    assert lib.ds4b200_kv_rows_to_raw_table_f32(p, 2, 500, 64, p, None, 1e-6, None, p, None) == EINVAL
+    assert lib.ds4b200_kv_rows_to_raw_table_f32(None, 0, 512, 64, None, None, 1e-6, None, None, None) == 0
     assert lib.ds4b200_swiglu_rows_f32(p, p, None, p, 2, 6, 64, 5, 10.0, 1, 0, None) == EINVAL
     assert lib.ds4b200_hc_pre_rows_f32(p, p, p, p, p, p, p, 2, 4098, 20, 1e-6, None) == EINVAL
     assert lib.ds4b200_hc_pre_rows_f32(p, p, p, p, p, p, p, 2, 4096, 0, 1e-6, None) == EINVAL
