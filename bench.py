@@ -597,8 +597,10 @@ def layer_row_stages_leg(tokens, peak):
     post_a, comb_a, x = stage("hc_attn_pre", lambda: ops.hc_pre_rows(resid_hc, fn_a, scale3, base24))
     stage("attn_norm+q8_0", lambda: ops.rms_norm_q8_0_rows(x, w_n))
     stage("q_a_norm", lambda: ops.rms_norm_rows(q_lora, w_q))
-    stage("kv_norm+rope+fp8+f16", lambda: ops.kv_rows_to_raw(kv_raw, pos, rope, raw_rows, norm_w=w_kv))
-    table = stage("rope_angle_table", lambda: ops.rope_table_rows(pos, rope))
+    # the KV row chain evaluates the 32 angles of its token anyway: it leaves them as the chunk's angle table
+    table = torch.zeros(T, N_ROT // 2, 2, device=dev)
+    stage("kv_norm+rope+fp8+f16+angle_table", lambda: ops.kv_rows_to_raw(kv_raw, pos, rope, raw_rows, norm_w=w_kv,
+                                                                        table_out=table))
     stage("q_norm+rope", lambda: ops.rope_rows(q_raw, None, None, unit_rms=True, out=q_raw, table=table))
     stage("attn_out_inverse_rope+q8_0", lambda: ops.rope_q8_0_rows(kqv, None, None, inverse=True, table=table))
     resid_attn = stage("hc_attn_post", lambda: ops.hc_post_rows(attn_out, resid_hc, post_a, comb_a))

@@ -107,6 +107,7 @@ SIGNATURES = {
     "ds4b200_kv_rows_to_raw_f32": (_I, [_P, _L, _I, _I, _P, _RP, _P, _F, _P, _P, _P]),
     "ds4b200_rope_fp8_store_rows_table": (_I, [_P, _L, _I, _I, _P, _P, _F, _I, _P, _P, _P, _P, _P, _P]),
     "ds4b200_kv_rows_to_raw_table_f32": (_I, [_P, _L, _I, _I, _P, _P, _F, _P, _P, _P]),
+    "ds4b200_kv_rows_to_raw_table_out_f32": (_I, [_P, _L, _I, _I, _P, _RP, _P, _F, _P, _P, _P, _P]),
     "ds4b200_swa_window_push_rows_f32": (_I, [_P, _I, _I, _P, _I, _I, C.POINTER(C.c_int), _P]),
     "ds4b200_swiglu_rows_f32": (_I, [_P, _P, _P, _P, _L, _I, _I, _I, _F, _I, _I, _P]),
     "ds4b200_hc_pre_rows_f32": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _F, _P]),

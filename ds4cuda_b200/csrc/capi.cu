@@ -330,6 +330,22 @@ int ds4b200_kv_rows_to_raw_table_f32(const float *kv_in, int64_t n_rows, int hea
     return launched("kv_rows_to_raw_table");
 }
 
+int ds4b200_kv_rows_to_raw_table_out_f32(const float *kv_in, int64_t n_rows, int head_dim, int n_rot,
+                                         const int32_t *pos, const ds4b200_rope_params *params, const float *norm_w,
+                                         float eps, const int32_t *slots, float *raw_out, float *cs_out, void *stream) {
+    REQUIRE(n_rows >= 0, "kv_rows_to_raw_table_out: n_rows < 0");
+    if (n_rows == 0) return 0;
+    REQUIRE(kv_in && raw_out && pos && params && cs_out, "kv_rows_to_raw_table_out: null pointer");
+    REQUIRE(head_dim > 0 && head_dim <= 1024 && head_dim % 64 == 0 && n_rot == 64 && n_rot <= head_dim,
+            "kv_rows_to_raw_table_out: head_dim must be a multiple of 64, at most 1024, and n_rot 64");
+    REQUIRE(params->theta_scale > 0.0f || params->freq_base > 0.0f, "kv_rows_to_raw_table_out: no theta_scale and no freq_base");
+    REQUIRE(a16(kv_in) && a16(norm_w) && a16(raw_out) && (reinterpret_cast<uintptr_t>(cs_out) & 7u) == 0,
+            "kv_rows_to_raw_table_out: buffers need 16-byte alignment (cs_out 8)");
+    ds4b200::rope_fp8_store_rows(kv_in, n_rows, head_dim, n_rot, pos, params, norm_w, eps, DS4B200_FP8_BLOCK64_POW2,
+                                 slots, nullptr, nullptr, nullptr, nullptr, STREAM(stream), raw_out, nullptr, cs_out);
+    return launched("kv_rows_to_raw_table_out");
+}
+
 int ds4b200_swa_window_push_rows_f32(float *raw_kv, int cap, int n_raw, const float *new_rows, int n_new,
                                      int head_dim, int *n_raw_after, void *stream) {
     REQUIRE(cap > 0 && n_raw >= 0 && n_raw <= cap && n_new >= 0, "swa_window_push_rows: bad window state");

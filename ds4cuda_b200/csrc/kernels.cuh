@@ -54,7 +54,9 @@ void rope_fp8_store_rows(const float *kv_in, int64_t n_rows, int head_dim, int n
                          const int32_t *pos, const ds4b200_rope_params *p, const float *norm_w,
                          float eps, int scale_mode, const int32_t *slots, uint8_t *codes,
                          float *scales, float *tail_out, float *rope_out, cudaStream_t s,
-                         float *raw_out = nullptr, const float *cs_table = nullptr);
+                         float *raw_out = nullptr, const float *cs_table = nullptr, float *cs_out = nullptr);
+// cs_out (n_rot <= 64, one KV row per token, no cs_table): the (cos, sin) pairs this launch evaluates for its rows are
+// also written to cs_out[r][n_rot/2][2], which is then the chunk's angle table for the RoPE launches that follow.
 
 // Read side of the FP8 byte cache: rows at slots[] -> f32 (optionally f16-rounded).
 void fp8_cache_load_rows(const uint8_t *codes, const float *scales, const float *tail, const int32_t *slots,

@@ -50,8 +50,9 @@ extern "C" int ds4b200_layer_rows_f32(const ds4b200_layer_dims *d, const ds4b200
         return rc ? set_error(rc, "layer_rows: hook stage %d returned %d", stage, rc) : 0;
     };
     int rc;
+    // the chunk's angle table: written by the KV row chain below (one KV row per token evaluates exactly the
+    // table's entries), read by the two head-row RoPE stages after it
     const float *cs = (b->rope_cs && d->n_rot <= 64) ? b->rope_cs : nullptr;
-    if (cs) ds4b200::rope_table_rows(pos, T, d->n_rot, rope, b->rope_cs, s);
 
     // ---- attention half
     ds4b200::hc_pre_rows(resid_in, w->hc_attn_fn, w->hc_attn_scale, w->hc_attn_base, b->post, b->comb, b->x, T, n,
@@ -64,7 +65,7 @@ extern "C" int ds4b200_layer_rows_f32(const ds4b200_layer_dims *d, const ds4b200
                            d->eps, s);
     ds4b200::rope_fp8_store_rows(b->kv_raw, T, hd, d->n_rot, pos, &rope, w->kv_a_norm, d->eps,
                                  DS4B200_FP8_BLOCK64_POW2, nullptr, nullptr, nullptr, nullptr, nullptr, s,
-                                 b->raw_rows, cs);
+                                 b->raw_rows, nullptr, cs ? b->rope_cs : nullptr);
     if ((rc = launch_ok("q_a norm / kv chain"))) return rc;
     if ((rc = call(DS4B200_STAGE_Q_B))) return rc;
     ds4b200::rope_rows(b->q, b->q, T, d->n_heads, hd, d->n_rot, pos, 0, rope, 0, 1, d->eps, s, nullptr, nullptr, cs);

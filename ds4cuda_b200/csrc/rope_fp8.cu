@@ -62,10 +62,12 @@ __device__ __forceinline__ void rope_tail_apply(float4 (&v)[VPT], int lane, int 
     }
 }
 
+// cs_save (optional, forward rotation only): the lane's (cos, sin) is also written there, which makes this
+// row's evaluation the chunk's angle table entry (the bits rope_table_kernel would write).
 template <int VPT>
 __device__ __forceinline__ void rope_tail_warp(float4 (&v)[VPT], int lane, int n4, int n_nope, int n_rot,
                                                float posf, const RopeDev &p, bool inverse,
-                                               const float2 *cs_row = nullptr) {
+                                               const float2 *cs_row = nullptr, float2 *cs_save = nullptr) {
     if (n_rot <= 64) {
         float c = 1.0f, sn = 0.0f;
         if (2 * lane < n_rot) {
@@ -78,6 +80,7 @@ __device__ __forceinline__ void rope_tail_warp(float4 (&v)[VPT], int lane, int n
                 float te = posf;
                 for (int k = 0; k < lane; ++k) te *= ts;
                 rope_cs(p, lane, te, inverse, c, sn);
+                if (cs_save) cs_save[lane] = make_float2(c, sn);
             }
         }
         rope_tail_apply<VPT>(v, lane, n4, n_nope, c, sn);
@@ -264,6 +267,7 @@ struct StoreArgs {
     float *rope_out;
     float *raw_out;     // BLOCK64_POW2 only: f16-rounded round-trip row, the raw-KV cache form
     const float2 *cs_table;   // optional [n_rows][n_rot / 2] from rope_table_kernel (replaces pos + rope)
+    float2 *cs_out;           // optional [n_rows][n_rot / 2]: the angles evaluated here become that table
 };
 
 // f32 -> f16 -> f32, the rounding the reference applies when a row enters its raw KV cache
@@ -305,7 +309,8 @@ __global__ void __launch_bounds__(kRowsPerCta * 32) rope_fp8_store_kernel(StoreA
     }
     if (a.do_rope) {                                  // cuda/forward_layer.cu:910 KV RoPE
         if (a.cs_table) rope_tail_apply<VPT>(v, lane, n4, n_nope, cs.x, cs.y);
-        else rope_tail_warp<VPT>(v, lane, n4, n_nope, a.n_rot, (float)a.pos[row], a.rope, false);
+        else rope_tail_warp<VPT>(v, lane, n4, n_nope, a.n_rot, (float)a.pos[row], a.rope, false, nullptr,
+                                 a.cs_out ? a.cs_out + row * (a.n_rot >> 1) : nullptr);
     }
     if (a.rope_out) {
 #pragma unroll
@@ -565,11 +570,12 @@ void rope_fp8_store_rows(const float *kv_in, int64_t n_rows, int head_dim, int n
                          const int32_t *pos, const ds4b200_rope_params *p, const float *norm_w,
                          float eps, int scale_mode, const int32_t *slots, uint8_t *codes,
                          float *scales, float *tail_out, float *rope_out, cudaStream_t s, float *raw_out,
-                         const float *cs_table) {
+                         const float *cs_table, float *cs_out) {
     if (n_rows <= 0) return;
     StoreArgs a{};
     a.raw_out = raw_out;
     a.cs_table = (p && n_rot <= 64) ? reinterpret_cast<const float2 *>(cs_table) : nullptr;
+    a.cs_out = (p && n_rot <= 64 && !cs_table) ? reinterpret_cast<float2 *>(cs_out) : nullptr;
     a.kv_in = kv_in; a.n_rows = n_rows; a.head_dim = head_dim; a.n_rot = n_rot; a.pos = pos;
     a.do_rope = p != nullptr;
     if (p) a.rope = to_dev(*p);

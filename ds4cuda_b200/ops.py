@@ -183,10 +183,15 @@ def fp8_cache_load_rows(codes, scales, slots, n_rot, scale_mode, tail=None, f16_
     return out
 
 
-def kv_rows_to_raw(kv, pos, params, raw_out, n_rot=64, slots=None, norm_w=None, eps=1e-6, table=None):
+def kv_rows_to_raw(kv, pos, params, raw_out, n_rot=64, slots=None, norm_w=None, eps=1e-6, table=None, table_out=None):
     """norm -> RoPE -> FP8 round trip -> f16 round, written to raw_out[slot] (f32 rows).  `table`
-    (rope_table_rows, one row per kv row) replaces pos + params."""
+    (rope_table_rows, one row per kv row) replaces pos + params; `table_out` [rows, n_rot/2, 2] receives the
+    angles this launch evaluates (the chunk's table, for the RoPE launches that follow)."""
     rows, D = kv.shape
+    if table_out is not None:
+        check(_lib.load().ds4b200_kv_rows_to_raw_table_out_f32(_p(kv), rows, D, n_rot, _p(pos), C.byref(params),
+                                                               _p(norm_w), eps, _p(slots), _p(raw_out), _p(table_out), _s()))
+        return raw_out
     if table is not None:
         check(_lib.load().ds4b200_kv_rows_to_raw_table_f32(_p(kv), rows, D, n_rot, _p(table), _p(norm_w), eps,
                                                            _p(slots), _p(raw_out), _s()))

@@ -251,6 +251,13 @@ int ds4b200_kv_rows_to_raw_table_f32(const float *kv_in, int64_t n_rows, int hea
                                      const float *cs_table, const float *norm_w, float eps, const int32_t *slots,
                                      float *raw_out, void *stream);
 
+/* ds4b200_kv_rows_to_raw_f32 that also leaves the chunk's angle table: with one KV row per token the 32
+ * (cos, sin) pairs this launch evaluates per row ARE the table's entries, so cs_out[r][n_rot/2][2] receives them
+ * (the bits ds4b200_rope_table_rows writes) and the head-row RoPE launches that follow take it as cs_table. */
+int ds4b200_kv_rows_to_raw_table_out_f32(const float *kv_in, int64_t n_rows, int head_dim, int n_rot,
+                                         const int32_t *pos, const ds4b200_rope_params *params, const float *norm_w,
+                                         float eps, const int32_t *slots, float *raw_out, float *cs_out, void *stream);
+
 /* Sliding raw-KV window [cap][head_dim] holding n_raw rows: push n_new rows at once
  * (f16-rounded on entry).  Equivalent to n_new single-row pushes of the reference
  * (append while there is room, else shift every row down by one and write last,

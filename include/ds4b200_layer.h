@@ -90,9 +90,10 @@ typedef struct ds4b200_layer_buffers {      /* caller-owned device workspace for
      * rewritten: ATTN_OUT then reads kqv_q / kqv_scale instead of rotated f32 rows. */
     int8_t *kqv_q;                          /* [T][n_heads][head_dim] */
     float *kqv_scale;                       /* [T][n_heads][head_dim/32] */
-    /* Optional: room for the chunk's RoPE angle table (ds4b200_rope_table_rows).  When given, the
-     * layer fills it once and its three RoPE stages read it instead of evaluating 32 cos / sin pairs
-     * per head row; the rotated rows keep their bits. */
+    /* Optional: room for the chunk's RoPE angle table (the entries ds4b200_rope_table_rows writes).
+     * When given, the KV row chain, which evaluates a token's 32 angles anyway, leaves them here, and
+     * the two head-row RoPE stages behind it read them instead of evaluating 32 cos / sin pairs per
+     * head row; the rotated rows keep their bits. */
     float *rope_cs;                         /* [T][n_rot/2][2] */
 } ds4b200_layer_buffers;
 

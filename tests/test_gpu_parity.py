@@ -792,6 +792,10 @@ def test_rope_angle_table_keeps_the_bits(ops, il):
     ops.kv_rows_to_raw(kv, pos, rp, raw_a, norm_w=w)
     ops.kv_rows_to_raw(kv, None, None, raw_b, norm_w=w, table=table)
     assert torch.equal(raw_a, raw_b)
+    # ... and the chain that leaves the table as a by-product writes the same table and the same rows
+    raw_c, table_c = torch.zeros(T, D, device="cuda"), torch.zeros(T, 32, 2, device="cuda")
+    ops.kv_rows_to_raw(kv, pos, rp, raw_c, norm_w=w, table_out=table_c)
+    assert torch.equal(raw_c, raw_a) and torch.equal(table_c, table)
     for mode in (ops.FP8_BLOCK64_POW2, ops.FP8_ROW_AMAX):
         outs = []
         for kw in (dict(pos=pos, params=rp), dict(pos=None, params=None, table=table)):
