@@ -2,8 +2,8 @@
 // per token on the fifth-generation tensor cores (tcgen05, accumulators in tensor memory).
 //
 // Arithmetic: cuda/hc_sinkhorn.cu:85-305 of the reference (RMS over the token's 4*n_embd
-// residual block, 24 dot products with hc_fn, sigmoid gates, weighted stream sum); the Sinkhorn
-// sweeps over the 16 comb values run afterwards in hc_sinkhorn_rows_kernel.
+// residual block, 24 dot products with hc_fn, sigmoid gates, weighted stream sum, Sinkhorn sweeps over
+// the 16 comb values).
 //
 // Shape of the work: per token the step streams 64 KiB once and needs 2*24*16384 flops, 10
 // flop per byte: at the HBM rate that is the whole f32 SIMT peak, and as warp-level MMAs it is
@@ -35,8 +35,9 @@
 //     the token (4 tokens per CTA per step) over distributed shared memory, announced by a
 //     remote mbarrier arrival;
 //   * sixteen warps per CTA finish the CTA's own tokens: add the 32 partial records in a fixed
-//     order, gates, post / comb values, then the weighted stream sum over the whole 4096-wide
-//     row, re-read from L2, where the step's rows still are.
+//     order, gates, post values, then the weighted stream sum over the whole 4096-wide
+//     row, re-read from L2, where the step's rows still are; two of those warps then run the Sinkhorn
+//     sweeps of the step's four tokens, 16 lanes per token.
 // Every residual row crosses HBM once; nothing is reduced across clusters; every sum has a fixed
 // order, so two runs agree bit for bit.
 //
@@ -187,7 +188,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 hc_pre_tc_kernel(const __grid_constant__ CUtensorMap x_map, const float *__restrict__ residual_hc,
                  const uint16_t *__restrict__ hc_fn, const float *__restrict__ hc_scale,
                  const float *__restrict__ hc_base, float *__restrict__ post_out, float *__restrict__ comb_out,
-                 float *__restrict__ out, int64_t n_tokens, float eps, int *status) {
+                 float *__restrict__ out, int64_t n_tokens, int iters, float eps, int *status) {
     constexpr int n_embd = 4096;
     constexpr int64_t hc_dim = 4 * (int64_t)n_embd;
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -203,6 +204,8 @@ hc_pre_tc_kernel(const __grid_constant__ CUtensorMap x_map, const float *__restr
     __shared__ int abort_s;
     __shared__ float tot_s[kTokensPerCta][kRec];
     __shared__ float pre_s[kTokensPerCta][4];
+    __shared__ float comb_s[2][kTokensPerCta][16];           // comb values before the Sinkhorn sweeps, per step parity
+    __shared__ __align__(8) uint64_t comb_ready[2], comb_free[2];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t rank = cluster_rank();
@@ -219,6 +222,7 @@ hc_pre_tc_kernel(const __grid_constant__ CUtensorMap x_map, const float *__restr
             mbar_init(&acc_full[i], 1); mbar_init(&acc_free[i], 4);
             mbar_init(&xch_full[i], kC * 2 * kTokensPerCta); mbar_init(&xch_free[i], kC);
             mbar_init(&ss_ready[i], kPrepGroups * 2);
+            mbar_init(&comb_ready[i], 2); mbar_init(&comb_free[i], 2);
         }
     }
     __syncthreads();
@@ -289,6 +293,24 @@ hc_pre_tc_kernel(const __grid_constant__ CUtensorMap x_map, const float *__restr
                 }
                 mma_commit(&acc_full[buf]);
             }
+        }
+    } else if (warp == 2 || warp == 3) {
+        // ---------------------------------------------------------------- Sinkhorn sweeps, 16 lanes per token
+        // (with the sweeps in two of the finishing warps the call took 133 us instead of 120; here they run
+        // beside everything else)
+        const int m = (warp - 2) * 2 + (lane >> 4), k = lane & 15;
+        for (int it = 0; it < my_steps; ++it) {
+            const int buf = it & 1;
+            const int64_t t = ((int64_t)(first_step + it * step_stride)) * kStepTokens + (int64_t)rank * kTokensPerCta + m;
+            wait_phase(&comb_ready[buf], ((uint32_t)it >> 1) & 1u, abort_flag, status);
+            const float v = comb_s[buf][m][k];
+            // the first shuffles of the sweeps consume v, so the load has returned before the buffer is handed back
+            const float probe = __shfl_sync(0xffffffffu, v, lane ^ 1);
+            __syncwarp();
+            if (lane == 0)     // `probe` as an operand keeps the arrival behind the shuffle in the instruction stream
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(&comb_free[buf])), "f"(probe) : "memory");
+            const float c = sinkhorn_4x4_lanes(v, lane, iters, eps);
+            if (t < n_tokens) comb_out[t * 16 + k] = c;
         }
     } else if (warp >= kPrepWarp0 && warp < kTailWarp0) {
         // ---------------------------------------------------------------- operand writers / accumulator drain
@@ -441,21 +463,26 @@ hc_pre_tc_kernel(const __grid_constant__ CUtensorMap x_map, const float *__restr
             // the exchange buffer has been read: the sources may fill it again
             if (tt < kC) mbar_arrive_remote(map_to_rank(smem_addr(&xch_free[buf]), (uint32_t)tt));
             const int64_t t0 = (int64_t)step * kStepTokens + (int64_t)rank * kTokensPerCta;
+            // warps 16-17: the four tokens' 16 comb values before the Sinkhorn sweeps, handed to warps 2-3 through
+            // shared memory; threads 64-79 the pre gates, 80-95 the post gates
             if (tt < 96) {
-                const int m = tt >= 32 ? (tt - 32) >> 4 : (tt & 15) >> 2;
+                const int m = tt < 64 ? tt >> 4 : (tt & 15) >> 2;
                 const int64_t t = t0 + m;
                 const float rms = rms_scale(tot_s[m][kMixN], (float)hc_dim, eps);
-                if (tt < 16) {
+                if (tt < 64) {
+                    const int k = tt & 15;
+                    wait_phase(&comb_free[buf], (((uint32_t)it >> 1) & 1u) ^ 1u, abort_flag, status);
+                    comb_s[buf][m][k] = (tot_s[m][8 + k] * rms) * hc_scale[2] + hc_base[8 + k];
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&comb_ready[buf]);
+                } else if (tt < 80) {
                     const int h = tt & 3;
                     const float z = (tot_s[m][h] * rms) * hc_scale[0] + hc_base[h];
                     pre_s[m][h] = 1.0f / (1.0f + expf(-z)) + eps;
-                } else if (tt < 32) {
+                } else {
                     const int h = tt & 3;
                     const float z = (tot_s[m][4 + h] * rms) * hc_scale[1] + hc_base[4 + h];
                     if (t < n_tokens) post_out[t * 4 + h] = 2.0f / (1.0f + expf(-z));
-                } else {
-                    const int k = (tt - 32) & 15;
-                    if (t < n_tokens) comb_out[t * 16 + k] = (tot_s[m][8 + k] * rms) * hc_scale[2] + hc_base[8 + k];
                 }
             }
             named_bar(1, kTailThreads);
@@ -467,6 +494,8 @@ hc_pre_tc_kernel(const __grid_constant__ CUtensorMap x_map, const float *__restr
             // pieces go through a four-deep register window: a piece's registers are reloaded with the next
             // token's piece as soon as it has been used, so the loads of one token overlap the arithmetic
             // and the stores of the previous one, and no barrier separates the tokens.
+            // (Requesting a step's first pieces one iteration ahead, before the wait for its partial sums, changed
+            // nothing: these warps wait for the copy-and-MMA pipeline, not the other way round.)
             const float *xrow = residual_hc + t0 * hc_dim + 4 * tt;
             float4 win[4][2];
 #pragma unroll
@@ -580,7 +609,7 @@ const DeviceSetup *device_setup() {
 }
 
 bool launch(const float *residual_hc, const uint16_t *hc_fn, const float *hc_scale, const float *hc_base,
-            float *post, float *comb, float *out, int64_t n_tokens, float eps, cudaStream_t s) {
+            float *post, float *comb, float *out, int64_t n_tokens, int iters, float eps, cudaStream_t s) {
     const DeviceSetup *d = device_setup();
     if (!d || !d->status || d->max_clusters < 1) return false;
     CUtensorMap x_map;
@@ -598,7 +627,7 @@ bool launch(const float *residual_hc, const uint16_t *hc_fn, const float *hc_sca
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     if (cudaLaunchKernelEx(&cfg, hc_pre_tc_kernel, x_map, residual_hc, hc_fn, hc_scale, hc_base, post, comb, out,
-                           n_tokens, eps, d->status) != cudaSuccess) {
+                           n_tokens, iters, eps, d->status) != cudaSuccess) {
         cudaGetLastError();        // the caller falls back to another kernel: do not leave the error behind
         return false;
     }
@@ -610,9 +639,10 @@ bool launch(const float *residual_hc, const uint16_t *hc_fn, const float *hc_sca
 // Returns false when the shape has no variant here or the launch could not be configured
 // (nothing was launched then).
 bool hc_pre_rows_tc(const float *residual_hc, const uint16_t *hc_fn, const float *hc_scale, const float *hc_base,
-                    float *post, float *comb, float *out, int64_t n_tokens, int n_embd, float eps, cudaStream_t s) {
+                    float *post, float *comb, float *out, int64_t n_tokens, int n_embd, int iters, float eps,
+                    cudaStream_t s) {
     if (n_embd != 4096 || !aligned16(residual_hc) || !aligned16(out) || !aligned16(hc_fn)) return false;
-    return launch(residual_hc, hc_fn, hc_scale, hc_base, post, comb, out, n_tokens, eps, s);
+    return launch(residual_hc, hc_fn, hc_scale, hc_base, post, comb, out, n_tokens, iters, eps, s);
 }
 
 }  // namespace ds4b200

@@ -86,7 +86,7 @@ bool hc_pre_rows_mma(const float *residual_hc, const uint16_t *hc_fn, const floa
 
 // tcgen05 variant (n_embd 4096, clusters of 16 CTAs)
 bool hc_pre_rows_tc(const float *residual_hc, const uint16_t *hc_fn, const float *hc_scale, const float *hc_base,
-                    float *post, float *comb, float *out, int64_t n_tokens, int n_embd, float eps, cudaStream_t s);
+                    float *post, float *comb, float *out, int64_t n_tokens, int n_embd, int iters, float eps, cudaStream_t s);
 
 // hc_pre_rows, then RMSNorm(out) * norm_w -> normed (optional) and its Q8_0 blocks xq / xscale (optional).
 void hc_pre_norm_rows(const float *residual_hc, const uint16_t *hc_fn, const float *hc_scale, const float *hc_base,
