@@ -371,7 +371,7 @@ def only_ops(tokens):
         resid, fn = rnd(T, 4, n), (rnd(24, 4 * n) / 128).half()
         sc, base = torch.ones(3, device=dev), torch.zeros(24, device=dev)
         return (lambda: ops.hc_pre_rows(resid, fn, sc, base)), T * (4 * n * 4 + n * 4 + 80) + fn.numel() * 2, \
-            "full HC pre: 24 dots per token on the tensor cores + gates + stream sum + Sinkhorn rows"
+            "full HC pre: 24 dots per token on the tensor cores + gates + stream sum + Sinkhorn sweeps"
 
     def hc_post_block():
         resid, block = rnd(T, 4, n), rnd(T, n)
