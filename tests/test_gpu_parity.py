@@ -572,6 +572,10 @@ def test_hc_post_and_sinkhorn_mix_rows(ops, oracle, ref, n_embd, T):
     wmixed, wcomb = oracle.hc_sinkhorn_mix_rows(logits, resid)
     assert_close(host(gcomb), wcomb, what="sinkhorn comb")
     assert_close(host(mixed), wmixed, what="sinkhorn mix")
+    # the sweeps with 16 lanes per token (the rows kernel, and inside the tensor-core HC pre kernel) against the
+    # sweeps worked through by one thread (the mix launch without a comb buffer): same bits, hence the same mix
+    one_thread = ops.hc_sinkhorn_mix_rows(dev(logits), dev(resid))
+    assert_bits(host(mixed), host(one_thread), "mix from the 16-lane sweeps vs from the one-thread sweeps")
     if ref and n_embd == 4096:
         from ds4cuda_b200 import _lib
         L = _lib.load()
