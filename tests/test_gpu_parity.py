@@ -557,6 +557,27 @@ def test_hc_pre_drop_in_launchers_and_reference_kernels(ops, oracle, ref):
         assert_close(host(out), host(rout), what="out vs reference kernel")
 
 
+def test_hc_pre_tensor_core_kernel_against_the_reference_kernel_token_by_token(ops, ref):
+    """A batch large enough for the tcgen05 kernel (Sinkhorn sweeps included) against the reference's own
+    v2 launcher called once per token on the same rows."""
+    g = inputs.rng(702)
+    n, T = 4096, 130                                       # two full steps of 64 tokens and a ragged third
+    resid = dev(inputs.normal(g, (T, 4, n)))
+    wts = inputs.hc_pre_weights(8, n)
+    fn, scale, base = dev(wts["fn"]), dev(wts["scale"]), dev(wts["base"])
+    post, comb, out = ops.hc_pre_rows(resid, fn, scale, base)
+    rpost, rcomb, rout = torch.empty(T, 4, device="cuda"), torch.empty(T, 16, device="cuda"), torch.empty(T, n, device="cuda")
+    scratch = torch.zeros(32, device="cuda")
+    for t in range(T):
+        ref.call("hc_attn_pre_v2_f32", resid[t], fn, scale, base, rpost[t], rcomb[t], rout[t], n, 4, 20, 1e-6,
+                 scratch, scratch[8:])
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert_close(host(post), host(rpost), what="post vs reference kernel")
+    assert_close(host(comb), host(rcomb), what="comb vs reference kernel")
+    assert_close(host(out), host(rout), what="out vs reference kernel")
+
+
 @pytest.mark.parametrize("n_embd,T", [(4096, 9), (1024, 5), (8192, 2), (100, 4)])
 def test_hc_post_and_sinkhorn_mix_rows(ops, oracle, ref, n_embd, T):
     g = inputs.rng(710 + n_embd)
