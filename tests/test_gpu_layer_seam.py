@@ -283,7 +283,10 @@ def test_batched_layer_with_reference_matvecs_in_the_hook_against_the_reference_
              B["x_norm"][t], ids[t], B["router_w"][t], fused_mid, K, FF, N, NEXP, 10.0, kxq, kxs, kxb)
     torch.cuda.synchronize()
     dots_err = rel_err(snap["mid"][t], fused_mid)
-    assert dots_err <= 1e-6, f"dots + separate SwiGLU tail vs the fused launcher: {dots_err:.3e}"
+    n_diff = int((snap["mid"][t] != fused_mid).sum())
+    print(f"dots + separate SwiGLU tail vs the reference's fused launcher: {n_diff} of {fused_mid.numel()} values differ, "
+          f"max-abs / max {dots_err:.2e}")
+    assert n_diff == 0, f"dots + separate SwiGLU tail vs the fused launcher: {n_diff} values differ, {dots_err:.3e}"
 
     # ------------------------------------------------------------ every stage of every token against the reference's arena
     F32_BAR, LOOSE = 1e-5, 5e-2
