@@ -14,8 +14,8 @@
 // Layout.  A cluster of 16 CTAs splits the 16384 columns of a token row: CTA r owns the
 // contiguous columns [1024 r, 1024 r + 1024) and keeps hc_fn[:, those columns] resident in
 // shared memory as TF32 (f16 is exact in TF32) in the K-major 128-byte-swizzled layout the
-// MMA's B operand wants (32 chunks of 24 rows x 32 columns, 96 KiB).  A step is 64 tokens, a
-// stage 128 of the CTA's columns.
+// MMA's B operand wants (32 chunks of 24 rows x 32 columns, 96 KiB).  A step is 64 tokens (the last
+// one of a cluster may be shorter, so that the clusters finish together), a stage 128 of the CTA's columns.
 //   * one thread streams the stages into a 3-slot ring with tiled TMA loads (no cluster
 //     broadcast): a box of 132 columns x 64 tokens lands as rows of 528 bytes, the 16 bytes of
 //     padding keep row-per-thread reads off each other's banks;
@@ -185,7 +185,8 @@ __device__ __forceinline__ bool wait_phase_tight(uint64_t *bar, uint32_t parity,
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
-hc_pre_tc_kernel(const __grid_constant__ CUtensorMap x_map, const float *__restrict__ residual_hc,
+hc_pre_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap x_map16,
+                 const float *__restrict__ residual_hc,
                  const uint16_t *__restrict__ hc_fn, const float *__restrict__ hc_scale,
                  const float *__restrict__ hc_base, float *__restrict__ post_out, float *__restrict__ comb_out,
                  float *__restrict__ out, int64_t n_tokens, int iters, float eps, int *status) {
@@ -209,9 +210,19 @@ hc_pre_tc_kernel(const __grid_constant__ CUtensorMap x_map, const float *__restr
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t rank = cluster_rank();
-    const int n_steps = (int)((n_tokens + kStepTokens - 1) / kStepTokens);
+    // Schedule.  `rounds` full steps of 64 tokens per cluster, taken round robin; what is left (fewer than
+    // 64 tokens per cluster) is split evenly over the clusters in multiples of 16 tokens and handled as one
+    // last, shorter step each (16-token boxes), so no cluster runs a whole extra step while the others idle.
     const int first_step = (int)cluster_id(), step_stride = (int)n_clusters();
-    const int my_steps = first_step < n_steps ? (n_steps - first_step + step_stride - 1) / step_stride : 0;
+    const int rounds = (int)(n_tokens / ((int64_t)kStepTokens * step_stride));
+    const int64_t tail_first = (int64_t)rounds * step_stride * kStepTokens;
+    const int64_t tail_all = n_tokens - tail_first;                       // < 64 * clusters
+    const int tail_share = tail_all > 0 ? (int)(((tail_all + step_stride - 1) / step_stride + 15) / 16) * 16 : 0;
+    const int64_t tail_base = tail_first + (int64_t)first_step * tail_share;
+    const int tail_count = tail_base < n_tokens ? tail_share : 0;         // tokens past n_tokens are masked below
+    const int my_steps = rounds + (tail_count > 0 ? 1 : 0);
+#define DS4B200_STEP_BASE(it) ((it) < rounds ? ((int64_t)first_step + (int64_t)(it) * step_stride) * kStepTokens : tail_base)
+#define DS4B200_STEP_COUNT(it) ((it) < rounds ? kStepTokens : tail_count)
     volatile int *abort_flag = &abort_s;
 
     if (tid == 0) {
@@ -255,13 +266,20 @@ hc_pre_tc_kernel(const __grid_constant__ CUtensorMap x_map, const float *__restr
         if (lane == 0) {
             int slot = 0;
             uint32_t use_parity = 1;                     // a fresh barrier passes a wait on parity 1
-            int step = first_step, sg = 0;
+            int it = 0, sg = 0;
             for (int n = 0; n < total_stages; ++n) {
                 wait_phase_tight(&slot_free[slot], use_parity, abort_flag, status);
-                mbar_arrive_expect_tx(&full[slot], kSlotBytes);
-                tma_load_2d(ring + slot * kSlotBytes, &x_map, (int)(rank * kColsPerCta + sg * kStageCols), step * kStepTokens, &full[slot]);
+                const int col = (int)(rank * kColsPerCta + sg * kStageCols);
+                if (it < rounds) {
+                    mbar_arrive_expect_tx(&full[slot], kSlotBytes);
+                    tma_load_2d(ring + slot * kSlotBytes, &x_map, col, (int)DS4B200_STEP_BASE(it), &full[slot]);
+                } else {                                 // the short last step: 16 tokens per box
+                    mbar_arrive_expect_tx(&full[slot], (uint32_t)(tail_count * kRowBytes));
+                    for (int j = 0; j < tail_count; j += 16)
+                        tma_load_2d(ring + slot * kSlotBytes + j * kRowBytes, &x_map16, col, (int)(tail_base + j), &full[slot]);
+                }
                 if (++slot == kSlots) { slot = 0; use_parity ^= 1u; }
-                if (++sg == kStages) { sg = 0; step += step_stride; }
+                if (++sg == kStages) { sg = 0; ++it; }
             }
         }
     } else if (warp == 1) {
@@ -301,7 +319,8 @@ hc_pre_tc_kernel(const __grid_constant__ CUtensorMap x_map, const float *__restr
         const int m = (warp - 2) * 2 + (lane >> 4), k = lane & 15;
         for (int it = 0; it < my_steps; ++it) {
             const int buf = it & 1;
-            const int64_t t = ((int64_t)(first_step + it * step_stride)) * kStepTokens + (int64_t)rank * kTokensPerCta + m;
+            const int in_step = (int)rank * kTokensPerCta + m;                 // this token's index within the step
+            const int64_t t = in_step < DS4B200_STEP_COUNT(it) ? DS4B200_STEP_BASE(it) + in_step : n_tokens;
             wait_phase(&comb_ready[buf], ((uint32_t)it >> 1) & 1u, abort_flag, status);
             const float v = comb_s[buf][m][k];
             // the first shuffles of the sweeps consume v, so the load has returned before the buffer is handed back
@@ -443,7 +462,6 @@ hc_pre_tc_kernel(const __grid_constant__ CUtensorMap x_map, const float *__restr
         // ---------------------------------------------------------------- the CTA's own tokens
         const int tt = tid - kTailWarp0 * 32;
         for (int it = 0; it < my_steps; ++it) {
-            const int step = first_step + it * step_stride;
             const int buf = it & 1;
             // one thread watches the exchange buffer fill; the others sleep in the hardware barrier
             if (tt == 0) wait_phase(&xch_full[buf], ((uint32_t)it >> 1) & 1u, abort_flag, status, true);
@@ -462,7 +480,10 @@ hc_pre_tc_kernel(const __grid_constant__ CUtensorMap x_map, const float *__restr
             named_bar(1, kTailThreads);
             // the exchange buffer has been read: the sources may fill it again
             if (tt < kC) mbar_arrive_remote(map_to_rank(smem_addr(&xch_free[buf]), (uint32_t)tt));
-            const int64_t t0 = (int64_t)step * kStepTokens + (int64_t)rank * kTokensPerCta;
+            // this CTA's four tokens of the step; in the short last step the ranks past its end have none
+            // (their t0 is then n_tokens, which every guard below treats as "no token")
+            const int64_t t0 = (int)rank * kTokensPerCta < DS4B200_STEP_COUNT(it)
+                                   ? DS4B200_STEP_BASE(it) + (int64_t)rank * kTokensPerCta : n_tokens;
             // warps 16-17: the four tokens' 16 comb values before the Sinkhorn sweeps, handed to warps 2-3 through
             // shared memory; threads 64-79 the pre gates, 80-95 the post gates
             if (tt < 96) {
@@ -532,6 +553,8 @@ hc_pre_tc_kernel(const __grid_constant__ CUtensorMap x_map, const float *__restr
             }
         }
     }
+#undef DS4B200_STEP_BASE
+#undef DS4B200_STEP_COUNT
     // nobody leaves while a peer may still write into its shared memory
     tc_fence_before();
     __syncthreads();
@@ -542,11 +565,11 @@ hc_pre_tc_kernel(const __grid_constant__ CUtensorMap x_map, const float *__restr
     }
 }
 
-// The residual block as a 2-D tensor {16384 columns, T tokens}.  A box of 132 columns x 64 tokens lands
-// as 64 rows of 528 bytes: the stage's 128 columns plus one 16-byte unit of padding (the next columns,
+// The residual block as a 2-D tensor {16384 columns, T tokens}.  A box of 132 columns x 64 tokens (16 for the
+// short last step) lands as rows of 528 bytes: the stage's 128 columns plus one 16-byte unit of padding (the next columns,
 // or zero fill past the end of the row), which keeps the row-per-thread reads of the operand writers
 // free of bank conflicts.  Rows past the end of the batch are zero-filled by the copy.
-bool encode_rows_map(CUtensorMap *map, const float *residual_hc, int64_t n_tokens) {
+bool encode_rows_map(CUtensorMap *map, const float *residual_hc, int64_t n_tokens, int box_tokens) {
     using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -564,7 +587,7 @@ bool encode_rows_map(CUtensorMap *map, const float *residual_hc, int64_t n_token
     if (!encode) return false;
     const cuuint64_t dims[2] = {16384, (cuuint64_t)n_tokens};
     const cuuint64_t strides[1] = {65536};
-    const cuuint32_t box[2] = {kRowBytes / 4, kStepTokens};
+    const cuuint32_t box[2] = {kRowBytes / 4, (cuuint32_t)box_tokens};
     const cuuint32_t elem[2] = {1, 1};
     return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(residual_hc), dims, strides, box, elem,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -612,10 +635,12 @@ bool launch(const float *residual_hc, const uint16_t *hc_fn, const float *hc_sca
             float *post, float *comb, float *out, int64_t n_tokens, int iters, float eps, cudaStream_t s) {
     const DeviceSetup *d = device_setup();
     if (!d || !d->status || d->max_clusters < 1) return false;
-    CUtensorMap x_map;
-    if (!encode_rows_map(&x_map, residual_hc, n_tokens)) return false;
-    const int64_t n_steps = (n_tokens + kStepTokens - 1) / kStepTokens;
-    const int64_t clusters = n_steps < d->max_clusters ? n_steps : d->max_clusters;
+    CUtensorMap x_map, x_map16;
+    if (!encode_rows_map(&x_map, residual_hc, n_tokens, kStepTokens) || !encode_rows_map(&x_map16, residual_hc, n_tokens, 16))
+        return false;
+    // as many clusters as fit, unless the batch is so small that 16 tokens each need fewer
+    const int64_t n_groups16 = (n_tokens + 15) / 16;
+    const int64_t clusters = n_groups16 < d->max_clusters ? n_groups16 : d->max_clusters;
     cudaLaunchConfig_t cfg{};
     cudaLaunchAttribute attr{};
     attr.id = cudaLaunchAttributeClusterDimension;
@@ -626,7 +651,7 @@ bool launch(const float *residual_hc, const uint16_t *hc_fn, const float *hc_sca
     cfg.stream = s;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, hc_pre_tc_kernel, x_map, residual_hc, hc_fn, hc_scale, hc_base, post, comb, out,
+    if (cudaLaunchKernelEx(&cfg, hc_pre_tc_kernel, x_map, x_map16, residual_hc, hc_fn, hc_scale, hc_base, post, comb, out,
                            n_tokens, iters, eps, d->status) != cudaSuccess) {
         cudaGetLastError();        // the caller falls back to another kernel: do not leave the error behind
         return false;

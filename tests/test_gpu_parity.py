@@ -480,11 +480,14 @@ def test_hc_pre_rows(ops, oracle, n_embd, T):
     assert_close(host(out), wout, what="hc_pre out")
 
 
-@pytest.mark.parametrize("T", [65, 449, 1000, 1344])
+@pytest.mark.parametrize("T", [65, 120, 449, 1000, 1344, 1423])
 def test_hc_pre_rows_token_batches_on_the_tensor_cores(ops, oracle, T):
-    """More than 64 tokens of width 4096 take the tcgen05 kernel: a step is 64 tokens per cluster, so these
-    sizes cover one to three steps per cluster, a ragged last step, and the double-buffered accumulators
-    and exchange buffers coming round again.  Two runs must agree bit for bit (fixed summation orders)."""
+    """More than 64 tokens of width 4096 take the tcgen05 kernel: full steps of 64 tokens per cluster, round
+    robin, and what is left split evenly over the clusters as one shorter last step each (multiples of 16
+    tokens).  The sizes cover: only a short step (65; 120 leaves some clusters without any token), full steps
+    followed by a short one that is ragged at the end (449, 1000, 1423), full rounds only (1344 = 3 x 7 x 64 on
+    seven clusters), and the double-buffered accumulators and exchange buffers coming round again.  Two runs
+    must agree bit for bit (fixed summation orders)."""
     g = inputs.rng(7100 + T)
     resid = inputs.normal(g, (T, 4, 4096))
     wts = inputs.hc_pre_weights(6, 4096)
