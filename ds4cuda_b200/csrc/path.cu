@@ -372,19 +372,40 @@ int ds4b200_path_run_host_chunked(ds4b200_path *p, const ds4b200_path_io *h, int
 #define D2H(host, dev, off, cnt, esz) \
     if (host) CUDA_OK(cudaMemcpyAsync((char *)(host) + (off) * (esz), (const char *)(dev) + (off) * (esz), \
                                       (size_t)((cnt) * (esz)), cudaMemcpyDeviceToHost, out), "path_run_host_chunked: D2H")
+    // Slice boundaries.  The first slice's copy-in and the last slice's compute and copy-out overlap with
+    // nothing, so those two slices are half as long as the others (with four slices or more; a second,
+    // finer step of the ramp measured the same).
+    std::vector<int64_t> bound(n_chunks + 1);
+    {
+        auto weight = [&](int k) { return (n_chunks >= 4 && (k == 0 || k == n_chunks - 1)) ? 0.5 : 1.0; };
+        double total_w = 0.0;
+        for (int k = 0; k < n_chunks; ++k) total_w += weight(k);
+        double acc = 0.0;
+        bound[0] = 0;
+        for (int k = 0; k < n_chunks; ++k) {
+            acc += weight(k);
+            int64_t b = (int64_t)(T * (acc / total_w) + 0.5);
+            if (b <= bound[k]) b = bound[k] + 1;             // every slice has at least one row
+            if (b > T - (n_chunks - 1 - k)) b = T - (n_chunks - 1 - k);
+            bound[k + 1] = b;
+        }
+        bound[n_chunks] = T;
+    }
+    // The small per-token inputs go over once, whole: per copy the engine pays about 10 us whatever the size,
+    // and per slice that was six such copies.
+    H2D(p->norm_w, h->norm_w, 0, E, 4);
+    H2D(p->ids, h->ids, 0, T, 4);
+    H2D(p->pos, h->pos, 0, T, 4);
+    H2D(p->router_w, h->router_w, 0, T * c.top_k, 4);
+    H2D(p->hc_logits, h->hc_logits, 0, T * 16, 4);
     for (int k = 0; k < n_chunks; ++k) {
-        const int64_t t0 = T * k / n_chunks, n = T * (k + 1) / n_chunks - t0;
+        const int64_t t0 = bound[k], n = bound[k + 1] - t0;
         cudaEvent_t in_ready = p->chunk_events[2 * k], done = p->chunk_events[2 * k + 1];
         // ---- inputs of this chunk, on the copy-in stream
-        if (k == 0) H2D(p->norm_w, h->norm_w, 0, E, 4);
-        H2D(p->ids, h->ids, t0, n, 4);
-        H2D(p->pos, h->pos, t0, n, 4);
         H2D(p->residual, h->residual, t0 * E, n * E, 4);
         H2D(p->kv, h->kv, t0 * c.kv_dim, n * c.kv_dim, 4);
         H2D(p->gate, h->gate, t0 * c.top_k * c.ff_dim, n * c.top_k * c.ff_dim, 4);
         H2D(p->up, h->up, t0 * c.top_k * c.ff_dim, n * c.top_k * c.ff_dim, 4);
-        H2D(p->router_w, h->router_w, t0 * c.top_k, n * c.top_k, 4);
-        H2D(p->hc_logits, h->hc_logits, t0 * 16, n * 16, 4);
         H2D(p->hc_a, h->hc_resid, t0 * 4 * E, n * 4 * E, 4);
         CUDA_OK(cudaEventRecord(in_ready, in), "path_run_host_chunked: event");
         // ---- the layer chain over this chunk's rows
