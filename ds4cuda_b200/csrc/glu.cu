@@ -173,7 +173,8 @@ __global__ void swiglu_scalar_kernel(const float *gate, const float *up, const f
 }
 
 // Counts (n, d) pairs, d in [1, 2], n spread over +-2^-40..2^40 and signs, for which
-// div_by_1to2 differs from the IEEE division, plus (a, b) pairs for which div_with_rcp does.
+// div_by_1to2 differs from the IEEE division, plus (a, b) pairs for which div_with_rcp does, plus block
+// maxima for which q8_0_block_scale differs from amax / 127 and its IEEE reciprocal.
 // Pairs come from a counter-based hash.
 __global__ void div_selfcheck_kernel(uint64_t first, uint64_t count, unsigned long long *mismatches) {
     unsigned bad = 0;
@@ -195,6 +196,14 @@ __global__ void div_selfcheck_kernel(uint64_t first, uint64_t count, unsigned lo
                                          (uint32_t)((z >> 9) & 0x7fffffu));
         const float a = qt * b;
         bad += (__float_as_uint(div_with_rcp(a, b, 1.0f / b)) != __float_as_uint(a / b));
+        // the Q8_0 block scale and its reciprocal against the plain IEEE expressions (cuda/dense_q8.cu:140-143):
+        // every mantissa at the exponents 2^-99 .. 2^126, taken in turn (2^31 counters cover them all)
+        const uint64_t kk = first + k;
+        const float amax = __uint_as_float(((28u + (uint32_t)((kk >> 23) % 226u)) << 23) | (uint32_t)(kk & 0x7fffffu));
+        float sd, sid;
+        q8_0_block_scale(amax, sd, sid);
+        const float want_d = amax / 127.0f;
+        bad += (__float_as_uint(sd) != __float_as_uint(want_d)) + (__float_as_uint(sid) != __float_as_uint(1.0f / want_d));
     }
     bad = __reduce_add_sync(0xffffffffu, bad);
     if ((threadIdx.x & 31) == 0 && bad) atomicAdd(mismatches, (unsigned long long)bad);

@@ -444,8 +444,11 @@ def test_swiglu_rows(ops, oracle, mode, k, n):
     assert_close(host(fast), oracle.swiglu_rows(gate, up, w, om, 10.0, True), what="fast-exp variant")
 
 
-def test_swiglu_division_is_the_ieee_quotient(ops):
-    # 2^31 hashed (numerator, divisor in [1, 2]) pairs: the branch-free division must give n / d bit for bit
+def test_branch_free_divisions_are_the_ieee_quotients(ops):
+    """2^31 counters: hashed (numerator, divisor in [1, 2]) pairs for the SwiGLU division, hashed pairs for the
+    shared-reciprocal division of the FP8 row quantiser, and for the Q8_0 block scale every mantissa at each of
+    the exponents 2^-99 .. 2^126 (amax / 127 through the reciprocal of 127 with an exact correction, and its
+    reciprocal through one Newton step): all must equal the plain IEEE expressions bit for bit."""
     assert ops.div_selfcheck(0, 1 << 31) == 0
 
 
