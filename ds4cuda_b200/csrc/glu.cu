@@ -174,7 +174,8 @@ __global__ void swiglu_scalar_kernel(const float *gate, const float *up, const f
 
 // Counts (n, d) pairs, d in [1, 2], n spread over +-2^-40..2^40 and signs, for which
 // div_by_1to2 differs from the IEEE division, plus (a, b) pairs for which div_with_rcp does, plus block
-// maxima for which q8_0_block_scale differs from amax / 127 and its IEEE reciprocal.
+// maxima for which q8_0_block_scale differs from amax / 127 and its IEEE reciprocal, or q8k_block_scale from
+// -127 / max and its IEEE reciprocal.
 // Pairs come from a counter-based hash.
 __global__ void div_selfcheck_kernel(uint64_t first, uint64_t count, unsigned long long *mismatches) {
     unsigned bad = 0;
@@ -204,6 +205,15 @@ __global__ void div_selfcheck_kernel(uint64_t first, uint64_t count, unsigned lo
         q8_0_block_scale(amax, sd, sid);
         const float want_d = amax / 127.0f;
         bad += (__float_as_uint(sd) != __float_as_uint(want_d)) + (__float_as_uint(sid) != __float_as_uint(1.0f / want_d));
+        // the Q8_K block scale, both signs of the same maxima
+#pragma unroll
+        for (int sgn = 0; sgn < 2; ++sgn) {
+            const float smax = sgn ? -amax : amax;
+            float is, dq;
+            q8k_block_scale(smax, is, dq);
+            const float want_is = -127.0f / smax;
+            bad += (__float_as_uint(is) != __float_as_uint(want_is)) + (__float_as_uint(dq) != __float_as_uint(1.0f / want_is));
+        }
     }
     bad = __reduce_add_sync(0xffffffffu, bad);
     if ((threadIdx.x & 31) == 0 && bad) atomicAdd(mismatches, (unsigned long long)bad);

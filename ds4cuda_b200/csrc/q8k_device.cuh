@@ -17,6 +17,20 @@ __device__ __forceinline__ uint32_t q8k_pack4(int a, int b, int c, int d) {
            ((uint32_t)(d & 0xff) << 24);
 }
 
+// iscale = -127 / max and d = 1 / iscale as the IEEE quotients (cuda/moe_iq2_pair.cu:196-206), branch-free for
+// maxima between 1e-30 and 1e30 in magnitude: reciprocal by one Newton step, quotient with an exact residual
+// correction (both checked against the plain expressions for every mantissa in that range).
+__device__ __forceinline__ void q8k_block_scale(float smax, float &iscale, float &d) {
+    const float as = fabsf(smax);
+    if (as > 1.0e-30f && as < 1.0e30f) {
+        iscale = div_with_rcp(-127.0f, smax, rcp_newton(smax));
+        d = rcp_newton(iscale);
+    } else {
+        iscale = -127.0f / smax;
+        d = 1.0f / iscale;
+    }
+}
+
 // One warp, one block: lane l holds elements 4l..4l+3 in e[0..3] and 128+4l..128+4l+3 in
 // e[4..7].  Writes qb[256], *scale_b and sums_b[16].
 __device__ __forceinline__ void q8k_block_store(const float (&e)[8], int lane, int8_t *qb, float *scale_b,
@@ -46,7 +60,8 @@ __device__ __forceinline__ void q8k_block_store(const float (&e)[8], int lane, i
     mine = fabsf(c1) == amax ? c1 : mine;
     mine = fabsf(c0) == amax ? c0 : mine;
     const float smax = __shfl_sync(0xffffffffu, mine, src);
-    const float iscale = -127.0f / smax;
+    float iscale, dq;
+    q8k_block_scale(smax, iscale, dq);
     const uint32_t p0 = q8_pack4_sat(iscale * e[0], iscale * e[1], iscale * e[2], iscale * e[3]);
     const uint32_t p1 = q8_pack4_sat(iscale * e[4], iscale * e[5], iscale * e[6], iscale * e[7]);
     reinterpret_cast<uint32_t *>(qb)[lane] = p0;
@@ -59,7 +74,7 @@ __device__ __forceinline__ void q8k_block_store(const float (&e)[8], int lane, i
         sums_b[lane >> 2] = (int16_t)s0;
         sums_b[8 + (lane >> 2)] = (int16_t)s1;
     }
-    if (lane == 0) *scale_b = 1.0f / iscale;
+    if (lane == 0) *scale_b = dq;
 }
 
 }  // namespace ds4b200
