@@ -55,7 +55,7 @@ class LayerBuffers(C.Structure):
     NAMES = ("x", "x_norm", "xq", "xscale", "q_lora", "q_lora_norm", "kv_raw", "raw_rows", "q", "kqv", "attn_out",
              "post", "comb", "resid_mid", "sh_gate", "sh_up", "sh_mid", "gate", "up", "router_w", "mid_q",
              "mid_scale", "mid_bsums", "moe_out", "shexp_out")
-    OPTIONAL = ("kqv_q", "kqv_scale", "rope_cs")
+    OPTIONAL = ("kqv_q", "kqv_scale", "rope_cs", "ffn_kq", "ffn_kscale", "ffn_kbsums")
     _fields_ = [(n, C.c_void_p) for n in NAMES + OPTIONAL]
 
 
@@ -94,6 +94,7 @@ SIGNATURES = {
     "ds4b200_add_f32": (_I, [_P, _P, _P, _L, _P]),
     "ds4b200_rms_norm_rows_f32": (_I, [_P, _P, _P, _L, _P, _P, _P, _L, _I, _F, _P]),
     "ds4b200_rms_norm_q8_0_rows_f32": (_I, [_P, _P, _P, _L, _P, _P, _P, _P, _L, _I, _F, _P]),
+    "ds4b200_rms_norm_q8_K_rows_f32": (_I, [_P, _P, _P, _L, _P, _P, _P, _P, _P, _P, _P, _L, _I, _F, _P]),
     "ds4b200_quantize_q8_0_rows_f32": (_I, [_P, _P, _P, _L, _P]),
     "ds4b200_quantize_q8_K_rows_f32": (_I, [_P, _P, _P, _P, _L, _P]),
     "ds4b200_embed_gather_rows": (_I, [_P, _I, _P, _L, _I, _P, _P, _F, _P, _I, _P, _P, _P]),

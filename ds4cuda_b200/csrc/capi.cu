@@ -103,6 +103,28 @@ int ds4b200_rms_norm_q8_0_rows_f32(const float *x, const float *residual_in, con
     return launched("rms_norm_q8_0_rows");
 }
 
+int ds4b200_rms_norm_q8_K_rows_f32(const float *x, const float *residual_in, const float *w,
+                                   int64_t weight_dim, float *y_f32, float *residual_out, int8_t *xq,
+                                   float *xscale, int8_t *kq, float *kscale, int16_t *kbsums, int64_t n_rows,
+                                   int n, float eps, void *stream) {
+    REQUIRE(n_rows >= 0 && n >= 0, "rms_norm_q8_K_rows: negative size");
+    if (n_rows == 0 || n == 0) return 0;
+    REQUIRE(n_rows < ((int64_t)1 << 31), "rms_norm_q8_K_rows: n_rows >= 2^31");
+    REQUIRE(x && kq && kscale && kbsums, "rms_norm_q8_K_rows: null pointer");
+    REQUIRE(!xq == !xscale, "rms_norm_q8_K_rows: xq and xscale go together");
+    REQUIRE(n % 256 == 0 && n <= 8192, "rms_norm_q8_K_rows: n must be a multiple of 256, at most 8192");
+    REQUIRE(weight_dim == 0 || weight_dim == n || weight_dim == (int64_t)n * n_rows,
+            "rms_norm_q8_K_rows: weight_dim must be 0, n or n*n_rows");
+    REQUIRE(weight_dim == 0 || w, "rms_norm_q8_K_rows: w is null");
+    REQUIRE(!residual_out || residual_in, "rms_norm_q8_K_rows: residual_out without residual_in");
+    REQUIRE(a16(x) && a16(residual_in) && a16(w) && a16(y_f32) && a16(residual_out) && a4(xq) && a4(kq) &&
+                (reinterpret_cast<uintptr_t>(kbsums) & 1u) == 0,
+            "rms_norm_q8_K_rows: f32 buffers need 16-byte, xq / kq 4-byte and kbsums 2-byte alignment");
+    ds4b200::rms_norm_rows(x, residual_in, w, weight_dim, y_f32, nullptr, residual_out, n_rows, n, eps,
+                           STREAM(stream), xq, xscale, kq, kscale, kbsums);
+    return launched("rms_norm_q8_K_rows");
+}
+
 int ds4b200_quantize_q8_0_rows_f32(const float *x, int8_t *xq, float *xscale, int64_t n_blocks, void *stream) {
     REQUIRE(n_blocks >= 0, "quantize_q8_0_rows: n_blocks < 0");
     if (n_blocks == 0) return 0;

@@ -19,7 +19,8 @@ void add_f32(const float *a, const float *b, float *y, int64_t n, cudaStream_t s
 
 void rms_norm_rows(const float *x, const float *residual_in, const float *w, int64_t weight_dim,
                    float *y_f32, uint16_t *y_bf16, float *residual_out, int64_t n_rows, int n,
-                   float eps, cudaStream_t s, int8_t *xq = nullptr, float *xscale = nullptr);
+                   float eps, cudaStream_t s, int8_t *xq = nullptr, float *xscale = nullptr,
+                   int8_t *kq = nullptr, float *kscale = nullptr, int16_t *kbsums = nullptr);
 
 // Activation quantisers (cuda/dense_q8.cu:122-152, cuda/moe_iq2_pair.cu:159-235).
 void quantize_q8_0_rows(const float *x, int8_t *xq, float *xscale, int64_t n_blocks, cudaStream_t s);

@@ -41,6 +41,13 @@ extern "C" int ds4b200_layer_rows_f32(const ds4b200_layer_dims *d, const ds4b200
                      (reinterpret_cast<uintptr_t>(b->kqv_q) & 3u)))
         return set_error(-EINVAL, "layer_rows: the Q8_0 form of the inverse RoPE needs head_dim % 32 == 0 and aligned rows");
 
+    if (!b->ffn_kq != !b->ffn_kscale || !b->ffn_kq != !b->ffn_kbsums)
+        return set_error(-EINVAL, "layer_rows: ffn_kq, ffn_kscale and ffn_kbsums go together");
+    if (b->ffn_kq && (d->n_embd % 256 || (reinterpret_cast<uintptr_t>(b->ffn_kq) & 3u) ||
+                      (reinterpret_cast<uintptr_t>(b->x) & 15u) || (reinterpret_cast<uintptr_t>(b->x_norm) & 15u) ||
+                      (reinterpret_cast<uintptr_t>(w->ffn_norm) & 15u)))
+        return set_error(-EINVAL, "layer_rows: the Q8_K form of the ffn norm needs n_embd % 256 == 0 and aligned rows");
+
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int n = d->n_embd, hd = d->head_dim;
     ds4b200_rope_params rope;
@@ -86,7 +93,7 @@ extern "C" int ds4b200_layer_rows_f32(const ds4b200_layer_dims *d, const ds4b200
     ds4b200::hc_pre_rows(b->resid_mid, w->hc_ffn_fn, w->hc_ffn_scale, w->hc_ffn_base, b->post, b->comb, b->x, T, n,
                          d->sinkhorn_iters, d->eps, s);
     ds4b200::rms_norm_rows(b->x, nullptr, w->ffn_norm, n, b->x_norm, nullptr, nullptr, T, n, d->eps, s, b->xq,
-                           b->xscale);
+                           b->xscale, b->ffn_kq, b->ffn_kscale, b->ffn_kbsums);
     if ((rc = launch_ok("hc attn post / hc ffn pre / ffn norm"))) return rc;
     if ((rc = call(DS4B200_STAGE_FFN_UP))) return rc;
     ds4b200::swiglu_rows(b->sh_gate, b->sh_up, nullptr, b->sh_mid, T, 1, d->ff_dim, DS4B200_GLU_PLAIN, 0.0f, 0, 0, s);

@@ -13,6 +13,7 @@
 // scalar two-pass kernel (second pass served by L2).
 #include "device_utils.cuh"
 #include "kernels.cuh"
+#include "q8k_device.cuh"
 
 namespace ds4b200 {
 namespace {
@@ -30,6 +31,9 @@ struct NormArgs {
     float eps;
     int8_t *xq;        // optional Q8_0 split form of the normalised row (n % 32 == 0)
     float *xscale;     // [n_rows][n / 32]
+    int8_t *kq;        // optional Q8_K form of the normalised row (n % 256 == 0, CTA kernel only)
+    float *kscale;     // [n_rows][n / 256]
+    int16_t *kbsums;   // [n_rows][n / 256][16]
 };
 
 __device__ __forceinline__ const float *row_gain(const NormArgs &a, int64_t row) {
@@ -77,6 +81,16 @@ __device__ __forceinline__ int q8_round(float v) {
     return q > 127 ? 127 : (q < -128 ? -128 : q);
 }
 
+// y = x * scale * w for one float4 of the row
+__device__ __forceinline__ float4 normalised4(const float4 &v, float scale, const float *g, int i, bool live) {
+    float4 y = make_float4(v.x * scale, v.y * scale, v.z * scale, v.w * scale);
+    if (g && live) {
+        const float4 w4 = ld_ro4(g + 4 * i);
+        y.x *= w4.x; y.y *= w4.y; y.z *= w4.z; y.w *= w4.w;
+    }
+    return y;
+}
+
 template <int VPT>
 __device__ __forceinline__ void store_row(const NormArgs &a, int64_t row, int first, int stride,
                                           const float4 (&v)[VPT], float scale) {
@@ -88,11 +102,7 @@ __device__ __forceinline__ void store_row(const NormArgs &a, int64_t row, int fi
     for (int j = 0; j < VPT; ++j) {
         const int i = first + j * stride;
         const bool live = i < n4;
-        float4 y = make_float4(v[j].x * scale, v[j].y * scale, v[j].z * scale, v[j].w * scale);
-        if (g && live) {
-            const float4 w4 = ld_ro4(g + 4 * i);
-            y.x *= w4.x; y.y *= w4.y; y.z *= w4.z; y.w *= w4.w;
-        }
+        const float4 y = normalised4(v[j], scale, g, i, live);
         if (live && yf) st_stream4(yf + 4 * i, y);
         if (live && yb) st_bf16x4(yb + 4 * i, y);
         if (a.xq) {
@@ -112,10 +122,74 @@ __device__ __forceinline__ void store_row(const NormArgs &a, int64_t row, int fi
     }
 }
 
-// One CTA per row; the row lives in VPT float4 registers per thread.
+// The normalised row as the Q8_K blocks the routed experts' gate / up dots read (the reference quantises the
+// row inside that launcher, cuda/moe_iq2_pair.cu:159-235).  A block of 256 values is held by 64 consecutive
+// threads, two warps (blockDim is a multiple of 64 and so is n / 4): each warp finds the element of largest
+// magnitude of its half, the first one on ties, the halves meet in shared memory, and the lower half wins a
+// tie between them, as index order has it.
 template <int VPT>
+__device__ __forceinline__ void q8_K_half_maxima(const NormArgs &a, int64_t row, const float4 (&v)[VPT], float scale,
+                                                 float4 (&y)[VPT], float2 (*half_max)[32]) {
+    const int n4 = a.n >> 2;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float *g = row_gain(a, row);
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        const bool live = i < n4;                       // a warp is live or dead as a whole
+        y[j] = normalised4(v[j], scale, g, i, live);
+        const float mine_a = live ? amax4(y[j]) : 0.0f;
+        float amax = mine_a;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        const unsigned hits = __ballot_sync(0xffffffffu, mine_a == amax);
+        float mine = y[j].w;
+        mine = fabsf(y[j].z) == amax ? y[j].z : mine;
+        mine = fabsf(y[j].y) == amax ? y[j].y : mine;
+        mine = fabsf(y[j].x) == amax ? y[j].x : mine;
+        const float smax = __shfl_sync(0xffffffffu, mine, __ffs(hits) - 1);
+        if (lane == 0) half_max[j][warp] = make_float2(amax, smax);
+    }
+}
+
+template <int VPT>
+__device__ __forceinline__ void store_row_q8_K(const NormArgs &a, int64_t row, const float4 (&y)[VPT],
+                                               float2 (*half_max)[32]) {
+    const int n4 = a.n >> 2;
+    const int warp = threadIdx.x >> 5;
+    __syncthreads();
+    const int blocks_per_row = a.n >> 8;
+    // lane j works out the scale of the warp pair's block j (an all-zero block keeps 0, 0); the others
+    // read it by shuffle
+    const int lane = threadIdx.x & 31;
+    float lane_iscale = 0.0f, lane_dq = 0.0f;
+    if (lane < VPT) {
+        const float2 lo = half_max[lane][warp & ~1], hi = half_max[lane][warp | 1];
+        const float amax = fmaxf(lo.x, hi.x);
+        if (amax != 0.0f) q8k_block_scale(lo.x == amax ? lo.y : hi.y, lane_iscale, lane_dq);
+    }
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        const float iscale = __shfl_sync(0xffffffffu, lane_iscale, j);
+        const float dq = __shfl_sync(0xffffffffu, lane_dq, j);
+        if (i >= n4) continue;
+        const int64_t blk = row * blocks_per_row + (i >> 6);
+        const uint32_t packed = q8_pack4_sat(iscale * y[j].x, iscale * y[j].y, iscale * y[j].z, iscale * y[j].w);
+        reinterpret_cast<uint32_t *>(a.kq + row * a.n)[i] = packed;
+        int sum = __dp4a((int)packed, 0x01010101, 0);   // 16 consecutive values = 4 consecutive lanes
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        if ((i & 3) == 0) a.kbsums[blk * 16 + ((i & 63) >> 2)] = (int16_t)sum;
+        if ((i & 63) == 0) a.kscale[blk] = dq;
+    }
+}
+
+// One CTA per row; the row lives in VPT float4 registers per thread.
+template <int VPT, bool Q8K>
 __global__ void rms_norm_cta_kernel(NormArgs a) {
     __shared__ float red[33];
+    __shared__ float2 half_max[Q8K ? VPT : 1][32];
     const int64_t row = blockIdx.x;
     float4 v[VPT];
     float ss = load_row<VPT>(a, row, threadIdx.x, blockDim.x, v);
@@ -131,7 +205,14 @@ __global__ void rms_norm_cta_kernel(NormArgs a) {
         ss = block_sum(ss, red);
     }
     const float scale = rms_scale(ss, (float)a.n, a.eps);
-    store_row<VPT>(a, row, threadIdx.x, blockDim.x, v, scale);
+    if (Q8K) {
+        float4 y[VPT];
+        store_row<VPT>(a, row, threadIdx.x, blockDim.x, v, scale);
+        q8_K_half_maxima<VPT>(a, row, v, scale, y, half_max);
+        store_row_q8_K<VPT>(a, row, y, half_max);
+    } else {
+        store_row<VPT>(a, row, threadIdx.x, blockDim.x, v, scale);
+    }
 }
 
 // One warp per row (rows up to 1024 floats): shuffle reduction only.
@@ -190,7 +271,8 @@ __global__ void add_scalar_kernel(const float *__restrict__ a, const float *__re
 
 template <int VPT>
 void launch_cta(const NormArgs &a, int threads, cudaStream_t s) {
-    rms_norm_cta_kernel<VPT><<<(unsigned)a.n_rows, threads, 0, s>>>(a);
+    if (a.kq) rms_norm_cta_kernel<VPT, true><<<(unsigned)a.n_rows, threads, 0, s>>>(a);
+    else rms_norm_cta_kernel<VPT, false><<<(unsigned)a.n_rows, threads, 0, s>>>(a);
 }
 template <int VPT>
 void launch_warp(const NormArgs &a, cudaStream_t s) {
@@ -216,9 +298,11 @@ void add_f32(const float *a, const float *b, float *y, int64_t n, cudaStream_t s
 
 void rms_norm_rows(const float *x, const float *residual_in, const float *w, int64_t weight_dim,
                    float *y_f32, uint16_t *y_bf16, float *residual_out, int64_t n_rows, int n,
-                   float eps, cudaStream_t s, int8_t *xq, float *xscale) {
+                   float eps, cudaStream_t s, int8_t *xq, float *xscale, int8_t *kq, float *kscale,
+                   int16_t *kbsums) {
     if (n_rows <= 0 || n <= 0) return;
-    const NormArgs a{x, residual_in, w, weight_dim, y_f32, y_bf16, residual_out, n_rows, n, eps, xq, xscale};
+    const NormArgs a{x, residual_in, w, weight_dim, y_f32, y_bf16, residual_out, n_rows, n, eps, xq, xscale,
+                     kq, kscale, kbsums};
     const bool vec = (n & 3) == 0 && n <= 8192 && aligned16(x) && aligned16(residual_in) &&
                      aligned16(w) && aligned16(y_f32) && aligned8(y_bf16) &&
                      aligned16(residual_out);
@@ -227,7 +311,7 @@ void rms_norm_rows(const float *x, const float *residual_in, const float *w, int
         return;
     }
     const int n4 = n >> 2;
-    if (n4 <= 256 && n_rows >= 64) {           // warp per row
+    if (n4 <= 256 && n_rows >= 64 && !kq) {    // warp per row
         const int vpt = (n4 + 31) / 32;
         if (vpt <= 1) launch_warp<1>(a, s);
         else if (vpt <= 2) launch_warp<2>(a, s);

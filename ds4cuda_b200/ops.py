@@ -86,6 +86,23 @@ def rms_norm_q8_0_rows(x, w=None, residual=None, eps=1e-6, want_f32=True, want_r
     return y, ro, xq, xs
 
 
+def rms_norm_q8_K_rows(x, w=None, residual=None, eps=1e-6, want_f32=True, want_residual=False, want_q8_0=False):
+    """RMSNorm + Q8_K activation quantiser (and optionally the Q8_0 one on the same row).  Returns
+    (y_f32, residual_out, (xq, xscale) or None, (kq int8 [rows, n], kscale [rows, n/256], kbsums int16 [rows, n/16]))."""
+    rows, n = x.shape
+    y = torch.empty_like(x) if want_f32 else None
+    ro = torch.empty_like(x) if want_residual else None
+    xq = torch.empty((rows, n), dtype=torch.int8, device=x.device) if want_q8_0 else None
+    xs = torch.empty((rows, n // 32), dtype=torch.float32, device=x.device) if want_q8_0 else None
+    kq = torch.empty((rows, n), dtype=torch.int8, device=x.device)
+    ks = torch.empty((rows, n // 256), dtype=torch.float32, device=x.device)
+    kb = torch.empty((rows, n // 16), dtype=torch.int16, device=x.device)
+    check(_lib.load().ds4b200_rms_norm_q8_K_rows_f32(_p(x), _p(residual), _p(w), 0 if w is None else w.numel(), _p(y),
+                                                     _p(ro), _p(xq), _p(xs), _p(kq), _p(ks), _p(kb), rows, n, eps,
+                                                     _s()))
+    return y, ro, ((xq, xs) if want_q8_0 else None), (kq, ks, kb)
+
+
 def quantize_q8_0_rows(x):
     """x with numel % 32 == 0 -> (int8 like x, f32 scales [numel/32])."""
     xq = torch.empty(x.shape, dtype=torch.int8, device=x.device)

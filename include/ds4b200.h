@@ -150,6 +150,17 @@ int ds4b200_rms_norm_q8_0_rows_f32(const float *x, const float *residual_in, con
                                    int8_t *xq, float *xscale, int64_t n_rows, int n, float eps,
                                    void *stream);
 
+/* The same RMSNorm leaving the row as the Q8_K blocks the routed experts' IQ2_XXS gate / up dots
+ * read, which the reference quantises inside that launcher (cuda/moe_iq2_pair.cu:159-235 called on
+ * the normalised row at :404-421): kq[n_rows][n] int8, kscale[n_rows][n/256],
+ * kbsums[n_rows][n/256][16].  xq / xscale (the Q8_0 form, both or neither) and y_f32 are nullable:
+ * the feed-forward norm of a layer feeds a Q8_0 matvec (shared expert) and the Q8_K dots (routed
+ * experts) from the same row.  n a multiple of 256, at most 8192; 16-byte aligned f32 buffers. */
+int ds4b200_rms_norm_q8_K_rows_f32(const float *x, const float *residual_in, const float *w,
+                                   int64_t weight_dim, float *y_f32, float *residual_out,
+                                   int8_t *xq, float *xscale, int8_t *kq, float *kscale,
+                                   int16_t *kbsums, int64_t n_rows, int n, float eps, void *stream);
+
 /* The activation quantisers on their own.  Q8_0 split form: n_blocks blocks of 32 f32 ->
  * int8 + one f32 scale each (cuda/dense_q8.cu:122-152).  Q8_K: n_blocks blocks of 256 ->
  * int8, one f32 scale and 16 int16 partial sums each (cuda/moe_iq2_pair.cu:159-235; on equal

@@ -95,6 +95,12 @@ typedef struct ds4b200_layer_buffers {      /* caller-owned device workspace for
      * the two head-row RoPE stages behind it read them instead of evaluating 32 cos / sin pairs per
      * head row; the rotated rows keep their bits. */
     float *rope_cs;                         /* [T][n_rot/2][2] */
+    /* Optional (all three or none; n_embd % 256 == 0): the feed-forward norm also leaves its row as the
+     * Q8_K blocks the routed experts' IQ2_XXS gate / up dots read (cuda/moe_iq2_pair.cu:404-421 quantises
+     * the row inside that launcher), so FFN_UP needs no quantiser launch of its own. */
+    int8_t *ffn_kq;                         /* [T][n_embd] */
+    float *ffn_kscale;                      /* [T][n_embd/256] */
+    int16_t *ffn_kbsums;                    /* [T][n_embd/256][16] */
 } ds4b200_layer_buffers;
 
 /* Called on the issuing thread between row stages; must enqueue its work on `stream` (or

@@ -109,6 +109,11 @@ def test_checked_entry_points_reject_bad_arguments_without_a_gpu(lib):
     assert lib.ds4b200_rms_norm_rows_f32(p, None, None, 0, None, None, None, 4, 16, 1e-6, None) == EINVAL
     assert lib.ds4b200_rms_norm_rows_f32(p, None, None, 0, p, None, p, 4, 16, 1e-6, None) == EINVAL
     assert lib.ds4b200_rms_norm_rows_f32(None, None, None, 0, None, None, None, 0, 16, 1e-6, None) == 0
+    q = C.c_void_p(0x1000)
+    assert lib.ds4b200_rms_norm_q8_K_rows_f32(q, None, None, 0, None, None, None, None, q, q, q, 4, 4000, 1e-6, None) == EINVAL
+    assert lib.ds4b200_rms_norm_q8_K_rows_f32(q, None, None, 0, None, None, q, None, q, q, q, 4, 4096, 1e-6, None) == EINVAL
+    assert lib.ds4b200_rms_norm_q8_K_rows_f32(q, None, None, 0, None, None, None, None, q, None, q, 4, 4096, 1e-6, None) == EINVAL
+    assert lib.ds4b200_rms_norm_q8_K_rows_f32(q, None, None, 0, None, None, None, None, q, q, q, 0, 4096, 1e-6, None) == 0
     assert lib.ds4b200_embed_gather_rows(p, 7, p, 4, 64, None, None, 1e-6, p, 1, None, None, None) == EINVAL
     assert lib.ds4b200_embed_gather_rows(p, 1, p, 4, 48, None, None, 1e-6, p, 1, None, None, None) == EINVAL
     assert lib.ds4b200_embed_gather_rows(p, 0, p, 4, 64, None, None, 1e-6, None, 1, None, None, None) == EINVAL

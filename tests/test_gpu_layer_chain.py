@@ -165,7 +165,11 @@ def test_layer_rows_entry_point_sequences_the_same_chain(ops):
     mq, ms, mb, _ = ops.swiglu_q8_K_rows(S["gate"], S["up"], S["router_w"], ops.GLU_CLAMP_REF, 10.0, fast_exp=True)
     want = ops.hc_post_rows(S["moe_out"], resid_attn, post_f, comb_f, block_out2=S["shexp_out"])
     torch.cuda.synchronize()
-    eq = lambda a, b, what: (torch.equal(a, b) or pytest.fail(f"{what} differs"))
+    def eq(a, b, what):
+        if not torch.equal(a, b):
+            where = (a != b).nonzero()
+            pytest.fail(f"{what} differs at {where.shape[0]} of {a.numel()} places, first {where[:4].tolist()}: "
+                        f"{a[tuple(where[0])].item()!r} against {b[tuple(where[0])].item()!r}")
     eq(snap["x_norm"], xn, "attn norm"); eq(snap["xq"], xq, "attn norm Q8_0")
     eq(B["q_lora_norm"], qn, "q_a norm"); eq(B["raw_rows"], raw, "raw KV rows")
     eq(B["q"], q_cur, "q norm + RoPE"); eq(B["kqv"], kqv_back, "inverse RoPE")
@@ -179,8 +183,10 @@ def test_layer_rows_entry_point_sequences_the_same_chain(ops):
     kq = torch.zeros(T, H, hd, dtype=torch.int8, device="cuda")
     ks = torch.zeros(T, H, hd // 32, device="cuda")
     cs = torch.zeros(T, 32, 2, device="cuda")       # and the angle table: same bits in every RoPE stage
+    fkq = torch.zeros(T, n, dtype=torch.int8, device="cuda")      # and the ffn norm's row as Q8_K blocks
+    fks, fkb = torch.zeros(T, n // 256, device="cuda"), torch.zeros(T, n // 16, dtype=torch.int16, device="cuda")
     buffers_q = _lib.LayerBuffers(*[B[nm].data_ptr() for nm in _lib.LayerBuffers.NAMES], kq.data_ptr(), ks.data_ptr(),
-                                  cs.data_ptr())
+                                  cs.data_ptr(), fkq.data_ptr(), fks.data_ptr(), fkb.data_ptr())
     out_q = torch.zeros(T, 4, n, device="cuda")
     rc = L.ds4b200_layer_rows_f32(C.byref(dims), C.byref(weights), C.byref(buffers_q), resid_hc.data_ptr(),
                                   pos.data_ptr(), T, out_q.data_ptr(), cb, None, None)
@@ -191,6 +197,10 @@ def test_layer_rows_entry_point_sequences_the_same_chain(ops):
     eq(B["kqv"], S["kqv"], "kqv left as the attention stage wrote it"); eq(out_q, want, "residual streams (Q8_0 form)")
     eq(B["q"], q_cur, "q norm + RoPE from the table"); eq(B["raw_rows"], raw, "raw KV rows from the table")
     eq(cs, ops.rope_table_rows(pos, p), "angle table")
+    wkq, wks, wkb = ops.quantize_q8_K_rows(xfn)
+    eq(fkq, wkq, "ffn norm Q8_K values"); eq(fks.view(-1), wks, "ffn norm Q8_K scales")
+    eq(fkb.view(-1), wkb, "ffn norm Q8_K sums"); eq(B["x_norm"], xfn, "ffn norm beside its Q8_K form")
+    eq(B["xq"], xfq, "ffn norm Q8_0 beside its Q8_K form")
 
     # a hook that fails stops the layer with its code
     bad = _lib.StageHook(lambda user, stage, n_tokens, stream: -7 if stage == _lib.STAGE_Q_B else 0)

@@ -194,6 +194,9 @@ def test_batched_layer_with_reference_matvecs_in_the_hook_against_the_reference_
              sh_mid=f32(T, 1, FF), gate=f32(T, K, FF), up=f32(T, K, FF), router_w=f32(T, K), mid_q=i8(T, K, FF),
              mid_scale=f32(T, K, FF // 256), mid_bsums=torch.zeros(T, K, FF // 256, 16, dtype=torch.int16, device="cuda"),
              moe_out=f32(T, N), shexp_out=f32(T, N))
+    ffn_kq, ffn_ks = i8(T, N), f32(T, N // 256)                            # the ffn norm's row as Q8_K blocks
+    ffn_kb = torch.zeros(T, N // 16, dtype=torch.int16, device="cuda")
+    ref_ffn_k = []                                                         # what the reference's quantiser made of each row
     sxq, sxs = i8(H * HD), f32(H * HD // 32)                               # Q8_0 scratch of the matvec launchers
     kxq, kxs, kxb = i8(K * FF), f32(K * FF // 256), torch.zeros(K * FF // 256 * 16, dtype=torch.int16, device="cuda")
     window, attn_low = f32(128, HD), f32(T, LOW)
@@ -247,6 +250,7 @@ def test_batched_layer_with_reference_matvecs_in_the_hook_against_the_reference_
                 ref.call("hash_router_topk_w_f32", probs, ids[t], B["router_w"][t], K, 1.5, 6.103515625e-5)
                 ref.call("test_iq2_pair_dots", blob["ffn_gate_exps.weight"], blob["ffn_up_exps.weight"], B["x_norm"][t],
                          ids[t], B["gate"][t], B["up"][t], K, FF, N, NEXP, kxq, kxs, kxb)
+                ref_ffn_k.append((kxq[:N].clone(), kxs[:N // 256].clone(), kxb[:N // 16].clone()))
         elif stage == _lib.STAGE_FFN_DOWN:                                 # :1296, :1416
             # the reference's down-projection takes the f32 mid rows and quantises them itself
             snap["mid"] = ops.swiglu_rows(B["gate"], B["up"], B["router_w"], ops.GLU_CLAMP_REF, 10.0, fast_exp=True)
@@ -262,7 +266,8 @@ def test_batched_layer_with_reference_matvecs_in_the_hook_against_the_reference_
                    ffn_norm="ffn_norm.weight")
     dims = _lib.LayerDims(N, H, HD, 64, QL, FF, K, 20, il, 1, 1e-6, 10.0)
     weights = _lib.LayerWeights(*[blob[w_names[nm]].data_ptr() for nm in _lib.LayerWeights.NAMES])
-    buffers = _lib.LayerBuffers(*[B[nm].data_ptr() for nm in _lib.LayerBuffers.NAMES])
+    buffers = _lib.LayerBuffers(*[B[nm].data_ptr() for nm in _lib.LayerBuffers.NAMES], None, None, None,
+                                ffn_kq.data_ptr(), ffn_ks.data_ptr(), ffn_kb.data_ptr())
     got = f32(T, 4, N)
     cb = _lib.StageHook(hook)
     rc = L.ds4b200_layer_rows_f32(C.byref(dims), C.byref(weights), C.byref(buffers), resid_in.data_ptr(), pos.data_ptr(),
@@ -270,6 +275,12 @@ def test_batched_layer_with_reference_matvecs_in_the_hook_against_the_reference_
     assert rc == 0, (L.ds4b200_last_error(), failure)
     torch.cuda.synchronize()
     assert ops.device_status() == 0
+
+    # ------------------------------------------------------------ the ffn norm's Q8_K blocks == what the reference's
+    # quantiser (inside its routed gate / up launcher) made of the same normalised row, token by token
+    for t in range(T):
+        rq, rs, rb = ref_ffn_k[t]
+        assert torch.equal(ffn_kq[t], rq) and torch.equal(ffn_ks[t], rs) and torch.equal(ffn_kb[t], rb), t
 
     # ------------------------------------------------------------ the routed epilogue's Q8_K blocks == what the reference's
     # down-projection quantised for itself from the same f32 rows (its scratch still holds the last token's)

@@ -768,6 +768,54 @@ def test_rms_norm_with_fused_q8_0(ops, oracle, rows, n):
     assert torch.equal(xq3, xq) and torch.equal(xs3, xs)
 
 
+@pytest.mark.parametrize("rows,n", [(1, 4096), (5, 1024), (300, 4096), (64, 512), (3, 8192), (70, 256), (2048, 4096)])
+def test_rms_norm_with_fused_q8_K(ops, oracle, rows, n):
+    """RMSNorm that leaves its row as Q8_K blocks (the form the routed experts' IQ2_XXS dots read;
+    cuda/moe_iq2_pair.cu:159-235): bitwise the quantiser run on the kernel's own normalised row, with
+    and without the Q8_0 form, the f32 row and the residual beside it."""
+    g = inputs.rng(830 + rows + n)
+    x, r, w = inputs.normal(g, (rows, n)), inputs.normal(g, (rows, n)), inputs.uniform(g, (n,), 0.5, 1.5)
+    r[0] = 0.0
+    x[0, :256] = 0.0                                        # an all-zero block
+    if n >= 512:
+        w[256:512] = 1.0
+        x[0, 256:512] = np.clip(x[0, 256:512], -3, 3)
+        x[0, 256 + 200] = -3.5                              # equal magnitudes in the two warps that share
+        x[0, 256 + 17] = 3.5                                # the block: the earlier element wins
+    if rows > 1:
+        r[1] = 0.0
+        w[3] = w[70] = 1.0
+        x[1, 3], x[1, 70] = -9.0, 9.0                       # a tie inside one warp: lane 0 before lane 17
+    y, ro, q0, (kq, ks, kb) = ops.rms_norm_q8_K_rows(dev(x), dev(w), residual=dev(r), want_residual=True,
+                                                     want_q8_0=True)
+    want, _, want_ro = oracle.rms_norm_rows(x, w, residual=r, want_residual=True)
+    assert_bits(host(ro), want_ro, "residual sum")
+    assert_close(host(y), want, what="normed row")
+    wq, ws, wb = oracle.quantize_q8_K_rows(host(y).ravel())
+    assert_bits(host(ks).ravel(), ws, "fused Q8_K scales")
+    assert_bits(host(kq).ravel(), wq, "fused Q8_K values")
+    assert_bits(host(kb).ravel(), wb, "fused Q8_K partial sums")
+    if n >= 512:
+        assert host(ks)[0, 0] == 0.0 and not host(kq)[0, :256].any()
+        assert host(ks)[0, 1] < 0                           # d = -max/127 with max = +y[0, 273]
+    if rows > 1:
+        assert host(ks)[1, 0] > 0                           # max = y[1, 3] < 0
+    kq2, ks2, kb2 = ops.quantize_q8_K_rows(y)
+    assert torch.equal(kq2, kq) and torch.equal(ks2, ks.view(-1)) and torch.equal(kb2, kb.view(-1))
+    # the other outputs are those of the kernels without the Q8_K form
+    # (many short rows go one warp per row without the Q8_K form and one CTA per row with it: another
+    # summation order, so only rows of the same kernel are compared bit for bit)
+    y0, ro0, xq0, xs0 = ops.rms_norm_q8_0_rows(dev(x), dev(w), residual=dev(r), want_residual=True)
+    assert torch.equal(ro0, ro)
+    if n > 1024 or rows < 64:
+        assert torch.equal(y0, y) and torch.equal(xq0, q0[0]) and torch.equal(xs0, q0[1])
+    wq0, ws0 = ops.quantize_q8_0_rows(y)
+    assert torch.equal(wq0, q0[0]) and torch.equal(ws0.view_as(q0[1]), q0[1])
+    none, _, no_q0, (kq3, ks3, kb3) = ops.rms_norm_q8_K_rows(dev(x), dev(w), residual=dev(r), want_f32=False)
+    assert none is None and no_q0 is None
+    assert torch.equal(kq3, kq) and torch.equal(ks3, ks) and torch.equal(kb3, kb)
+
+
 def test_inverse_rope_with_q8_0_output(ops, ref):
     """The inverse RoPE whose rows leave as Q8_0 blocks: the f32 copy equals rope_rows bit for bit, the
     blocks equal the stand-alone quantiser on those rows, and both equal what the reference's grouped
