@@ -39,7 +39,8 @@
 //     row, re-read from L2, where the step's rows still are; two of those warps then run the Sinkhorn
 //     sweeps of the step's four tokens, 16 lanes per token.
 // Every residual row crosses HBM once; nothing is reduced across clusters; every sum has a fixed
-// order, so two runs agree bit for bit.
+// order that does not depend on the token's place in the batch, so two runs agree bit for bit and
+// a token's outputs are the same whether it is computed in a batch of 4096 or in a slice of it.
 //
 // What the tensor-core unit costs here (measured on B200 with single-CTA probes): every tcgen05
 // operation — an MMA of any shape up to N=64, a commit, a shared-to-tensor-memory copy — takes
@@ -200,7 +201,8 @@ hc_pre_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
     __shared__ __align__(8) uint64_t a_full[kARing], a_free[kARing];
     __shared__ __align__(8) uint64_t acc_full[2], acc_free[2];
     __shared__ __align__(8) uint64_t xch_full[2], xch_free[2], ss_ready[2];
-    __shared__ float ss_part[2][kPrepGroups][kStepTokens];   // sum(x^2) per token, per group, per step parity
+    __shared__ float ss_part[2][kPrepGroups][kStepTokens];   // sum(x^2) per token, per stage residue mod 3, per step parity
+    static_assert(kStages % kPrepGroups == 2 && kPrepGroups == 3, "the residue a group files its share under assumes 8 = 2 mod 3");
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
     __shared__ float tot_s[kTokensPerCta][kRec];
@@ -352,7 +354,11 @@ hc_pre_tc_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
             // ---- past the end of a step: publish this group's share of sum(x^2)
             const int n_step = n / kStages < my_steps ? n / kStages : my_steps;
             if (n_step > cur_step) {
-                if (!is_lo) ss_part[cur_step & 1][group][token] = (ss0 + ss1) + (ss2 + ss3);
+                // A step has 8 stages and the groups take chunks in turn, so in step `it` this group had the
+                // stages sg with sg % 3 == (group + it) % 3, in rising order.  Filed under that residue, the
+                // three shares add up in the same order wherever in the batch the token sits.
+                if (!is_lo)
+                    ss_part[cur_step & 1][(group + cur_step) % kPrepGroups][token] = (ss0 + ss1) + (ss2 + ss3);
                 ss0 = ss1 = ss2 = ss3 = 0.0f;
                 __syncwarp();
                 if (!is_lo && lane == 0) mbar_arrive(&ss_ready[cur_step & 1]);

@@ -584,6 +584,23 @@ def test_hc_pre_tensor_core_kernel_against_the_reference_kernel_token_by_token(o
     assert_close(host(out), host(rout), what="out vs reference kernel")
 
 
+def test_hc_pre_of_a_token_does_not_depend_on_its_place_in_the_batch(ops):
+    """The tcgen05 kernel on a batch and on slices of it (other step, other cluster, the short last step, another
+    turn of the operand groups): every token's outputs keep their bits, which is what lets a batch be split over
+    ranks or chunks without changing results."""
+    g = inputs.rng(703)
+    n, T = 4096, 2100
+    resid = dev(inputs.normal(g, (T, 4, n)))
+    wts = inputs.hc_pre_weights(9, n)
+    fn, scale, base = dev(wts["fn"]), dev(wts["scale"]), dev(wts["base"])
+    post, comb, out = ops.hc_pre_rows(resid, fn, scale, base)
+    for lo, hi in [(0, 1050), (1050, 2100), (64, 1987), (448, 896), (7 * 64, 2100), (1, 130), (2000, 2100)]:
+        p, c, o = ops.hc_pre_rows(resid[lo:hi], fn, scale, base)
+        assert torch.equal(o, out[lo:hi]), (lo, hi, int((o != out[lo:hi]).any(dim=1).sum()))
+        assert torch.equal(p, post[lo:hi]) and torch.equal(c, comb[lo:hi]), (lo, hi)
+    assert ops.device_status() == 0
+
+
 @pytest.mark.parametrize("n_embd,T", [(4096, 9), (1024, 5), (8192, 2), (100, 4)])
 def test_hc_post_and_sinkhorn_mix_rows(ops, oracle, ref, n_embd, T):
     g = inputs.rng(710 + n_embd)
