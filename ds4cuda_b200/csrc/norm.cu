@@ -11,6 +11,10 @@
 // traffic is 128-bit, coalesced, with the streaming cache policy.  Rows that are
 // not 16-byte aligned, not a multiple of 4 long, or longer than 8192 take a
 // scalar two-pass kernel (second pass served by L2).
+//
+// A row's bits do not depend on how many rows a call has: whichever shape of CTA
+// the row count selects, the squares are added in the order of the many-row
+// kernel for that row length (rms_norm_cta_kernel).
 #include "device_utils.cuh"
 #include "kernels.cuh"
 #include "q8k_device.cuh"
@@ -189,21 +193,41 @@ __device__ __forceinline__ void store_row_q8_K(const NormArgs &a, int64_t row, c
 template <int VPT, bool Q8K>
 __global__ void rms_norm_cta_kernel(NormArgs a) {
     __shared__ float red[33];
+    __shared__ float sq[2048];                 // squares per float4 of the row (rows of up to 8192 floats)
     __shared__ float2 half_max[Q8K ? VPT : 1][32];
     const int64_t row = blockIdx.x;
     float4 v[VPT];
     float ss = load_row<VPT>(a, row, threadIdx.x, blockDim.x, v);
-    if (blockDim.x == 256) {
+    const int n4 = a.n >> 2;
+    if (blockDim.x == 256 && n4 > 256) {
         // one barrier instead of three: every thread adds the eight warp sums itself, in the order the
         // butterfly of block_sum adds them (same bits)
         ss = warp_sum(ss);
         if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
         __syncthreads();
-        ss = __fadd_rn(__fadd_rn(__fadd_rn(red[0], red[4]), __fadd_rn(red[2], red[6])),
-                       __fadd_rn(__fadd_rn(red[1], red[5]), __fadd_rn(red[3], red[7])));
     } else {
-        ss = block_sum(ss, red);
+        // Any other shape of CTA adds the row up in the order of the kernel that many rows of this length
+        // get, so that a row's bits do not depend on how many rows the call has: rows of up to 1024 floats
+        // as one warp does (lane l takes float4 l, l + 32, ... in turn, then the butterfly), longer ones as
+        // 256 threads do (thread t takes float4 t, t + 256, ..., butterflies, the eight warp sums below).
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            if (i < n4) sq[i] = dot4(v[j]);
+        }
+        __syncthreads();
+        const int takers = n4 <= 256 ? 32 : 256;
+        if (threadIdx.x < takers) {
+            float part = 0.0f;
+            for (int i = threadIdx.x; i < n4; i += takers) part += sq[i];
+            part = warp_sum(part);
+            if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = part;
+        }
+        __syncthreads();
     }
+    ss = n4 <= 256 ? red[0]
+                   : __fadd_rn(__fadd_rn(__fadd_rn(red[0], red[4]), __fadd_rn(red[2], red[6])),
+                               __fadd_rn(__fadd_rn(red[1], red[5]), __fadd_rn(red[3], red[7])));
     const float scale = rms_scale(ss, (float)a.n, a.eps);
     if (Q8K) {
         float4 y[VPT];

@@ -785,6 +785,27 @@ def test_rms_norm_with_fused_q8_0(ops, oracle, rows, n):
     assert torch.equal(xq3, xq) and torch.equal(xs3, xs)
 
 
+@pytest.mark.parametrize("n", [4096, 1024, 512, 2048, 8192, 256])
+def test_rms_norm_of_a_row_does_not_depend_on_the_number_of_rows(ops, n):
+    """One row, a few rows and many rows go to differently shaped CTAs (or to one warp per row); all of them add
+    a row up in the same order, so a token normalised alone has the bits it has inside a chunk.  The same for the
+    forms that also leave Q8_0 / Q8_K blocks."""
+    g = inputs.rng(840 + n)
+    T = 700
+    x, w = dev(inputs.normal(g, (T, n))), dev(inputs.uniform(g, (n,), 0.5, 1.5))
+    full = ops.rms_norm_rows(x, w)[0]
+    _, _, fq, fs = ops.rms_norm_q8_0_rows(x, w)
+    yk, _, _, (kq, ks, kb) = ops.rms_norm_q8_K_rows(x, w)
+    assert torch.equal(yk, full)
+    for lo, hi in [(0, 1), (3, 5), (0, 63), (0, 64), (100, 395), (0, 296), (5, 700)]:
+        assert torch.equal(ops.rms_norm_rows(x[lo:hi], w)[0], full[lo:hi]), (lo, hi)
+        y0, _, q0, s0 = ops.rms_norm_q8_0_rows(x[lo:hi], w)
+        assert torch.equal(y0, full[lo:hi]) and torch.equal(q0, fq[lo:hi]) and torch.equal(s0, fs[lo:hi]), (lo, hi)
+        y1, _, _, (q1, s1, b1) = ops.rms_norm_q8_K_rows(x[lo:hi], w)
+        assert torch.equal(y1, full[lo:hi]) and torch.equal(q1, kq[lo:hi]) and torch.equal(s1, ks[lo:hi]), (lo, hi)
+        assert torch.equal(b1, kb[lo:hi]), (lo, hi)
+
+
 @pytest.mark.parametrize("rows,n", [(1, 4096), (5, 1024), (300, 4096), (64, 512), (3, 8192), (70, 256), (2048, 4096)])
 def test_rms_norm_with_fused_q8_K(ops, oracle, rows, n):
     """RMSNorm that leaves its row as Q8_K blocks (the form the routed experts' IQ2_XXS dots read;
@@ -820,12 +841,10 @@ def test_rms_norm_with_fused_q8_K(ops, oracle, rows, n):
     kq2, ks2, kb2 = ops.quantize_q8_K_rows(y)
     assert torch.equal(kq2, kq) and torch.equal(ks2, ks.view(-1)) and torch.equal(kb2, kb.view(-1))
     # the other outputs are those of the kernels without the Q8_K form
-    # (many short rows go one warp per row without the Q8_K form and one CTA per row with it: another
-    # summation order, so only rows of the same kernel are compared bit for bit)
+    # (many short rows go one warp per row without the Q8_K form and one CTA per row with it: same bits)
     y0, ro0, xq0, xs0 = ops.rms_norm_q8_0_rows(dev(x), dev(w), residual=dev(r), want_residual=True)
     assert torch.equal(ro0, ro)
-    if n > 1024 or rows < 64:
-        assert torch.equal(y0, y) and torch.equal(xq0, q0[0]) and torch.equal(xs0, q0[1])
+    assert torch.equal(y0, y) and torch.equal(xq0, q0[0]) and torch.equal(xs0, q0[1])
     wq0, ws0 = ops.quantize_q8_0_rows(y)
     assert torch.equal(wq0, q0[0]) and torch.equal(ws0.view_as(q0[1]), q0[1])
     none, _, no_q0, (kq3, ks3, kb3) = ops.rms_norm_q8_K_rows(dev(x), dev(w), residual=dev(r), want_f32=False)
