@@ -171,6 +171,20 @@ def test_checked_entry_points_reject_bad_arguments_without_a_gpu(lib):
     bad_dims = LayerDims(4096, 64, 500, 64, 1024, 2048, 6, 20, 2, 1, 1e-6, 10.0)
     assert lib.ds4b200_layer_rows_f32(C.byref(bad_dims), C.byref(wts), C.byref(bufs), p, p, 4, p, hook, None, None) == EINVAL
     assert b"geometry" in lib.ds4b200_last_error()
+    # optional buffers come in groups: kqv_q with kqv_scale; ffn_kq with ffn_kscale and ffn_kbsums
+    a = 0x1000
+    full = {n: a for n in LayerBuffers.NAMES}
+    all_w = LayerWeights(*[a] * len(LayerWeights.NAMES))
+    half = LayerBuffers(**full, kqv_q=a)
+    assert lib.ds4b200_layer_rows_f32(C.byref(dims), C.byref(all_w), C.byref(half), p, p, 4, p, hook, None, None) == EINVAL
+    assert b"go together" in lib.ds4b200_last_error()
+    two_of_three = LayerBuffers(**full, ffn_kq=a, ffn_kbsums=a)
+    assert lib.ds4b200_layer_rows_f32(C.byref(dims), C.byref(all_w), C.byref(two_of_three), p, p, 4, p, hook, None, None) == EINVAL
+    assert b"ffn_kq, ffn_kscale and ffn_kbsums go together" in lib.ds4b200_last_error()
+    narrow = LayerDims(4096 + 32, 64, 512, 64, 1024, 2048, 6, 20, 2, 1, 1e-6, 10.0)      # not a multiple of 256
+    q8k = LayerBuffers(**full, ffn_kq=a, ffn_kscale=a, ffn_kbsums=a)
+    assert lib.ds4b200_layer_rows_f32(C.byref(narrow), C.byref(all_w), C.byref(q8k), p, p, 4, p, hook, None, None) == EINVAL
+    assert b"Q8_K form of the ffn norm" in lib.ds4b200_last_error()
     assert lib.ds4b200_path_create(None) is None
     from ds4cuda_b200._lib import PathConfig
     bad = PathConfig(n_tokens=0)
