@@ -465,12 +465,16 @@ def only_ops(tokens):
         return (lambda: ops.swiglu_q8_K_rows(gate, up, w, ops.GLU_CLAMP_REF, 10.0, fast_exp=True)), \
             T * TOP_K * (FF_DIM * 8 + FF_DIM + FF_DIM // 256 * 36), "expert epilogue leaving as Q8_K blocks"
 
+    def swiglu_q8_0():
+        gate, up = rnd(T, 1, FF_DIM), rnd(T, 1, FF_DIM)
+        return (lambda: ops.swiglu_q8_0_rows(gate, up)), T * (FF_DIM * 8 + FF_DIM + FF_DIM // 8), "shared expert's silu*up leaving as Q8_0 blocks"
+
     def quantize_q8_K():
         x = rnd(T * TOP_K, FF_DIM)
         return (lambda: ops.quantize_q8_K_rows(x)), T * TOP_K * (FF_DIM * 4 + FF_DIM + FF_DIM // 256 * 36), "Q8_K activation quantiser"
 
     for f in (hc_pre, hc_post_block, hc_head, rms_norm_cta, rms_norm_q8_0, rms_norm_q8_K, rms_norm_warp, rope_rows, rope_inverse,
-              rope_inverse_q8_0, rope_inverse_q8_0_table, rope_rows_table, rope_table, fp8_round_trip, rope_fp8_store, rope_fp8_store_table, swiglu_q8k, quantize_q8_K):
+              rope_inverse_q8_0, rope_inverse_q8_0_table, rope_rows_table, rope_table, fp8_round_trip, rope_fp8_store, rope_fp8_store_table, swiglu_q8k, swiglu_q8_0, quantize_q8_K):
         add(f.__name__, f)
     return reg
 
@@ -611,7 +615,7 @@ def layer_row_stages_leg(tokens, peak):
     resid_attn = stage("hc_attn_post", lambda: ops.hc_post_rows(attn_out, resid_hc, post_a, comb_a))
     post_f, comb_f, xf = stage("hc_ffn_pre", lambda: ops.hc_pre_rows(resid_attn, fn_f, scale3, base24))
     stage("ffn_norm+q8_0+q8_K", lambda: ops.rms_norm_q8_K_rows(xf, w_n, want_q8_0=True))
-    stage("shared_silu_mul", lambda: ops.swiglu_rows(sh_gate, sh_up))
+    stage("shared_silu_mul+q8_0", lambda: ops.swiglu_q8_0_rows(sh_gate, sh_up))
     stage("expert_swiglu+q8_K", lambda: ops.swiglu_q8_K_rows(gate, up, w_r, ops.GLU_CLAMP_REF, 10.0, fast_exp=True))
     stage("add+hc_ffn_post", lambda: ops.hc_post_rows(moe_out, resid_attn, post_f, comb_f, block_out2=shexp))
     # the same twelve stages through the one-call entry point (no-op hook: the stand-ins above are
@@ -627,7 +631,7 @@ def layer_row_stages_leg(tokens, peak):
                 mid_scale=z(T, TOP_K, FF_DIM // 256), mid_bsums=z(T, TOP_K, FF_DIM // 256, 16, dt=torch.int16),
                 moe_out=moe_out, shexp_out=shexp, kqv_q=z(T, 64, KV_DIM, dt=torch.int8), kqv_scale=z(T, 64, KV_DIM // 32),
                 rope_cs=z(T, N_ROT // 2, 2), ffn_kq=z(T, n, dt=torch.int8), ffn_kscale=z(T, n // 256),
-                ffn_kbsums=z(T, n // 16, dt=torch.int16))
+                ffn_kbsums=z(T, n // 16, dt=torch.int16), sh_q=z(T, FF_DIM, dt=torch.int8), sh_scale=z(T, FF_DIM // 32))
     wts = dict(hc_attn_fn=fn_a, hc_attn_scale=scale3, hc_attn_base=base24, attn_norm=w_n, q_a_norm=w_q, kv_a_norm=w_kv,
                hc_ffn_fn=fn_f, hc_ffn_scale=scale3, hc_ffn_base=base24, ffn_norm=w_n)
     dims = _lib.LayerDims(n, 64, KV_DIM, N_ROT, 1024, FF_DIM, TOP_K, 20, 2, 1, 1e-6, 10.0)

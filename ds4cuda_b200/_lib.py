@@ -55,7 +55,7 @@ class LayerBuffers(C.Structure):
     NAMES = ("x", "x_norm", "xq", "xscale", "q_lora", "q_lora_norm", "kv_raw", "raw_rows", "q", "kqv", "attn_out",
              "post", "comb", "resid_mid", "sh_gate", "sh_up", "sh_mid", "gate", "up", "router_w", "mid_q",
              "mid_scale", "mid_bsums", "moe_out", "shexp_out")
-    OPTIONAL = ("kqv_q", "kqv_scale", "rope_cs", "ffn_kq", "ffn_kscale", "ffn_kbsums")
+    OPTIONAL = ("kqv_q", "kqv_scale", "rope_cs", "ffn_kq", "ffn_kscale", "ffn_kbsums", "sh_q", "sh_scale")
     _fields_ = [(n, C.c_void_p) for n in NAMES + OPTIONAL]
 
 
@@ -124,6 +124,7 @@ SIGNATURES = {
     "ds4b200_layer_rows_f32": (_I, [C.POINTER(LayerDims), C.POINTER(LayerWeights), C.POINTER(LayerBuffers), _P, _P, _L, _P,
                                StageHook, _P, _P]),
     "ds4b200_swiglu_q8_K_rows_f32": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, C.c_float, _I, _P]),
+    "ds4b200_swiglu_q8_0_rows_f32": (_I, [_P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _F, _I, _P]),
     "ds4b200_compressor_chunk_f32": (_I, [_I, _P, _P, _P, _P, _I, _I, _I, _L, _I, _P, _P, _P, _P]),
     "ds4b200_compressor_step_f32": (_I, [_I, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, C.POINTER(C.c_int), _P]),
     "ds4b200_div_selfcheck": (_I, [C.c_uint64, C.c_uint64, _P, _P]),

@@ -510,6 +510,19 @@ int ds4b200_e4m3_decode_f32(const uint8_t *codes, float *x, int64_t n, void *str
     return launched("e4m3_decode");
 }
 
+int ds4b200_swiglu_q8_0_rows_f32(const float *gate, const float *up, const float *weights, int8_t *xq,
+                                 float *xscale, float *mid_f32, int64_t n_tokens, int k, int n, int mode,
+                                 float clamp, int fast_exp, void *stream) {
+    REQUIRE(n_tokens >= 0 && k >= 1 && n >= 32 && n % 32 == 0, "swiglu_q8_0_rows: n must be a multiple of 32, got %d", n);
+    if (n_tokens == 0) return 0;
+    REQUIRE(gate && up && xq && xscale, "swiglu_q8_0_rows: null pointer");
+    REQUIRE(mode >= DS4B200_GLU_PLAIN && mode <= DS4B200_GLU_CLAMP_SYM, "swiglu_q8_0_rows: unknown mode %d", mode);
+    REQUIRE(a16(gate) && a16(up) && a16(mid_f32) && a4(xq), "swiglu_q8_0_rows: pointers must be 16-byte aligned (xq: 4)");
+    ds4b200::swiglu_q8_0_rows(gate, up, weights, xq, xscale, mid_f32, n_tokens * k, n, mode, clamp, fast_exp,
+                              STREAM(stream));
+    return launched("swiglu_q8_0_rows");
+}
+
 int ds4b200_swiglu_q8_K_rows_f32(const float *gate, const float *up, const float *weights, int8_t *xq,
                                  float *xscale, int16_t *xbsums, float *mid_f32, int64_t n_tokens, int k,
                                  int n, int mode, float clamp, int fast_exp, void *stream) {

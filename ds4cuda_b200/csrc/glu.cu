@@ -151,6 +151,38 @@ swiglu_q8k_kernel(const float *__restrict__ gate, const float *__restrict__ up,
     }
 }
 
+// SwiGLU whose output leaves as Q8_0 blocks, the form the shared expert's down projection quantises its
+// activations to (launch_silu_mul_f32 at cuda/forward_layer.cu:1296, then the quantiser inside the Q8_0
+// matvec, cuda/dense_q8.cu:122-152).  A thread holds four values, a block of 32 is eight consecutive lanes;
+// n % 32 == 0, so the groups of eight lanes never straddle a row.  mid_f32 is optional.
+template <int MODE, bool FAST>
+__global__ void __launch_bounds__(256)
+swiglu_q8_0_kernel(const float *__restrict__ gate, const float *__restrict__ up, const float *__restrict__ weights,
+                   int8_t *__restrict__ xq, float *__restrict__ xscale, float *__restrict__ mid_f32, int64_t total4,
+                   int n4, float clamp) {
+    const int lane = threadIdx.x & 31;
+    // the loop bound is the warp's, not the thread's: the shuffles below want all 32 lanes
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i - lane < total4;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const bool live = i < total4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (live) {
+            v = glu4<MODE, FAST>(ld_stream4(gate + 4 * i), ld_stream4(up + 4 * i), clamp);
+            if (weights) v = mul4_rn(v, __ldg(weights + i / n4));
+            if (mid_f32) st_stream4(mid_f32 + 4 * i, v);
+        }
+        float amax = amax4(v);
+#pragma unroll
+        for (int off = 4; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+        float d, id;
+        q8_0_block_scale(amax, d, id);
+        if (live) {
+            reinterpret_cast<uint32_t *>(xq)[i] = q8_pack4_sat(v.x * id, v.y * id, v.z * id, v.w * id);
+            if ((i & 7) == 0) xscale[i >> 3] = d;
+        }
+    }
+}
+
 template <int MODE, bool FAST>
 __global__ void swiglu_scalar_kernel(const float *gate, const float *up, const float *weights,
                                      float *out, int64_t n_tokens, int k, int n, float clamp,
@@ -273,6 +305,21 @@ void swiglu_q8_K_rows(const float *gate, const float *up, const float *weights, 
     else if (mode == DS4B200_GLU_CLAMP_REF) { if (fast_exp) DS4B200_Q8K(DS4B200_GLU_CLAMP_REF, true); else DS4B200_Q8K(DS4B200_GLU_CLAMP_REF, false); }
     else { if (fast_exp) DS4B200_Q8K(DS4B200_GLU_CLAMP_SYM, true); else DS4B200_Q8K(DS4B200_GLU_CLAMP_SYM, false); }
 #undef DS4B200_Q8K
+}
+
+void swiglu_q8_0_rows(const float *gate, const float *up, const float *weights, int8_t *xq, float *xscale,
+                      float *mid_f32, int64_t n_rows, int n, int mode, float clamp, int fast_exp, cudaStream_t s) {
+    const int n4 = n >> 2;
+    const int64_t total4 = n_rows * n4;
+    if (total4 <= 0) return;
+    int64_t blocks = (total4 + 255) / 256;
+    if (blocks > (int64_t)1 << 30) blocks = (int64_t)1 << 30;
+#define DS4B200_Q80(M, F) swiglu_q8_0_kernel<M, F><<<(unsigned)blocks, 256, 0, s>>>(gate, up, weights, xq, xscale, \
+                                                                                   mid_f32, total4, n4, clamp)
+    if (mode == DS4B200_GLU_PLAIN) { if (fast_exp) DS4B200_Q80(DS4B200_GLU_PLAIN, true); else DS4B200_Q80(DS4B200_GLU_PLAIN, false); }
+    else if (mode == DS4B200_GLU_CLAMP_REF) { if (fast_exp) DS4B200_Q80(DS4B200_GLU_CLAMP_REF, true); else DS4B200_Q80(DS4B200_GLU_CLAMP_REF, false); }
+    else { if (fast_exp) DS4B200_Q80(DS4B200_GLU_CLAMP_SYM, true); else DS4B200_Q80(DS4B200_GLU_CLAMP_SYM, false); }
+#undef DS4B200_Q80
 }
 
 void swiglu_rows(const float *gate, const float *up, const float *weights, float *out,

@@ -123,6 +123,8 @@ void compressor_chunk(int is_attn, const float *kv_cur, const float *sc_cur, con
 void swiglu_q8_K_rows(const float *gate, const float *up, const float *weights, int8_t *xq, float *xscale,
                       int16_t *xbsums, float *mid_f32, int64_t n_rows, int n, int mode, float clamp,
                       int fast_exp, cudaStream_t s);
+void swiglu_q8_0_rows(const float *gate, const float *up, const float *weights, int8_t *xq, float *xscale,
+                      float *mid_f32, int64_t n_rows, int n, int mode, float clamp, int fast_exp, cudaStream_t s);
 void div_selfcheck(uint64_t first, uint64_t count, unsigned long long *mismatches, cudaStream_t s);
 void e4m3_encode(const float *x, uint8_t *codes, int64_t n, cudaStream_t s);
 void e4m3_decode(const uint8_t *codes, float *x, int64_t n, cudaStream_t s);

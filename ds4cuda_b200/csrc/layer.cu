@@ -48,6 +48,11 @@ extern "C" int ds4b200_layer_rows_f32(const ds4b200_layer_dims *d, const ds4b200
                       (reinterpret_cast<uintptr_t>(w->ffn_norm) & 15u)))
         return set_error(-EINVAL, "layer_rows: the Q8_K form of the ffn norm needs n_embd % 256 == 0 and aligned rows");
 
+    if (!b->sh_q != !b->sh_scale) return set_error(-EINVAL, "layer_rows: sh_q and sh_scale go together");
+    if (b->sh_q && (d->ff_dim % 32 || (reinterpret_cast<uintptr_t>(b->sh_q) & 3u) ||
+                    (reinterpret_cast<uintptr_t>(b->sh_gate) & 15u) || (reinterpret_cast<uintptr_t>(b->sh_up) & 15u)))
+        return set_error(-EINVAL, "layer_rows: the Q8_0 form of the shared expert's rows needs aligned rows");
+
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int n = d->n_embd, hd = d->head_dim;
     ds4b200_rope_params rope;
@@ -96,7 +101,11 @@ extern "C" int ds4b200_layer_rows_f32(const ds4b200_layer_dims *d, const ds4b200
                            b->xscale, b->ffn_kq, b->ffn_kscale, b->ffn_kbsums);
     if ((rc = launch_ok("hc attn post / hc ffn pre / ffn norm"))) return rc;
     if ((rc = call(DS4B200_STAGE_FFN_UP))) return rc;
-    ds4b200::swiglu_rows(b->sh_gate, b->sh_up, nullptr, b->sh_mid, T, 1, d->ff_dim, DS4B200_GLU_PLAIN, 0.0f, 0, 0, s);
+    if (b->sh_q)       // straight into the shared down projection's activation blocks
+        ds4b200::swiglu_q8_0_rows(b->sh_gate, b->sh_up, nullptr, b->sh_q, b->sh_scale, nullptr, T, d->ff_dim,
+                                  DS4B200_GLU_PLAIN, 0.0f, 0, s);
+    else
+        ds4b200::swiglu_rows(b->sh_gate, b->sh_up, nullptr, b->sh_mid, T, 1, d->ff_dim, DS4B200_GLU_PLAIN, 0.0f, 0, 0, s);
     ds4b200::swiglu_q8_K_rows(b->gate, b->up, b->router_w, b->mid_q, b->mid_scale, b->mid_bsums, nullptr,
                               T * d->top_k, d->ff_dim, DS4B200_GLU_CLAMP_REF, d->clamp, d->glu_fast_exp, s);
     if ((rc = launch_ok("shared silu / routed epilogue"))) return rc;

@@ -271,6 +271,17 @@ def swiglu_rows(gate, up, weights=None, mode=GLU_PLAIN, clamp=0.0, combine=False
     return out
 
 
+def swiglu_q8_0_rows(gate, up, weights=None, mode=GLU_PLAIN, clamp=0.0, fast_exp=False, want_f32=False):
+    """gate/up [T, k, n] -> (xq int8 [T, k, n], xscale [T, k, n/32], mid f32 or None): the SwiGLU rows as Q8_0 blocks."""
+    T, k, n = gate.shape
+    xq = torch.empty((T, k, n), dtype=torch.int8, device=gate.device)
+    xs = torch.empty((T, k, n // 32), dtype=torch.float32, device=gate.device)
+    mid = torch.empty((T, k, n), dtype=torch.float32, device=gate.device) if want_f32 else None
+    check(_lib.load().ds4b200_swiglu_q8_0_rows_f32(_p(gate), _p(up), _p(weights), _p(xq), _p(xs), _p(mid), T, k, n, mode,
+                                                   clamp, int(fast_exp), _s()))
+    return xq, xs, mid
+
+
 def hc_pre_rows(resid, fn_f16, scale3, base24, iters=20, eps=1e-6):
     """resid [T, 4, n]; fn_f16 [24, 4n] float16.  Returns (post [T,4], comb [T,16], out [T,n])."""
     T, _, n = resid.shape

@@ -287,6 +287,16 @@ int ds4b200_swiglu_q8_K_rows_f32(const float *gate, const float *up, const float
                                  float *xscale, int16_t *xbsums, float *mid_f32, int64_t n_tokens, int k,
                                  int n, int mode, float clamp, int fast_exp, void *stream);
 
+/* SwiGLU whose output leaves as Q8_0 blocks, the form the shared expert's down projection
+ * quantises its activations to (launch_silu_mul_f32 at cuda/forward_layer.cu:1296, then the
+ * quantiser inside the Q8_0 matvec, cuda/dense_q8.cu:122-152): per 32 elements d = amax/127,
+ * q = clamp(rint(v/d)), exactly as ds4b200_quantize_q8_0_rows_f32 would quantise the f32 rows.
+ * gate, up [n_tokens][k][n]; weights [n_tokens][k] nullable; xq int8 [n_tokens*k*n]; xscale
+ * [n_tokens*k*n/32]; mid_f32 nullable (also writes the f32 rows).  n a multiple of 32. */
+int ds4b200_swiglu_q8_0_rows_f32(const float *gate, const float *up, const float *weights, int8_t *xq,
+                                 float *xscale, float *mid_f32, int64_t n_tokens, int k, int n, int mode,
+                                 float clamp, int fast_exp, void *stream);
+
 /* One streaming-compressor step after its two projections: everything
  * launch_compressor_decode_step_f32{,_prealloc} (cuda/compressor.cuh:78,102; cuda/compressor.cu:328-420)
  * does once kv_cur / sc_cur = W_kv x, W_gate x are known, in one launch.

@@ -101,6 +101,11 @@ typedef struct ds4b200_layer_buffers {      /* caller-owned device workspace for
     int8_t *ffn_kq;                         /* [T][n_embd] */
     float *ffn_kscale;                      /* [T][n_embd/256] */
     int16_t *ffn_kbsums;                    /* [T][n_embd/256][16] */
+    /* Optional (both or neither; ff_dim % 32 == 0): the shared expert's silu(gate) * up leaves as the Q8_0
+     * blocks its down projection quantises the row to (cuda/forward_layer.cu:1296, then the quantiser
+     * inside the Q8_0 matvec, cuda/dense_q8.cu:122-152) and sh_mid is NOT written. */
+    int8_t *sh_q;                           /* [T][ff_dim] */
+    float *sh_scale;                        /* [T][ff_dim/32] */
 } ds4b200_layer_buffers;
 
 /* Called on the issuing thread between row stages; must enqueue its work on `stream` (or

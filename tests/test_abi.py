@@ -149,6 +149,10 @@ def test_checked_entry_points_reject_bad_arguments_without_a_gpu(lib):
     assert lib.ds4b200_hc_post_rows_f32(p, None, p, None, p, p, 2, 4096, None) == EINVAL
     assert lib.ds4b200_hc_post_rows_f32(None, p, p, None, p, p, 2, 4096, None) == EINVAL
     assert lib.ds4b200_hc_sinkhorn_mix_rows_f32(None, p, p, None, 2, 4096, 20, 1e-6, None) == EINVAL
+    assert lib.ds4b200_swiglu_q8_0_rows_f32(p, p, None, p, p, None, 2, 1, 2000, 0, 0.0, 0, None) == EINVAL   # n % 32
+    assert lib.ds4b200_swiglu_q8_0_rows_f32(p, p, None, None, p, None, 2, 1, 2048, 0, 0.0, 0, None) == EINVAL
+    assert lib.ds4b200_swiglu_q8_0_rows_f32(p, p, None, p, p, None, 2, 1, 2048, 9, 0.0, 0, None) == EINVAL   # mode
+    assert lib.ds4b200_swiglu_q8_0_rows_f32(p, p, None, p, p, None, 0, 1, 2048, 0, 0.0, 0, None) == 0
     assert lib.ds4b200_swiglu_q8_K_rows_f32(p, p, None, p, p, p, None, 2, 6, 2000, 1, 10.0, 1, None) == EINVAL
     assert b"256" in lib.ds4b200_last_error()
     assert lib.ds4b200_swiglu_q8_K_rows_f32(p, p, None, None, p, p, None, 2, 6, 2048, 1, 10.0, 1, None) == EINVAL
@@ -181,6 +185,9 @@ def test_checked_entry_points_reject_bad_arguments_without_a_gpu(lib):
     two_of_three = LayerBuffers(**full, ffn_kq=a, ffn_kbsums=a)
     assert lib.ds4b200_layer_rows_f32(C.byref(dims), C.byref(all_w), C.byref(two_of_three), p, p, 4, p, hook, None, None) == EINVAL
     assert b"ffn_kq, ffn_kscale and ffn_kbsums go together" in lib.ds4b200_last_error()
+    lone = LayerBuffers(**full, sh_q=a)
+    assert lib.ds4b200_layer_rows_f32(C.byref(dims), C.byref(all_w), C.byref(lone), p, p, 4, p, hook, None, None) == EINVAL
+    assert b"sh_q and sh_scale go together" in lib.ds4b200_last_error()
     narrow = LayerDims(4096 + 32, 64, 512, 64, 1024, 2048, 6, 20, 2, 1, 1e-6, 10.0)      # not a multiple of 256
     q8k = LayerBuffers(**full, ffn_kq=a, ffn_kscale=a, ffn_kbsums=a)
     assert lib.ds4b200_layer_rows_f32(C.byref(narrow), C.byref(all_w), C.byref(q8k), p, p, 4, p, hook, None, None) == EINVAL

@@ -197,6 +197,7 @@ def test_batched_layer_with_reference_matvecs_in_the_hook_against_the_reference_
     ffn_kq, ffn_ks = i8(T, N), f32(T, N // 256)                            # the ffn norm's row as Q8_K blocks
     ffn_kb = torch.zeros(T, N // 16, dtype=torch.int16, device="cuda")
     ref_ffn_k = []                                                         # what the reference's quantiser made of each row
+    ref_sh_q = []                                                          # the same for the shared expert's silu(gate) * up
     sxq, sxs = i8(H * HD), f32(H * HD // 32)                               # Q8_0 scratch of the matvec launchers
     kxq, kxs, kxb = i8(K * FF), f32(K * FF // 256), torch.zeros(K * FF // 256 * 16, dtype=torch.int16, device="cuda")
     window, attn_low = f32(128, HD), f32(T, LOW)
@@ -256,6 +257,7 @@ def test_batched_layer_with_reference_matvecs_in_the_hook_against_the_reference_
             snap["mid"] = ops.swiglu_rows(B["gate"], B["up"], B["router_w"], ops.GLU_CLAMP_REF, 10.0, fast_exp=True)
             for t in range(T):
                 matvec("ffn_down_shexp.weight", B["sh_mid"][t], B["shexp_out"][t], N, FF)
+                ref_sh_q.append((sxq[:FF].clone(), sxs[:FF // 32].clone()))    # what its quantiser made of the row
                 ref.call("routed_moe_q2k_sum6_full_f32_prealloc", blob["ffn_down_exps.weight"], snap["mid"][t], ids[t],
                          B["moe_out"][t], K, N, FF, NEXP, kxq, kxs, kxb)
         return 0
@@ -281,6 +283,13 @@ def test_batched_layer_with_reference_matvecs_in_the_hook_against_the_reference_
     for t in range(T):
         rq, rs, rb = ref_ffn_k[t]
         assert torch.equal(ffn_kq[t], rq) and torch.equal(ffn_ks[t], rs) and torch.equal(ffn_kb[t], rb), t
+
+    # ------------------------------------------------------------ the shared expert's rows as Q8_0 blocks (the fused
+    # form of silu(gate) * up) == what the reference's down projection quantised for itself, token by token
+    shq, shs, _ = ops.swiglu_q8_0_rows(B["sh_gate"], B["sh_up"])
+    for t in range(T):
+        rq, rs = ref_sh_q[t]
+        assert torch.equal(shq[t, 0], rq) and torch.equal(shs[t, 0], rs), t
 
     # ------------------------------------------------------------ the routed epilogue's Q8_K blocks == what the reference's
     # down-projection quantised for itself from the same f32 rows (its scratch still holds the last token's)

@@ -1055,6 +1055,30 @@ def test_swiglu_with_fused_q8_K(ops, oracle, T, k, n, fast):
     assert_bits(host(bs2), host(bs), "sums, no f32 rows")
 
 
+@pytest.mark.parametrize("T,k,n,mode,fast", [(3, 1, 2048, "plain", False), (300, 1, 2048, "plain", False),
+                                             (7, 1, 32, "plain", False), (5, 6, 96, "clamp", True), (1, 1, 2048, "plain", False)])
+def test_swiglu_with_fused_q8_0(ops, oracle, T, k, n, mode, fast):
+    """SwiGLU whose rows leave as Q8_0 blocks (the shared expert's silu(gate) * up ahead of its Q8_0 down
+    projection): the f32 rows are swiglu_rows' rows and the blocks are the quantiser's on those rows, bit for bit."""
+    g = inputs.rng(960 + T + n)
+    gate, up = inputs.normal(g, (T, k, n), 2.0), inputs.normal(g, (T, k, n), 2.0)
+    gate[0, 0, :32] = 0.0                                   # an all-zero block: scale 0, values 0
+    w = inputs.router_weights(g, T, k) if mode == "clamp" else None
+    m, c = (ops.GLU_CLAMP_REF, 10.0) if mode == "clamp" else (ops.GLU_PLAIN, 0.0)
+    dw = dev(w) if w is not None else None
+    xq, xs, mid = ops.swiglu_q8_0_rows(dev(gate), dev(up), dw, m, c, fast_exp=fast, want_f32=True)
+    plain = ops.swiglu_rows(dev(gate), dev(up), dw, m, c, False, fast)
+    assert_bits(host(mid), host(plain), "f32 rows of the fused kernel vs swiglu_rows")
+    wq, ws = oracle.quantize_q8_0_rows(host(mid).ravel())
+    assert_bits(host(xs).ravel(), ws, "Q8_0 scales")
+    assert_bits(host(xq).ravel(), wq, "Q8_0 values")
+    assert host(xs)[0, 0, 0] == 0.0 and not host(xq)[0, 0, :32].any()
+    q2, s2 = ops.quantize_q8_0_rows(plain)
+    assert torch.equal(q2, xq) and torch.equal(s2.view_as(xs), xs)
+    xq3, xs3, none = ops.swiglu_q8_0_rows(dev(gate), dev(up), dw, m, c, fast_exp=fast)
+    assert none is None and torch.equal(xq3, xq) and torch.equal(xs3, xs)
+
+
 def test_activation_quantisers_equal_the_reference_kernels(ops, ref):
     """Q8_K against the reference's launcher, Q8_0 against what its Q8_0 matvec leaves in the caller's
     scratch (cuda/moe_iq2_pair.cu:159-235, cuda/dense_q8.cu:122-168): bit for bit."""
