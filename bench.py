@@ -605,7 +605,7 @@ def layer_row_stages_leg(tokens, peak):
 
     post_a, comb_a, x = stage("hc_attn_pre", lambda: ops.hc_pre_rows(resid_hc, fn_a, scale3, base24))
     stage("attn_norm+q8_0", lambda: ops.rms_norm_q8_0_rows(x, w_n))
-    stage("q_a_norm", lambda: ops.rms_norm_rows(q_lora, w_q))
+    stage("q_a_norm+q8_0", lambda: ops.rms_norm_q8_0_rows(q_lora, w_q))
     # the KV row chain evaluates the 32 angles of its token anyway: it leaves them as the chunk's angle table
     table = torch.zeros(T, N_ROT // 2, 2, device=dev)
     stage("kv_norm+rope+fp8+f16+angle_table", lambda: ops.kv_rows_to_raw(kv_raw, pos, rope, raw_rows, norm_w=w_kv,
@@ -631,7 +631,8 @@ def layer_row_stages_leg(tokens, peak):
                 mid_scale=z(T, TOP_K, FF_DIM // 256), mid_bsums=z(T, TOP_K, FF_DIM // 256, 16, dt=torch.int16),
                 moe_out=moe_out, shexp_out=shexp, kqv_q=z(T, 64, KV_DIM, dt=torch.int8), kqv_scale=z(T, 64, KV_DIM // 32),
                 rope_cs=z(T, N_ROT // 2, 2), ffn_kq=z(T, n, dt=torch.int8), ffn_kscale=z(T, n // 256),
-                ffn_kbsums=z(T, n // 16, dt=torch.int16), sh_q=z(T, FF_DIM, dt=torch.int8), sh_scale=z(T, FF_DIM // 32))
+                ffn_kbsums=z(T, n // 16, dt=torch.int16), sh_q=z(T, FF_DIM, dt=torch.int8), sh_scale=z(T, FF_DIM // 32),
+                ql_q=z(T, 1024, dt=torch.int8), ql_scale=z(T, 32))
     wts = dict(hc_attn_fn=fn_a, hc_attn_scale=scale3, hc_attn_base=base24, attn_norm=w_n, q_a_norm=w_q, kv_a_norm=w_kv,
                hc_ffn_fn=fn_f, hc_ffn_scale=scale3, hc_ffn_base=base24, ffn_norm=w_n)
     dims = _lib.LayerDims(n, 64, KV_DIM, N_ROT, 1024, FF_DIM, TOP_K, 20, 2, 1, 1e-6, 10.0)

@@ -55,7 +55,7 @@ class LayerBuffers(C.Structure):
     NAMES = ("x", "x_norm", "xq", "xscale", "q_lora", "q_lora_norm", "kv_raw", "raw_rows", "q", "kqv", "attn_out",
              "post", "comb", "resid_mid", "sh_gate", "sh_up", "sh_mid", "gate", "up", "router_w", "mid_q",
              "mid_scale", "mid_bsums", "moe_out", "shexp_out")
-    OPTIONAL = ("kqv_q", "kqv_scale", "rope_cs", "ffn_kq", "ffn_kscale", "ffn_kbsums", "sh_q", "sh_scale")
+    OPTIONAL = ("kqv_q", "kqv_scale", "rope_cs", "ffn_kq", "ffn_kscale", "ffn_kbsums", "sh_q", "sh_scale", "ql_q", "ql_scale")
     _fields_ = [(n, C.c_void_p) for n in NAMES + OPTIONAL]
 
 

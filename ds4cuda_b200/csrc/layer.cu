@@ -53,6 +53,16 @@ extern "C" int ds4b200_layer_rows_f32(const ds4b200_layer_dims *d, const ds4b200
                     (reinterpret_cast<uintptr_t>(b->sh_gate) & 15u) || (reinterpret_cast<uintptr_t>(b->sh_up) & 15u)))
         return set_error(-EINVAL, "layer_rows: the Q8_0 form of the shared expert's rows needs aligned rows");
 
+    auto misaligned = [](const void *p, uintptr_t mask) { return (reinterpret_cast<uintptr_t>(p) & mask) != 0; };
+    // the norms that leave Q8_0 blocks run as the vector kernels only: rows and gains on 16 bytes
+    if (misaligned(b->x, 15) || misaligned(b->x_norm, 15) || misaligned(w->attn_norm, 15) || misaligned(w->ffn_norm, 15) ||
+        misaligned(b->xq, 3))
+        return set_error(-EINVAL, "layer_rows: x, x_norm and the norm gains need 16-byte alignment, xq 4-byte");
+    if (!b->ql_q != !b->ql_scale) return set_error(-EINVAL, "layer_rows: ql_q and ql_scale go together");
+    if (b->ql_q && (d->q_lora % 32 || d->q_lora > 8192 || misaligned(b->ql_q, 3) || misaligned(b->q_lora, 15) ||
+                    misaligned(b->q_lora_norm, 15) || misaligned(w->q_a_norm, 15)))
+        return set_error(-EINVAL, "layer_rows: the Q8_0 form of the q_a norm needs q_lora % 32 == 0 and aligned rows");
+
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int n = d->n_embd, hd = d->head_dim;
     ds4b200_rope_params rope;
@@ -74,7 +84,7 @@ extern "C" int ds4b200_layer_rows_f32(const ds4b200_layer_dims *d, const ds4b200
     if ((rc = launch_ok("hc attn pre / attn norm"))) return rc;
     if ((rc = call(DS4B200_STAGE_QKV_A))) return rc;
     ds4b200::rms_norm_rows(b->q_lora, nullptr, w->q_a_norm, d->q_lora, b->q_lora_norm, nullptr, nullptr, T, d->q_lora,
-                           d->eps, s);
+                           d->eps, s, b->ql_q, b->ql_scale);
     ds4b200::rope_fp8_store_rows(b->kv_raw, T, hd, d->n_rot, pos, &rope, w->kv_a_norm, d->eps,
                                  DS4B200_FP8_BLOCK64_POW2, nullptr, nullptr, nullptr, nullptr, nullptr, s,
                                  b->raw_rows, nullptr, cs ? b->rope_cs : nullptr);

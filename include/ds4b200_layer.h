@@ -106,6 +106,10 @@ typedef struct ds4b200_layer_buffers {      /* caller-owned device workspace for
      * inside the Q8_0 matvec, cuda/dense_q8.cu:122-152) and sh_mid is NOT written. */
     int8_t *sh_q;                           /* [T][ff_dim] */
     float *sh_scale;                        /* [T][ff_dim/32] */
+    /* Optional (both or neither; q_lora % 32 == 0): the q_a norm also leaves its row as the Q8_0 blocks
+     * the q_b projection quantises it to (cuda/forward_layer.cu:879 through cuda/dense_q8.cu:122-152). */
+    int8_t *ql_q;                           /* [T][q_lora] */
+    float *ql_scale;                        /* [T][q_lora/32] */
 } ds4b200_layer_buffers;
 
 /* Called on the issuing thread between row stages; must enqueue its work on `stream` (or

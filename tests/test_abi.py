@@ -188,6 +188,12 @@ def test_checked_entry_points_reject_bad_arguments_without_a_gpu(lib):
     lone = LayerBuffers(**full, sh_q=a)
     assert lib.ds4b200_layer_rows_f32(C.byref(dims), C.byref(all_w), C.byref(lone), p, p, 4, p, hook, None, None) == EINVAL
     assert b"sh_q and sh_scale go together" in lib.ds4b200_last_error()
+    lone = LayerBuffers(**full, ql_scale=a)
+    assert lib.ds4b200_layer_rows_f32(C.byref(dims), C.byref(all_w), C.byref(lone), p, p, 4, p, hook, None, None) == EINVAL
+    assert b"ql_q and ql_scale go together" in lib.ds4b200_last_error()
+    skewed = LayerBuffers(**{**full, "x_norm": a + 4})
+    assert lib.ds4b200_layer_rows_f32(C.byref(dims), C.byref(all_w), C.byref(skewed), p, p, 4, p, hook, None, None) == EINVAL
+    assert b"16-byte alignment" in lib.ds4b200_last_error()
     narrow = LayerDims(4096 + 32, 64, 512, 64, 1024, 2048, 6, 20, 2, 1, 1e-6, 10.0)      # not a multiple of 256
     q8k = LayerBuffers(**full, ffn_kq=a, ffn_kscale=a, ffn_kbsums=a)
     assert lib.ds4b200_layer_rows_f32(C.byref(narrow), C.byref(all_w), C.byref(q8k), p, p, 4, p, hook, None, None) == EINVAL

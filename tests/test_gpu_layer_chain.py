@@ -183,13 +183,15 @@ def test_layer_rows_entry_point_sequences_the_same_chain(ops):
     kq = torch.zeros(T, H, hd, dtype=torch.int8, device="cuda")
     ks = torch.zeros(T, H, hd // 32, device="cuda")
     cs = torch.zeros(T, 32, 2, device="cuda")       # and the angle table: same bits in every RoPE stage
+    qlq = torch.zeros(T, ql, dtype=torch.int8, device="cuda")     # the q_a norm's row as Q8_0 blocks
+    qls = torch.zeros(T, ql // 32, device="cuda")
     shq = torch.zeros(T, ff, dtype=torch.int8, device="cuda")     # the shared expert's rows as Q8_0 blocks, no f32
     shs = torch.zeros(T, ff // 32, device="cuda")
     fkq = torch.zeros(T, n, dtype=torch.int8, device="cuda")      # and the ffn norm's row as Q8_K blocks
     fks, fkb = torch.zeros(T, n // 256, device="cuda"), torch.zeros(T, n // 16, dtype=torch.int16, device="cuda")
     buffers_q = _lib.LayerBuffers(*[B[nm].data_ptr() for nm in _lib.LayerBuffers.NAMES], kq.data_ptr(), ks.data_ptr(),
                                   cs.data_ptr(), fkq.data_ptr(), fks.data_ptr(), fkb.data_ptr(), shq.data_ptr(),
-                                  shs.data_ptr())
+                                  shs.data_ptr(), qlq.data_ptr(), qls.data_ptr())
     out_q = torch.zeros(T, 4, n, device="cuda")
     B["sh_mid"].fill_(-7.0)                          # must stay untouched when the Q8_0 form is asked for
     rc = L.ds4b200_layer_rows_f32(C.byref(dims), C.byref(weights), C.byref(buffers_q), resid_hc.data_ptr(),
@@ -201,6 +203,9 @@ def test_layer_rows_entry_point_sequences_the_same_chain(ops):
     eq(B["kqv"], S["kqv"], "kqv left as the attention stage wrote it"); eq(out_q, want, "residual streams (Q8_0 form)")
     eq(B["q"], q_cur, "q norm + RoPE from the table"); eq(B["raw_rows"], raw, "raw KV rows from the table")
     eq(cs, ops.rope_table_rows(pos, p), "angle table")
+    wlq, wls = ops.quantize_q8_0_rows(qn)
+    eq(qlq.view(-1), wlq.view(-1), "q_a norm Q8_0 values"); eq(qls.view(-1), wls.view(-1), "q_a norm Q8_0 scales")
+    eq(B["q_lora_norm"], qn, "q_a norm beside its Q8_0 form")
     wsq, wss = ops.quantize_q8_0_rows(sh)
     eq(shq.view(-1), wsq.view(-1), "shared silu*up Q8_0 values"); eq(shs.view(-1), wss.view(-1), "shared silu*up Q8_0 scales")
     assert bool((B["sh_mid"] == -7.0).all()), "sh_mid rewritten beside its Q8_0 form"

@@ -196,7 +196,9 @@ def test_batched_layer_with_reference_matvecs_in_the_hook_against_the_reference_
              moe_out=f32(T, N), shexp_out=f32(T, N))
     ffn_kq, ffn_ks = i8(T, N), f32(T, N // 256)                            # the ffn norm's row as Q8_K blocks
     ffn_kb = torch.zeros(T, N // 16, dtype=torch.int16, device="cuda")
+    ql_q, ql_s = i8(T, QL), f32(T, QL // 32)                               # the q_a norm's row as Q8_0 blocks
     ref_ffn_k = []                                                         # what the reference's quantiser made of each row
+    ref_ql_q = []                                                          # ... for the q_a norm's row (q_b projection)
     ref_sh_q = []                                                          # the same for the shared expert's silu(gate) * up
     sxq, sxs = i8(H * HD), f32(H * HD // 32)                               # Q8_0 scratch of the matvec launchers
     kxq, kxs, kxb = i8(K * FF), f32(K * FF // 256), torch.zeros(K * FF // 256 * 16, dtype=torch.int16, device="cuda")
@@ -228,6 +230,7 @@ def test_batched_layer_with_reference_matvecs_in_the_hook_against_the_reference_
         elif stage == _lib.STAGE_Q_B:                                      # :879
             for t in range(T):
                 matvec("attn_q_b.weight", B["q_lora_norm"][t], B["q"][t], H * HD, QL)
+                ref_ql_q.append((sxq[:QL].clone(), sxs[:QL // 32].clone()))     # what its quantiser made of the row
         elif stage == _lib.STAGE_ATTENTION:                                # :950 (push), :1166 (raw-SWA attention)
             snap["q_cur"] = B["q"].clone()
             for t in range(T):
@@ -269,7 +272,8 @@ def test_batched_layer_with_reference_matvecs_in_the_hook_against_the_reference_
     dims = _lib.LayerDims(N, H, HD, 64, QL, FF, K, 20, il, 1, 1e-6, 10.0)
     weights = _lib.LayerWeights(*[blob[w_names[nm]].data_ptr() for nm in _lib.LayerWeights.NAMES])
     buffers = _lib.LayerBuffers(*[B[nm].data_ptr() for nm in _lib.LayerBuffers.NAMES], None, None, None,
-                                ffn_kq.data_ptr(), ffn_ks.data_ptr(), ffn_kb.data_ptr())
+                                ffn_kq.data_ptr(), ffn_ks.data_ptr(), ffn_kb.data_ptr(), None, None,
+                                ql_q.data_ptr(), ql_s.data_ptr())
     got = f32(T, 4, N)
     cb = _lib.StageHook(hook)
     rc = L.ds4b200_layer_rows_f32(C.byref(dims), C.byref(weights), C.byref(buffers), resid_in.data_ptr(), pos.data_ptr(),
@@ -283,6 +287,12 @@ def test_batched_layer_with_reference_matvecs_in_the_hook_against_the_reference_
     for t in range(T):
         rq, rs, rb = ref_ffn_k[t]
         assert torch.equal(ffn_kq[t], rq) and torch.equal(ffn_ks[t], rs) and torch.equal(ffn_kb[t], rb), t
+
+    # ------------------------------------------------------------ the q_a norm's Q8_0 blocks == what the reference's q_b
+    # projection quantised for itself from the same row, token by token
+    for t in range(T):
+        rq, rs = ref_ql_q[t]
+        assert torch.equal(ql_q[t], rq) and torch.equal(ql_s[t], rs), t
 
     # ------------------------------------------------------------ the shared expert's rows as Q8_0 blocks (the fused
     # form of silu(gate) * up) == what the reference's down projection quantised for itself, token by token
