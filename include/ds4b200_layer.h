@@ -10,7 +10,7 @@
  *   hc attn pre        resid_in -> x, post, comb                       (:808)
  *   attn norm + Q8_0   x -> x_norm, xq, xscale                        (:822, dense_q8.cu:122)
  *   QKV_A              caller: x_norm / xq -> q_lora, kv_raw           (:833, :856)
- *   q_a norm           q_lora -> q_lora_norm                           (:845)
+ *   q_a norm           q_lora -> q_lora_norm (+ ql_q, ql_scale: Q8_0)  (:845)
  *   kv chain           kv_raw -> raw_rows (norm, RoPE, FP8, f16)       (:868, :910, :921, :950)
  *   Q_B                caller: q_lora_norm -> q                        (:879)
  *   q norm + RoPE      q in place                                      (:890, :901)
@@ -19,9 +19,9 @@
  *   ATTN_OUT           caller: kqv -> attn_out                         (:1190, :1205)
  *   hc attn post       attn_out, resid_in, post, comb -> resid_mid     (:1217)
  *   hc ffn pre         resid_mid -> x, post, comb                      (:1235)
- *   ffn norm + Q8_0    x -> x_norm, xq, xscale                        (:1249)
+ *   ffn norm + Q8_0    x -> x_norm, xq, xscale (+ ffn_kq...: Q8_K)    (:1249, moe_iq2_pair.cu:404)
  *   FFN_UP             caller: x_norm / xq -> sh_gate, sh_up, gate, up, router_w   (:1260-1350)
- *   shared silu*up     sh_gate, sh_up -> sh_mid                        (:1285)
+ *   shared silu*up     sh_gate, sh_up -> sh_mid, or -> sh_q, sh_scale (Q8_0)       (:1285)
  *   routed epilogue    gate, up, router_w -> mid_q, mid_scale, mid_bsums (Q8_K)    (moe_iq2_pair.cu:352, :159)
  *   FFN_DOWN           caller: sh_mid, mid_q... -> shexp_out, moe_out  (:1296, :1416)
  *   add + hc ffn post  moe_out + shexp_out, resid_mid, post, comb -> resid_out     (:1447, :1456)
