@@ -115,6 +115,7 @@ SIGNATURES = {
     "ds4b200_hc_pre_norm_rows_f32": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _F, _P]),
     "ds4b200_output_hc_head_rows_f32": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _I, _F, _P]),
     "ds4b200_hc_post_rows_f32": (_I, [_P, _P, _P, _P, _P, _P, _L, _I, _P]),
+    "ds4b200_hc_post_pre_rows_f32": (_I, [_P] * 12 + [_L, _I, _I, _F, _P]),
     "ds4b200_hc_sinkhorn_rows_f32": (_I, [_P, _P, _L, _I, _F, _P]),
     "ds4b200_hc_sinkhorn_mix_rows_f32": (_I, [_P, _P, _P, _P, _L, _I, _I, _F, _P]),
     "ds4b200_hc_sinkhorn_mix_rows_static_f32": (_I, [_P, _P, _P, _L, _I, _I, _F, _P]),

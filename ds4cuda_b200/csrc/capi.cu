@@ -462,6 +462,32 @@ int ds4b200_hc_post_rows_f32(const float *block_out, const float *block_out2,
     return launched("hc_post_rows");
 }
 
+int ds4b200_hc_post_pre_rows_f32(const float *block_out, const float *block_out2, const float *residual_hc,
+                                 const float *post_in, const float *comb_in, const uint16_t *hc_fn,
+                                 const float *hc_scale, const float *hc_base, float *out_hc, float *post, float *comb,
+                                 float *out, int64_t n_tokens, int n_embd, int sinkhorn_iters, float eps,
+                                 void *stream) {
+    REQUIRE(n_tokens >= 0, "hc_post_pre_rows: n_tokens < 0");
+    if (n_tokens == 0) return 0;
+    REQUIRE(n_tokens < ((int64_t)1 << 31), "hc_post_pre_rows: n_tokens >= 2^31");
+    REQUIRE(residual_hc && comb_in && out_hc && hc_fn && hc_scale && hc_base && post && comb && out,
+            "hc_post_pre_rows: null pointer");
+    REQUIRE(!block_out || post_in, "hc_post_pre_rows: block_out without post_in");
+    REQUIRE(!block_out2 || block_out, "hc_post_pre_rows: block_out2 without block_out");
+    REQUIRE(n_embd > 0 && n_embd % 4 == 0 && n_embd <= 8192,
+            "hc_post_pre_rows: n_embd must be a multiple of 4, at most 8192");
+    REQUIRE(sinkhorn_iters >= 1, "hc_post_pre_rows: sinkhorn_iters < 1");
+    REQUIRE(out_hc != residual_hc && out != block_out, "hc_post_pre_rows: outputs alias inputs of the first step");
+    // two launches: the post step's rows go through HBM once more.  A one-kernel form would put the post
+    // arithmetic (80 multiply-adds per 16 bytes) into the operand-writing warps of the pre kernel, which are
+    // its longest stage already, and that kernel does not wait for memory.
+    ds4b200::hc_post_rows(block_out, block_out2, residual_hc, post_in, comb_in, nullptr, nullptr, out_hc, n_tokens,
+                          n_embd, 0, 0.0f, STREAM(stream));
+    ds4b200::hc_pre_rows(out_hc, hc_fn, hc_scale, hc_base, post, comb, out, n_tokens, n_embd, sinkhorn_iters, eps,
+                         STREAM(stream));
+    return launched("hc_post_pre_rows");
+}
+
 int ds4b200_hc_sinkhorn_mix_rows_f32(const float *logits, const float *residual_hc, float *out_hc,
                                      float *comb_out, int64_t n_tokens, int n_embd,
                                      int sinkhorn_iters, float eps, void *stream) {

@@ -329,6 +329,20 @@ def hc_post_rows(block_out, resid, post, comb, block_out2=None):
     return out
 
 
+def hc_post_pre_rows(block_out, resid, post, comb, fn_f16, scale3, base24, block_out2=None, iters=20, eps=1e-6):
+    """hc_post_rows then hc_pre_rows of its result.  Returns (out_hc [T,4,n], post [T,4], comb [T,16], out [T,n])."""
+    T, _, n = resid.shape
+    dev = resid.device
+    out_hc = torch.empty_like(resid)
+    post2 = torch.empty((T, 4), dtype=torch.float32, device=dev)
+    comb2 = torch.empty((T, 16), dtype=torch.float32, device=dev)
+    out = torch.empty((T, n), dtype=torch.float32, device=dev)
+    check(_lib.load().ds4b200_hc_post_pre_rows_f32(_p(block_out), _p(block_out2), _p(resid), _p(post), _p(comb),
+                                                   _p(fn_f16), _p(scale3), _p(base24), _p(out_hc), _p(post2), _p(comb2),
+                                                   _p(out), T, n, iters, eps, _s()))
+    return out_hc, post2, comb2, out
+
+
 def hc_sinkhorn_rows(logits, iters=20, eps=1e-6):
     """logits [T, 16] -> comb [T, 16]."""
     comb = torch.empty_like(logits)

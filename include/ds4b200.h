@@ -358,6 +358,17 @@ int ds4b200_hc_post_rows_f32(const float *block_out, const float *block_out2,
                              const float *residual_hc, const float *post, const float *comb,
                              float *out_hc, int64_t n_tokens, int n_embd, void *stream);
 
+/* The post step of one sub-block followed by the pre step of the next (cuda/forward_layer.cu:1217 ->
+ * :1235 inside a layer, :1456 -> :808 across layers): out_hc = post(block_out [+ block_out2],
+ * residual_hc, post_in, comb_in), then (post, comb, out) = pre(out_hc, hc_fn, hc_scale, hc_base).  Same
+ * bits as the two entry points called one after the other, which is what it does: two launches (post
+ * and comb may be the buffers post_in and comb_in point to). */
+int ds4b200_hc_post_pre_rows_f32(const float *block_out, const float *block_out2, const float *residual_hc,
+                                 const float *post_in, const float *comb_in, const uint16_t *hc_fn,
+                                 const float *hc_scale, const float *hc_base, float *out_hc, float *post,
+                                 float *comb, float *out, int64_t n_tokens, int n_embd, int sinkhorn_iters,
+                                 float eps, void *stream);
+
 /* Output HC head for n_tokens tokens (cuda/output_head.cu:62-149): RMS over the 4*n_embd
  * block, 4-row f16 matvec, w[h] = sigmoid(pre[h]*scale[0]+base[h]) + eps, out[t] = sum_h
  * w[h]*resid[t][h].  With norm_w given, the output RMSNorm that follows it in the forward

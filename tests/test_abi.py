@@ -148,6 +148,11 @@ def test_checked_entry_points_reject_bad_arguments_without_a_gpu(lib):
     assert lib.ds4b200_hc_pre_rows_f32(p, p, p, p, p, p, p, 2, 4096, 0, 1e-6, None) == EINVAL
     assert lib.ds4b200_hc_post_rows_f32(p, None, p, None, p, p, 2, 4096, None) == EINVAL
     assert lib.ds4b200_hc_post_rows_f32(None, p, p, None, p, p, 2, 4096, None) == EINVAL
+    assert lib.ds4b200_hc_post_pre_rows_f32(p, None, p, p, p, p, p, p, p, p, p, p, 2, 4096, 20, 1e-6, None) == EINVAL   # out_hc aliases the input
+    q2 = C.c_void_p(0x2000)
+    assert lib.ds4b200_hc_post_pre_rows_f32(p, None, p, None, p, p, p, p, q2, p, p, q2, 2, 4096, 20, 1e-6, None) == EINVAL   # block without post
+    assert lib.ds4b200_hc_post_pre_rows_f32(None, None, p, None, p, p, p, p, q2, p, p, q2, 2, 4096, 0, 1e-6, None) == EINVAL   # iters
+    assert lib.ds4b200_hc_post_pre_rows_f32(None, None, p, None, p, p, p, p, q2, p, p, q2, 0, 4096, 20, 1e-6, None) == 0
     assert lib.ds4b200_hc_sinkhorn_mix_rows_f32(None, p, p, None, 2, 4096, 20, 1e-6, None) == EINVAL
     assert lib.ds4b200_swiglu_q8_0_rows_f32(p, p, None, p, p, None, 2, 1, 2000, 0, 0.0, 0, None) == EINVAL   # n % 32
     assert lib.ds4b200_swiglu_q8_0_rows_f32(p, p, None, None, p, None, 2, 1, 2048, 0, 0.0, 0, None) == EINVAL

@@ -584,6 +584,26 @@ def test_hc_pre_tensor_core_kernel_against_the_reference_kernel_token_by_token(o
     assert_close(host(out), host(rout), what="out vs reference kernel")
 
 
+@pytest.mark.parametrize("T", [5, 130])
+def test_hc_post_then_pre_entry_point(ops, T):
+    """ds4b200_hc_post_pre_rows_f32 == hc_post_rows followed by hc_pre_rows, bit for bit, with and without the
+    second block term."""
+    g = inputs.rng(704 + T)
+    n = 4096
+    resid, block, block2 = dev(inputs.normal(g, (T, 4, n))), dev(inputs.normal(g, (T, n))), dev(inputs.normal(g, (T, n)))
+    post, comb = dev(inputs.uniform(g, (T, 4), 0.0, 2.0)), dev(inputs.uniform(g, (T, 16), 0.0, 0.5))
+    wts = inputs.hc_pre_weights(10, n)
+    fn, scale, base = dev(wts["fn"]), dev(wts["scale"]), dev(wts["base"])
+    for b2 in (None, block2):
+        mid = ops.hc_post_rows(block, resid, post, comb, block_out2=b2)
+        want = ops.hc_pre_rows(mid, fn, scale, base)
+        got = ops.hc_post_pre_rows(block, resid, post, comb, fn, scale, base, block_out2=b2)
+        assert torch.equal(got[0], mid)
+        for a, b in zip(got[1:], want):
+            assert torch.equal(a, b)
+    assert ops.device_status() == 0
+
+
 def test_hc_pre_of_a_token_does_not_depend_on_its_place_in_the_batch(ops):
     """The tcgen05 kernel on a batch and on slices of it (other step, other cluster, the short last step, another
     turn of the operand groups): every token's outputs keep their bits, which is what lets a batch be split over
