@@ -204,6 +204,14 @@ __global__ void swiglu_scalar_kernel(const float *gate, const float *up, const f
     }
 }
 
+// One decode row without slots, weights or a sum: no loop, 32-bit index.
+template <int MODE, bool FAST>
+__global__ void swiglu_row_kernel(const float *__restrict__ gate, const float *__restrict__ up, float *__restrict__ out,
+                                  int n, float clamp) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = glu_one<MODE, FAST>(gate[i], up[i], clamp);
+}
+
 // Counts (n, d) pairs, d in [1, 2], n spread over +-2^-40..2^40 and signs, for which
 // div_by_1to2 differs from the IEEE division, plus (a, b) pairs for which div_with_rcp does, plus block
 // maxima for which q8_0_block_scale differs from amax / 127 and its IEEE reciprocal, or q8k_block_scale from
@@ -259,6 +267,11 @@ void launch_mode(const float *gate, const float *up, const float *weights, float
     // A single decode row (a few thousand elements) is latency-bound: one element per
     // thread over many small CTAs finishes sooner than four per thread over two CTAs.
     const bool tiny = n_tokens * (int64_t)n <= 8192;
+    if (tiny && k == 1 && !weights) {
+        const int total = (int)(n_tokens * n);
+        swiglu_row_kernel<MODE, FAST><<<(unsigned)((total + 127) / 128), 128, 0, s>>>(gate, up, out, total, clamp);
+        return;
+    }
     if (!vec || tiny) {
         const int threads = tiny ? 128 : kThreads;
         int64_t blocks = (n_tokens * n + threads - 1) / threads;

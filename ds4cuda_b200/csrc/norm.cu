@@ -293,6 +293,12 @@ __global__ void add_scalar_kernel(const float *__restrict__ a, const float *__re
         y[i] = a[i] + b[i];
 }
 
+// one decode row: no loop, 32-bit index
+__global__ void add_row_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ y, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] = a[i] + b[i];
+}
+
 template <int VPT>
 void launch_cta(const NormArgs &a, int threads, cudaStream_t s) {
     if (a.kq) rms_norm_cta_kernel<VPT, true><<<(unsigned)a.n_rows, threads, 0, s>>>(a);
@@ -310,6 +316,12 @@ void launch_warp(const NormArgs &a, cudaStream_t s) {
 void add_f32(const float *a, const float *b, float *y, int64_t n, cudaStream_t s) {
     if (n <= 0) return;
     constexpr int kThreads = 256;
+    if (n <= 8192) {
+        // one decode row is latency-bound: one element per thread over many small CTAs finishes sooner than
+        // four per thread over a few
+        add_row_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(a, b, y, (int)n);
+        return;
+    }
     if (aligned16(a) && aligned16(b) && aligned16(y) && (n & 3) == 0) {
         const int64_t n4 = n >> 2;
         const int64_t blocks = (n4 + kThreads - 1) / kThreads;
