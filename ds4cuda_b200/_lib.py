@@ -61,6 +61,7 @@ class LayerBuffers(C.Structure):
 
 STAGE_QKV_A, STAGE_Q_B, STAGE_ATTENTION, STAGE_ATTN_OUT, STAGE_FFN_UP, STAGE_FFN_DOWN = range(6)
 StageHook = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int, C.c_int64, C.c_void_p)
+ChunkHook = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_void_p)
 
 TABLE_F16, TABLE_Q8_0 = 0, 1
 FP8_BLOCK64_POW2, FP8_ROW_AMAX = 0, 1
@@ -124,6 +125,8 @@ SIGNATURES = {
     "ds4b200_e4m3_selfcheck": (_I, [C.c_uint32, C.c_uint64, _P, _P]),
     "ds4b200_layer_rows_f32": (_I, [C.POINTER(LayerDims), C.POINTER(LayerWeights), C.POINTER(LayerBuffers), _P, _P, _L, _P,
                                StageHook, _P, _P]),
+    "ds4b200_chunk_rows_f32": (_I, [C.POINTER(LayerDims), C.POINTER(LayerWeights), _I, _I, C.POINTER(LayerBuffers), _P, _P, _P,
+                               _L, ChunkHook, _P, _P, C.POINTER(C.c_void_p)]),
     "ds4b200_swiglu_q8_K_rows_f32": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, C.c_float, _I, _P]),
     "ds4b200_swiglu_q8_0_rows_f32": (_I, [_P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _F, _I, _P]),
     "ds4b200_compressor_chunk_f32": (_I, [_I, _P, _P, _P, _P, _I, _I, _I, _L, _I, _P, _P, _P, _P]),

@@ -124,3 +124,40 @@ extern "C" int ds4b200_layer_rows_f32(const ds4b200_layer_dims *d, const ds4b200
                           0, 0.0f, s);
     return launch_ok("add + hc ffn post");
 }
+
+namespace {
+
+struct ChunkHook {
+    ds4b200_chunk_hook hook;
+    void *user;
+    int il;
+};
+
+int chunk_stage(void *user, int stage, int64_t n_tokens, void *stream) {
+    const ChunkHook *c = static_cast<const ChunkHook *>(user);
+    return c->hook(c->user, c->il, stage, n_tokens, stream);
+}
+
+}  // namespace
+
+extern "C" int ds4b200_chunk_rows_f32(const ds4b200_layer_dims *dims, const ds4b200_layer_weights *weights,
+                                      int n_layers, int first_layer, const ds4b200_layer_buffers *b, float *resid_a,
+                                      float *resid_b, const int32_t *pos, int64_t T, ds4b200_chunk_hook hook,
+                                      void *user, void *stream, float **resid_final) {
+    if (!dims || !weights || !b || !resid_a || !resid_b || !pos || !hook)
+        return set_error(-EINVAL, "chunk_rows: null argument");
+    if (n_layers < 0 || first_layer < 0) return set_error(-EINVAL, "chunk_rows: negative layer count or index");
+    if (resid_a == resid_b) return set_error(-EINVAL, "chunk_rows: resid_a and resid_b are the same buffer");
+    if (T < 0) return set_error(-EINVAL, "chunk_rows: negative token count");
+    float *cur = resid_a, *next = resid_b;
+    for (int i = 0; i < n_layers && T > 0; ++i) {
+        ds4b200_layer_dims d = *dims;
+        d.il = first_layer + i;
+        ChunkHook c{hook, user, d.il};
+        const int rc = ds4b200_layer_rows_f32(&d, &weights[i], b, cur, pos, T, next, chunk_stage, &c, stream);
+        if (rc) return rc;
+        float *t = cur; cur = next; next = t;
+    }
+    if (resid_final) *resid_final = cur;
+    return 0;
+}

@@ -123,6 +123,20 @@ int ds4b200_layer_rows_f32(const ds4b200_layer_dims *dims, const ds4b200_layer_w
                            int64_t n_tokens, float *resid_out, ds4b200_stage_hook hook, void *user,
                            void *stream);
 
+/* The layers of a chunk: the batched counterpart of the layer loop of ds4_forward_chunk
+ * (cuda/forward_batch.cu:264-284 run for all T tokens at once instead of token by token).  Layers
+ * first_layer .. first_layer + n_layers - 1 run in turn through ds4b200_layer_rows_f32 with weights[i]
+ * (an array of n_layers entries) and the RoPE parameters of their index (dims->il is ignored); the
+ * residual streams alternate between resid_a (holding the chunk's streams on entry) and resid_b, as the
+ * reference's HC ping / pong buffers do (cuda/session_state.cu:12-19).  *resid_final (host, nullable)
+ * receives the buffer that holds the streams after the last layer.  The hook gets the layer index. */
+typedef int (*ds4b200_chunk_hook)(void *user, int il, int stage, int64_t n_tokens, void *stream);
+
+int ds4b200_chunk_rows_f32(const ds4b200_layer_dims *dims, const ds4b200_layer_weights *weights, int n_layers,
+                           int first_layer, const ds4b200_layer_buffers *b, float *resid_a, float *resid_b,
+                           const int32_t *pos, int64_t n_tokens, ds4b200_chunk_hook hook, void *user, void *stream,
+                           float **resid_final);
+
 #ifdef __cplusplus
 }
 #endif

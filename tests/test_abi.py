@@ -180,6 +180,17 @@ def test_checked_entry_points_reject_bad_arguments_without_a_gpu(lib):
     bad_dims = LayerDims(4096, 64, 500, 64, 1024, 2048, 6, 20, 2, 1, 1e-6, 10.0)
     assert lib.ds4b200_layer_rows_f32(C.byref(bad_dims), C.byref(wts), C.byref(bufs), p, p, 4, p, hook, None, None) == EINVAL
     assert b"geometry" in lib.ds4b200_last_error()
+    from ds4cuda_b200._lib import ChunkHook
+    chook = ChunkHook(lambda user, il, stage, n, stream: 0)
+    final = C.c_void_p()
+    assert lib.ds4b200_chunk_rows_f32(C.byref(dims), C.byref(wts), 2, 0, C.byref(bufs), p, p, p, 4, chook, None, None, C.byref(final)) == EINVAL
+    assert b"same buffer" in lib.ds4b200_last_error()
+    other = C.c_void_p(0x2000)
+    assert lib.ds4b200_chunk_rows_f32(C.byref(dims), C.byref(wts), -1, 0, C.byref(bufs), p, other, p, 4, chook, None, None, None) == EINVAL
+    assert lib.ds4b200_chunk_rows_f32(C.byref(dims), C.byref(wts), 2, 0, C.byref(bufs), p, other, p, 4, chook, None, None, None) == EINVAL
+    assert b"null weight or buffer" in lib.ds4b200_last_error()          # the first layer's own check
+    assert lib.ds4b200_chunk_rows_f32(C.byref(dims), C.byref(wts), 0, 0, C.byref(bufs), p, other, p, 4, chook, None, None, C.byref(final)) == 0
+    assert final.value == p.value                                        # no layer: the streams stay where they were
     # optional buffers come in groups: kqv_q with kqv_scale; ffn_kq with ffn_kscale and ffn_kbsums
     a = 0x1000
     full = {n: a for n in LayerBuffers.NAMES}

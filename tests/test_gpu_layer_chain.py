@@ -220,3 +220,91 @@ def test_layer_rows_entry_point_sequences_the_same_chain(ops):
                                     pos.data_ptr(), T, out.data_ptr(), bad, None, None) == -7
     assert b"stage 1" in L.ds4b200_last_error()
     torch.cuda.synchronize()
+
+
+def test_chunk_rows_runs_the_layers_in_turn(ops):
+    """ds4b200_chunk_rows_f32 over three layers (indices 1..3: both RoPE parameter sets) == three calls of
+    ds4b200_layer_rows_f32 with the streams handed from one to the next; the hook sees (layer, stage)."""
+    import ctypes as C
+    from ds4cuda_b200 import _lib
+    L = _lib.load()
+    T, n, H, hd, ql, ff, k = 70, 4096, 64, 512, 1024, 2048, 6
+    n_layers, first = 3, 1
+    g = inputs.rng(996)
+    resid0 = dev(inputs.normal(g, (T, 4, n)))
+    pos = dev((200 + np.arange(T)).astype(np.int32))
+    per_layer = []
+    for i in range(n_layers):
+        wa, wf = inputs.hc_pre_weights(20 + 2 * i, n), inputs.hc_pre_weights(21 + 2 * i, n)
+        per_layer.append(dict(hc_attn_fn=dev(wa["fn"]), hc_attn_scale=dev(wa["scale"]), hc_attn_base=dev(wa["base"]),
+                              attn_norm=dev(inputs.uniform(g, (n,), 0.5, 1.5)), q_a_norm=dev(inputs.uniform(g, (ql,), 0.5, 1.5)),
+                              kv_a_norm=dev(inputs.uniform(g, (hd,), 0.5, 1.5)), hc_ffn_fn=dev(wf["fn"]),
+                              hc_ffn_scale=dev(wf["scale"]), hc_ffn_base=dev(wf["base"]),
+                              ffn_norm=dev(inputs.uniform(g, (n,), 0.5, 1.5))))
+    # stand-ins for what the caller's matvecs / attention would write, one set per layer
+    shapes = dict(q_lora=(T, ql), kv_raw=(T, hd), q=(T, H, hd), kqv=(T, H, hd), attn_out=(T, n), sh_gate=(T, 1, ff),
+                  sh_up=(T, 1, ff), gate=(T, k, ff), up=(T, k, ff), moe_out=(T, n), shexp_out=(T, n))
+    S = [{nm: dev(inputs.normal(g, shp)) for nm, shp in shapes.items()} for _ in range(n_layers)]
+    for s in S:
+        s["router_w"] = dev(inputs.router_weights(g, T, k))
+    f32 = lambda *shape: torch.zeros(*shape, device="cuda")
+    B = dict(x=f32(T, n), x_norm=f32(T, n), xq=torch.zeros(T, n, dtype=torch.int8, device="cuda"), xscale=f32(T, n // 32),
+             q_lora=f32(T, ql), q_lora_norm=f32(T, ql), kv_raw=f32(T, hd), raw_rows=f32(T, hd), q=f32(T, H, hd),
+             kqv=f32(T, H, hd), attn_out=f32(T, n), post=f32(T, 4), comb=f32(T, 16), resid_mid=f32(T, 4, n),
+             sh_gate=f32(T, 1, ff), sh_up=f32(T, 1, ff), sh_mid=f32(T, 1, ff), gate=f32(T, k, ff), up=f32(T, k, ff),
+             router_w=f32(T, k), mid_q=torch.zeros(T, k, ff, dtype=torch.int8, device="cuda"),
+             mid_scale=f32(T, k, ff // 256), mid_bsums=torch.zeros(T, k, ff // 256, 16, dtype=torch.int16, device="cuda"),
+             moe_out=f32(T, n), shexp_out=f32(T, n))
+    fills = {_lib.STAGE_QKV_A: ("q_lora", "kv_raw"), _lib.STAGE_Q_B: ("q",), _lib.STAGE_ATTENTION: ("kqv",),
+             _lib.STAGE_ATTN_OUT: ("attn_out",), _lib.STAGE_FFN_UP: ("sh_gate", "sh_up", "gate", "up", "router_w"),
+             _lib.STAGE_FFN_DOWN: ("moe_out", "shexp_out")}
+
+    def fill(layer, stage):
+        for name in fills[stage]:
+            B[name].copy_(S[layer][name])
+
+    buffers = _lib.LayerBuffers(*[B[nm].data_ptr() for nm in _lib.LayerBuffers.NAMES])
+    W = (_lib.LayerWeights * n_layers)(*[_lib.LayerWeights(*[w[nm].data_ptr() for nm in _lib.LayerWeights.NAMES])
+                                        for w in per_layer])
+    # layer by layer
+    cur, nxt = resid0.clone(), torch.zeros_like(resid0)
+    raws = []
+    for i in range(n_layers):
+        dims = _lib.LayerDims(n, H, hd, 64, ql, ff, k, 20, first + i, 1, 1e-6, 10.0)
+        cb = _lib.StageHook(lambda user, stage, n_tokens, stream, i=i: fill(i, stage) or 0)
+        rc = L.ds4b200_layer_rows_f32(C.byref(dims), C.byref(W[i]), C.byref(buffers), cur.data_ptr(), pos.data_ptr(), T,
+                                      nxt.data_ptr(), cb, None, None)
+        assert rc == 0, L.ds4b200_last_error()
+        raws.append(B["raw_rows"].clone())
+        cur, nxt = nxt, cur
+    want = cur.clone()
+    # the same through one call
+    a, b = resid0.clone(), torch.zeros_like(resid0)
+    seen, raws2 = [], []
+
+    def chook(user, il, stage, n_tokens, stream):
+        seen.append((il, stage))
+        if stage == _lib.STAGE_Q_B:
+            raws2.append(B["raw_rows"].clone())
+        fill(il - first, stage)
+        return 0
+
+    dims = _lib.LayerDims(n, H, hd, 64, ql, ff, k, 20, 99, 1, 1e-6, 10.0)       # il is taken from the loop, not from here
+    final = C.c_void_p()
+    cb2 = _lib.ChunkHook(chook)
+    rc = L.ds4b200_chunk_rows_f32(C.byref(dims), W, n_layers, first, C.byref(buffers), a.data_ptr(), b.data_ptr(),
+                                  pos.data_ptr(), T, cb2, None, None, C.byref(final))
+    assert rc == 0, L.ds4b200_last_error()
+    torch.cuda.synchronize()
+    assert seen == [(first + i, st) for i in range(n_layers) for st in range(6)]
+    got = a if final.value == a.data_ptr() else b
+    assert final.value == (b if n_layers % 2 else a).data_ptr()
+    assert torch.equal(got, want)
+    for r1, r2 in zip(raws, raws2):
+        assert torch.equal(r1, r2)                                               # the KV rows, RoPE of each layer's index
+    # a failing hook stops the chunk with its code
+    stop = _lib.ChunkHook(lambda user, il, stage, n_tokens, stream: -9 if (il, stage) == (first + 1, 2) else 0)
+    assert L.ds4b200_chunk_rows_f32(C.byref(dims), W, n_layers, first, C.byref(buffers), a.data_ptr(), b.data_ptr(),
+                                    pos.data_ptr(), T, stop, None, None, None) == -9
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
